@@ -1,0 +1,639 @@
+// The litnicelm `backend.library` plugin table (BackendApiV1, version 16)
+// implemented on CUDA. Each entry mirrors the behaviour of DefaultCpuBackend
+// (litnicelm src/model/backend/device_backend.cpp:657-1775) for the views the
+// host builds, and reports failures as C++ exceptions, which is the contract of
+// the loader (device_backend.cpp:182-230, main.cpp:37-40).
+//
+// All work of one backend instance is issued on one stream. The only host
+// synchronisation points are the host<->device copies, which the host requires
+// to be complete on return (host_tensor_stage.hpp:120-124, checkpoint.cpp:214-218).
+// Training entries are not implemented and throw; nothing falls back to the CPU.
+#include "common.cuh"
+
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+namespace lb {
+
+namespace {
+
+struct Backend {
+  int device = 0;
+  cudaStream_t st = nullptr;
+  DevErr *err_host = nullptr;  // host-mapped; kernels write, host reads after a sync
+  DevErr *err_dev = nullptr;
+  std::unordered_map<void *, void *> over_aligned;  // user pointer -> cudaMalloc base
+  int ctx_iteration = 0, ctx_group = 0;
+  long long launches = 0;
+};
+
+Backend *self(void *h) {
+  if (h == nullptr) throw std::invalid_argument("litnice_b200: null backend handle");
+  return static_cast<Backend *>(h);
+}
+
+void bind(Backend *b) { LB_CUDA(cudaSetDevice(b->device)); }
+
+void raise_device_error(Backend *b) {
+  if (b->err_host->code == DEVERR_NONE) return;
+  const int code = b->err_host->code, detail = b->err_host->detail;
+  b->err_host->code = DEVERR_NONE;
+  if (code == DEVERR_BAD_TOKEN_ID)
+    throw std::runtime_error("litnice_b200::embedding_lookup: embedding id out of range (id=" +
+                             std::to_string(detail) + ")");
+  throw std::runtime_error("litnice_b200: device error code " + std::to_string(code));
+}
+
+void sync_and_check(Backend *b) {
+  LB_CUDA(cudaStreamSynchronize(b->st));
+  raise_device_error(b);
+}
+
+void require_gpu_f32(LitniceView t, const char *who) {
+  if (t == nullptr) throw std::invalid_argument(std::string(who) + ": null view");
+  if (t->device != 1u) throw std::runtime_error(std::string(who) + " requires a GPU tensor");
+  if (t->dtype != 0u) throw std::runtime_error(std::string(who) + " requires an f32 tensor");
+}
+
+RowView flat_view(LitniceView t) {
+  RowView v{};
+  v.data = static_cast<char *>(t->data);
+  v.np = 0;
+  v.rows = 1;
+  v.cols = view_numel(t);
+  v.cs = 4;
+  return v;
+}
+
+[[noreturn]] void training_entry(const char *name) {
+  throw std::runtime_error(std::string("litnice_b200: ") + name +
+                           " belongs to training and is not implemented by this inference plugin");
+}
+
+// ---- lifecycle ---------------------------------------------------------------
+
+void *api_create(uint32_t device_kind) {
+  // The loader tries GPU (1) first, then CPU (0) (device_backend.cpp:208-220).
+  if (device_kind != 1u) return nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    throw std::runtime_error(std::string("litnice_b200: no CUDA device: ") + cudaGetErrorString(e));
+  int dev = 0;
+  if (const char *env = std::getenv("LITNICE_B200_DEVICE")) dev = std::atoi(env);
+  if (dev < 0 || dev >= count) throw std::runtime_error("litnice_b200: LITNICE_B200_DEVICE out of range");
+  auto *b = new Backend();
+  try {
+    b->device = dev;
+    bind(b);
+    cudaDeviceProp prop{};
+    LB_CUDA(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10)
+      throw std::runtime_error("litnice_b200: this plugin is built for sm_100a (B200) only; found sm_" +
+                               std::to_string(prop.major) + std::to_string(prop.minor));
+    LB_CUDA(cudaStreamCreateWithFlags(&b->st, cudaStreamNonBlocking));
+    LB_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&b->err_host), sizeof(DevErr), cudaHostAllocMapped));
+    b->err_host->code = DEVERR_NONE;
+    b->err_host->detail = 0;
+    LB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&b->err_dev), b->err_host, 0));
+  } catch (...) {
+    delete b;
+    throw;
+  }
+  return b;
+}
+
+void api_destroy(void *h) {
+  if (h == nullptr) return;
+  Backend *b = static_cast<Backend *>(h);
+  cudaSetDevice(b->device);
+  if (b->st) {
+    cudaStreamSynchronize(b->st);
+    cudaStreamDestroy(b->st);
+  }
+  if (b->err_host) cudaFreeHost(b->err_host);
+  delete b;
+}
+
+uint32_t api_device(void *h) {
+  self(h);
+  return 1u;
+}
+
+void *api_alloc(void *h, uint64_t bytes, uint32_t alignment) {
+  Backend *b = self(h);
+  if (bytes == 0) return nullptr;
+  if (alignment == 0 || (alignment & (alignment - 1)) != 0)
+    throw std::invalid_argument("litnice_b200::alloc: invalid alignment");
+  bind(b);
+  void *p = nullptr;
+  if (alignment <= 256) {  // cudaMalloc returns 256-byte aligned memory
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess)
+      throw std::runtime_error(std::string("litnice_b200::alloc failed: ") + cudaGetErrorString(e));
+    return p;
+  }
+  cudaError_t e = cudaMalloc(&p, bytes + alignment);
+  if (e != cudaSuccess)
+    throw std::runtime_error(std::string("litnice_b200::alloc failed: ") + cudaGetErrorString(e));
+  const uintptr_t a = (reinterpret_cast<uintptr_t>(p) + alignment - 1) & ~(uintptr_t)(alignment - 1);
+  b->over_aligned[reinterpret_cast<void *>(a)] = p;
+  return reinterpret_cast<void *>(a);
+}
+
+void api_free(void *h, void *ptr) {
+  Backend *b = self(h);
+  if (ptr == nullptr) return;
+  bind(b);
+  LB_CUDA(cudaStreamSynchronize(b->st));
+  auto it = b->over_aligned.find(ptr);
+  if (it != b->over_aligned.end()) {
+    LB_CUDA(cudaFree(it->second));
+    b->over_aligned.erase(it);
+  } else {
+    LB_CUDA(cudaFree(ptr));
+  }
+}
+
+void api_h2d(void *h, void *dst, const void *src, uint64_t bytes) {
+  Backend *b = self(h);
+  if (bytes == 0) return;
+  if (dst == nullptr || src == nullptr)
+    throw std::invalid_argument("litnice_b200::copy_host2device: null pointer");
+  bind(b);
+  LB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, b->st));
+  LB_CUDA(cudaStreamSynchronize(b->st));
+}
+
+void api_d2h(void *h, void *dst, const void *src, uint64_t bytes) {
+  Backend *b = self(h);
+  if (bytes == 0) return;
+  if (dst == nullptr || src == nullptr)
+    throw std::invalid_argument("litnice_b200::copy_device2host: null pointer");
+  bind(b);
+  LB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, b->st));
+  sync_and_check(b);
+}
+
+BackendMemoryInfo api_memory_info(void *h) {
+  Backend *b = self(h);
+  bind(b);
+  size_t fr = 0, tot = 0;
+  LB_CUDA(cudaMemGetInfo(&fr, &tot));
+  return BackendMemoryInfo{1u, fr, tot};
+}
+
+// ---- elementwise -------------------------------------------------------------
+
+// device_backend.cpp:715-732. Dense f32 views are copied flat; any other view
+// is copied element by element over its full logical shape. (For a rank-3
+// non-dense view the CPU backend walks only dims 0 and 1; every element it
+// writes receives the same value here, and the remaining elements of the
+// logical shape are copied as well.)
+void api_copy(void *h, LitniceView src, LitniceView dst) {
+  Backend *b = self(h);
+  require_gpu_f32(src, "litnice_b200::copy(src)");
+  require_gpu_f32(dst, "litnice_b200::copy(dst)");
+  bind(b);
+  if (view_is_contiguous(src) && view_is_contiguous(dst)) {
+    if (view_numel(src) != view_numel(dst)) throw std::runtime_error("litnice_b200::copy: numel mismatch");
+    launch_rowwise(EW_COPY, flat_view(src), nullptr, 0, 0.f, flat_view(dst), b->st);
+  } else {
+    RowView s = make_row_view(src, "copy(src)"), d = make_row_view(dst, "copy(dst)");
+    if (s.rows != d.rows || s.cols != d.cols) throw std::runtime_error("litnice_b200::copy: shape mismatch");
+    launch_rowwise(EW_COPY, s, nullptr, 0, 0.f, d, b->st);
+  }
+  ++b->launches;
+}
+
+void api_fill(void *h, LitniceView t, float v) {
+  Backend *b = self(h);
+  require_gpu_f32(t, "litnice_b200::fill");
+  bind(b);
+  RowView o = view_is_contiguous(t) ? flat_view(t) : make_row_view(t, "fill");
+  launch_rowwise(EW_FILL, o, nullptr, 0, v, o, b->st);
+  ++b->launches;
+}
+
+bool is_pos_broadcast(LitniceView a, LitniceView bb, LitniceView out) {
+  return a->rank == 3 && bb->rank == 2 && out->rank == 3 && a->dims[1] == bb->dims[0] &&
+         a->dims[2] == bb->dims[1] && out->dims[0] == a->dims[0] && out->dims[1] == a->dims[1] &&
+         out->dims[2] == a->dims[2];
+}
+
+// device_backend.cpp:752-813, including the rank-3 + rank-2 broadcast used for
+// X += pos_emb[0:s] (transformer.cpp:93-94).
+void api_add(void *h, LitniceView a, LitniceView bb, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(a, "litnice_b200::add(a)");
+  require_gpu_f32(bb, "litnice_b200::add(b)");
+  require_gpu_f32(out, "litnice_b200::add(out)");
+  bind(b);
+  const long long na = view_numel(a), nb = view_numel(bb), no = view_numel(out);
+  if (na == nb && na == no) {
+    if (view_is_contiguous(a) && view_is_contiguous(bb) && view_is_contiguous(out)) {
+      RowView fb = flat_view(bb);
+      launch_rowwise(EW_ADD, flat_view(a), &fb, 0, 0.f, flat_view(out), b->st);
+    } else {
+      RowView ra = make_row_view(a, "add(a)"), rb = make_row_view(bb, "add(b)"),
+              ro = make_row_view(out, "add(out)");
+      if (ra.cols != rb.cols || ra.cols != ro.cols)
+        throw std::runtime_error("litnice_b200::add: last-axis mismatch");
+      launch_rowwise(EW_ADD, ra, &rb, 0, 0.f, ro, b->st);
+    }
+  } else if (is_pos_broadcast(a, bb, out)) {
+    RowView ra = make_row_view(a, "add(a)"), ro = make_row_view(out, "add(out)");
+    RowView rb{};
+    rb.data = static_cast<char *>(bb->data);
+    rb.np = 1;
+    rb.pd[0] = bb->dims[0];
+    rb.ps[0] = bb->strides_bytes[0];
+    rb.rows = bb->dims[0];
+    rb.cols = bb->dims[1];
+    rb.cs = bb->strides_bytes[1];
+    launch_rowwise(EW_ADD, ra, &rb, a->dims[1], 0.f, ro, b->st);
+  } else {
+    throw std::runtime_error("litnice_b200::add: numel or broadcast shape mismatch");
+  }
+  ++b->launches;
+}
+
+void api_add_inplace(void *h, LitniceView a, LitniceView bb) {
+  api_add(h, a, bb, a);
+}
+
+void bias_op(void *h, EwOp op, LitniceView x, LitniceView bias, LitniceView out, const char *who) {
+  Backend *b = self(h);
+  require_gpu_f32(x, who);
+  require_gpu_f32(bias, who);
+  require_gpu_f32(out, who);
+  bind(b);
+  RowView rx = make_row_view(x, who), ro = make_row_view(out, who);
+  if (view_numel(bias) != rx.cols || ro.cols != rx.cols || ro.rows != rx.rows)
+    throw std::runtime_error(std::string(who) + ": semantic shape mismatch");
+  RowView rb{};
+  rb.data = static_cast<char *>(bias->data);
+  rb.np = 0;
+  rb.rows = 1;
+  rb.cols = rx.cols;
+  rb.cs = bias->strides_bytes[bias->rank - 1];
+  launch_rowwise(op, rx, &rb, 1, 0.f, ro, b->st);
+  ++b->launches;
+}
+
+// device_backend.cpp:840-940
+void api_add_bias(void *h, LitniceView x, LitniceView bias, LitniceView out) {
+  bias_op(h, EW_ADD_BIAS, x, bias, out, "litnice_b200::add_bias_rowwise");
+}
+void api_add_bias_relu(void *h, LitniceView x, LitniceView bias, LitniceView out) {
+  bias_op(h, EW_ADD_BIAS_RELU, x, bias, out, "litnice_b200::add_bias_relu_rowwise");
+}
+void api_add_bias_relu_inplace(void *h, LitniceView x, LitniceView bias) {
+  bias_op(h, EW_ADD_BIAS_RELU, x, bias, x, "litnice_b200::add_bias_relu_rowwise_inplace");
+}
+
+void unary_op(void *h, EwOp op, LitniceView x, float s, LitniceView out, const char *who) {
+  Backend *b = self(h);
+  require_gpu_f32(x, who);
+  require_gpu_f32(out, who);
+  bind(b);
+  if (view_numel(x) != view_numel(out)) throw std::runtime_error(std::string(who) + ": numel mismatch");
+  if (view_is_contiguous(x) && view_is_contiguous(out)) {
+    launch_rowwise(op, flat_view(x), nullptr, 0, s, flat_view(out), b->st);
+  } else {
+    RowView rx = make_row_view(x, who), ro = make_row_view(out, who);
+    if (rx.cols != ro.cols || rx.rows != ro.rows) throw std::runtime_error(std::string(who) + ": shape mismatch");
+    launch_rowwise(op, rx, nullptr, 0, s, ro, b->st);
+  }
+  ++b->launches;
+}
+
+// device_backend.cpp:942-964, :978-1001
+void api_mul_scalar(void *h, LitniceView x, float s, LitniceView out) {
+  unary_op(h, EW_MUL_SCALAR, x, s, out, "litnice_b200::mul_scalar");
+}
+void api_relu(void *h, LitniceView x, LitniceView out) {
+  unary_op(h, EW_RELU, x, 0.f, out, "litnice_b200::relu");
+}
+
+// device_backend.cpp:1675-1697
+void api_causal_mask(void *h, LitniceView scores, float neg_inf) {
+  Backend *b = self(h);
+  require_gpu_f32(scores, "litnice_b200::apply_causal_mask_inplace");
+  bind(b);
+  MatView m = make_mat_view(scores, "apply_causal_mask_inplace");
+  if (m.rows != m.cols)
+    throw std::runtime_error("litnice_b200::apply_causal_mask_inplace: scores must end with [T,T]");
+  launch_causal_mask(m, neg_inf, b->st);
+  ++b->launches;
+}
+
+// device_backend.cpp:1345-1366
+void api_embedding(void *h, LitniceView table, LitniceView ids, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(table, "litnice_b200::embedding_lookup(table)");
+  require_gpu_f32(out, "litnice_b200::embedding_lookup(out)");
+  if (ids == nullptr || ids->device != 1u || ids->dtype > 1u)
+    throw std::runtime_error("litnice_b200::embedding_lookup: unsupported index dtype");
+  if (table->rank != 2) throw std::runtime_error("litnice_b200::embedding_lookup: table must be rank 2");
+  bind(b);
+  RowView tv{};
+  tv.data = static_cast<char *>(table->data);
+  tv.np = 1;
+  tv.pd[0] = table->dims[0];
+  tv.ps[0] = table->strides_bytes[0];
+  tv.rows = table->dims[0];
+  tv.cols = table->dims[1];
+  tv.cs = table->strides_bytes[1];
+  RowView iv = make_row_view(ids, "embedding_lookup(ids)");
+  RowView ov = make_row_view(out, "embedding_lookup(out)");
+  if (ov.rows != iv.rows * iv.cols || ov.cols != tv.cols)
+    throw std::runtime_error("litnice_b200::embedding_lookup: shape mismatch");
+  launch_embedding(tv, static_cast<const char *>(ids->data), ids->dtype == 0u ? 1 : 0, iv, ov,
+                   b->err_dev, b->st);
+  ++b->launches;
+}
+
+void api_transpose(void *h, LitniceView x, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(x, "litnice_b200::transpose(x)");
+  require_gpu_f32(out, "litnice_b200::transpose(out)");
+  bind(b);
+  launch_transpose(make_mat_view(x, "transpose(x)"), make_mat_view(out, "transpose(out)"), b->st);
+  ++b->launches;
+}
+
+// ---- norm / softmax ------------------------------------------------------------
+
+// device_backend.cpp:1247-1279
+void api_layernorm(void *h, LitniceView x, LitniceView gamma, LitniceView beta, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(x, "litnice_b200::layernorm_forward(x)");
+  require_gpu_f32(gamma, "litnice_b200::layernorm_forward(gamma)");
+  require_gpu_f32(beta, "litnice_b200::layernorm_forward(beta)");
+  require_gpu_f32(out, "litnice_b200::layernorm_forward(out)");
+  bind(b);
+  RowView rx = make_row_view(x, "layernorm_forward(x)"), ro = make_row_view(out, "layernorm_forward(out)");
+  if (rx.rows != ro.rows || rx.cols != ro.cols || view_numel(gamma) != rx.cols || view_numel(beta) != rx.cols)
+    throw std::runtime_error("litnice_b200::layernorm_forward: shape mismatch");
+  launch_layernorm(rx, static_cast<const float *>(gamma->data), gamma->strides_bytes[gamma->rank - 1],
+                   static_cast<const float *>(beta->data), beta->strides_bytes[beta->rank - 1], ro, b->st);
+  ++b->launches;
+}
+
+// device_backend.cpp:1466-1517
+void api_softmax_rows(void *h, LitniceView x, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(x, "litnice_b200::softmax_rows(x)");
+  require_gpu_f32(out, "litnice_b200::softmax_rows(out)");
+  bind(b);
+  RowView rx = make_row_view(x, "softmax_rows(x)"), ro = make_row_view(out, "softmax_rows(out)");
+  if (rx.rows != ro.rows || rx.cols != ro.cols) throw std::runtime_error("litnice_b200::softmax_rows: shape mismatch");
+  launch_softmax_rows(rx, ro, 0, 1.0f, b->st);
+  ++b->launches;
+}
+
+// device_backend.cpp:1554-1592
+void api_causal_softmax(void *h, LitniceView scores, float scale, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(scores, "litnice_b200::scaled_causal_softmax_rows(scores)");
+  require_gpu_f32(out, "litnice_b200::scaled_causal_softmax_rows(out)");
+  bind(b);
+  RowView rx = make_row_view(scores, "scaled_causal_softmax_rows(scores)"),
+          ro = make_row_view(out, "scaled_causal_softmax_rows(out)");
+  if (rx.rows != ro.rows || rx.cols != ro.cols)
+    throw std::runtime_error("litnice_b200::scaled_causal_softmax_rows: shape mismatch");
+  launch_softmax_rows(rx, ro, 1, scale, b->st);
+  ++b->launches;
+}
+
+// ---- matrix products -------------------------------------------------------------
+
+MatView transposed(MatView v) {
+  std::swap(v.rows, v.cols);
+  std::swap(v.rs, v.cs);
+  return v;
+}
+
+MatView shared_matrix(LitniceView t, const char *who) {  // rank-2 operand used by every batch
+  MatView v = make_mat_view(t, who);
+  if (t->rank != 2) throw std::runtime_error(std::string(who) + ": rank-2 matrix required");
+  return v;
+}
+
+void run_gemm(Backend *b, const MatView &a, const MatView &bm, const MatView &c, const char *who) {
+  if (a.cols != bm.rows || c.rows != a.rows || c.cols != bm.cols)
+    throw std::runtime_error(std::string(who) + ": inner or output dimension mismatch");
+  if (a.batch != c.batch || (bm.batch != 1 && bm.batch != c.batch))
+    throw std::runtime_error(std::string(who) + ": batch mismatch");
+  bind(b);
+  launch_gemm_simt(a, bm, c, c.rows, c.cols, a.cols, GemmEpilogue{}, b->st);
+  ++b->launches;
+}
+
+// device_backend.cpp:1096-1110
+void api_gemm(void *h, LitniceView a, LitniceView bb, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(a, "litnice_b200::gemm(a)");
+  require_gpu_f32(bb, "litnice_b200::gemm(b)");
+  require_gpu_f32(out, "litnice_b200::gemm(out)");
+  run_gemm(b, make_mat_view(a, "gemm(a)"), make_mat_view(bb, "gemm(b)"), make_mat_view(out, "gemm(out)"),
+           "litnice_b200::gemm");
+}
+
+// device_backend.cpp:1112-1131
+void api_gemm_ranked_matrix_rhs(void *h, LitniceView a, LitniceView bb, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(a, "litnice_b200::gemm_ranked_matrix_rhs(a)");
+  require_gpu_f32(bb, "litnice_b200::gemm_ranked_matrix_rhs(b)");
+  require_gpu_f32(out, "litnice_b200::gemm_ranked_matrix_rhs(out)");
+  run_gemm(b, make_mat_view(a, "gemm_ranked_matrix_rhs(a)"), shared_matrix(bb, "gemm_ranked_matrix_rhs(b)"),
+           make_mat_view(out, "gemm_ranked_matrix_rhs(out)"), "litnice_b200::gemm_ranked_matrix_rhs");
+}
+
+// device_backend.cpp:1175-1193
+void api_gemm_batched(void *h, LitniceView a, LitniceView bb, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(a, "litnice_b200::gemm_batched(a)");
+  require_gpu_f32(bb, "litnice_b200::gemm_batched(b)");
+  require_gpu_f32(out, "litnice_b200::gemm_batched(out)");
+  run_gemm(b, make_mat_view(a, "gemm_batched(a)"), make_mat_view(bb, "gemm_batched(b)"),
+           make_mat_view(out, "gemm_batched(out)"), "litnice_b200::gemm_batched");
+}
+
+// device_backend.cpp:1216-1235: out[r,c] = sum_k a[r,k] * b[c,k]
+void api_gemm_batched_rhs_t(void *h, LitniceView a, LitniceView bb, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(a, "litnice_b200::gemm_batched_rhs_t(a)");
+  require_gpu_f32(bb, "litnice_b200::gemm_batched_rhs_t(b)");
+  require_gpu_f32(out, "litnice_b200::gemm_batched_rhs_t(out)");
+  run_gemm(b, make_mat_view(a, "gemm_batched_rhs_t(a)"), transposed(make_mat_view(bb, "gemm_batched_rhs_t(b)")),
+           make_mat_view(out, "gemm_batched_rhs_t(out)"), "litnice_b200::gemm_batched_rhs_t");
+}
+
+// ---- exec-context lanes ------------------------------------------------------------
+// The multistream attention variant brackets per-head work with these calls
+// (self_attention_fused_inplace_multistream.cpp:71-87). One in-order stream
+// already keeps the GPU busy for these shapes, so the lanes are serial aliases;
+// only the nesting is validated.
+
+uint32_t api_supports_ctx(void *h) {
+  self(h);
+  return 1u;
+}
+void api_start_iter(void *h) {
+  Backend *b = self(h);
+  if (b->ctx_iteration) throw std::runtime_error("litnice_b200: exec context iteration already started");
+  b->ctx_iteration = 1;
+}
+void api_finish_iter(void *h) {
+  Backend *b = self(h);
+  if (!b->ctx_iteration || b->ctx_group) throw std::runtime_error("litnice_b200: exec context iteration not open");
+  b->ctx_iteration = 0;
+}
+void api_start_group(void *h) {
+  Backend *b = self(h);
+  if (!b->ctx_iteration || b->ctx_group) throw std::runtime_error("litnice_b200: exec context group misuse");
+  b->ctx_group = 1;
+}
+void api_finish_group(void *h) {
+  Backend *b = self(h);
+  if (!b->ctx_group) throw std::runtime_error("litnice_b200: exec context group not open");
+  b->ctx_group = 0;
+}
+void require_group(void *h, const char *who) {
+  if (!self(h)->ctx_group) throw std::runtime_error(std::string(who) + ": no exec context group is open");
+}
+void api_gemm_batched_ctx(void *h, LitniceView a, LitniceView bb, LitniceView out) {
+  require_group(h, "litnice_b200::gemm_batched_exec_context");
+  api_gemm_batched(h, a, bb, out);
+}
+void api_gemm_batched_rhs_t_ctx(void *h, LitniceView a, LitniceView bb, LitniceView out) {
+  require_group(h, "litnice_b200::gemm_batched_rhs_t_exec_context");
+  api_gemm_batched_rhs_t(h, a, bb, out);
+}
+void api_causal_softmax_ctx(void *h, LitniceView scores, float scale, LitniceView out) {
+  require_group(h, "litnice_b200::scaled_causal_softmax_rows_exec_context");
+  api_causal_softmax(h, scores, scale, out);
+}
+
+// ---- training entries: not implemented ---------------------------------------------
+
+float api_sum_squares(void *, LitniceView) { training_entry("sum_squares_f32"); }
+void api_relu_backward(void *, LitniceView, LitniceView, LitniceView) { training_entry("relu_backward"); }
+void api_relu_backward_inplace(void *, LitniceView, LitniceView) { training_entry("relu_backward_inplace"); }
+void api_row_sum(void *, LitniceView, LitniceView) { training_entry("row_sum"); }
+void api_gemm_ranked_matrix_rhs_t(void *, LitniceView, LitniceView, LitniceView) { training_entry("gemm_ranked_matrix_rhs_t"); }
+void api_gemm_ranked_reduce_lhs_t(void *, LitniceView, LitniceView, LitniceView) { training_entry("gemm_ranked_reduce_lhs_t"); }
+void api_gemm_batched_lhs_t(void *, LitniceView, LitniceView, LitniceView) { training_entry("gemm_batched_lhs_t"); }
+void api_gemm_batched_lhs_t_ctx(void *, LitniceView, LitniceView, LitniceView) { training_entry("gemm_batched_lhs_t_exec_context"); }
+void api_layernorm_backward(void *, LitniceView, LitniceView, LitniceView, LitniceView, LitniceView, LitniceView) { training_entry("layernorm_backward"); }
+void api_accumulate_embedding_grads(void *, LitniceView, LitniceView, LitniceView, LitniceView) { training_entry("accumulate_embedding_grads"); }
+void api_cross_entropy_mean(void *, LitniceView, LitniceView, LitniceView) { training_entry("cross_entropy_mean"); }
+void api_cross_entropy_mean_backward_inplace(void *, LitniceView, LitniceView, LitniceView) { training_entry("cross_entropy_mean_backward_inplace"); }
+void api_backward_from_logits_targets(void *, LitniceView, LitniceView) { training_entry("backward_from_logits_targets"); }
+void api_softmax_backward_rows(void *, LitniceView, LitniceView, LitniceView) { training_entry("softmax_backward_rows"); }
+void api_softmax_backward_causal_rows(void *, LitniceView, LitniceView, LitniceView) { training_entry("softmax_backward_causal_rows"); }
+void api_softmax_backward_causal_rows_ctx(void *, LitniceView, LitniceView, LitniceView) { training_entry("softmax_backward_causal_rows_exec_context"); }
+void api_adamw_step(void *, LitniceView, LitniceView, LitniceView, LitniceView, uint64_t, float, float, float, float, uint32_t) { training_entry("adamw_step"); }
+
+// device_backend.cpp:1426-1428: synchronous scalar read.
+float api_read_scalar(void *h, LitniceView x) {
+  Backend *b = self(h);
+  require_gpu_f32(x, "litnice_b200::read_scalar_f32");
+  bind(b);
+  float v = 0.f;
+  LB_CUDA(cudaMemcpyAsync(&v, x->data, sizeof(float), cudaMemcpyDeviceToHost, b->st));
+  sync_and_check(b);
+  return v;
+}
+
+// device_backend.cpp:1752-1775. No caller exists in the host code; the file
+// range is staged through host memory and copied to the device.
+uint32_t api_file2device_supported(void *h) {
+  self(h);
+  return 1u;
+}
+void api_read_file2device(void *h, const char *path, void *dst, uint64_t size, uint64_t file_offset) {
+  Backend *b = self(h);
+  if (size == 0) return;
+  if (dst == nullptr || path == nullptr)
+    throw std::invalid_argument("litnice_b200::read_file2device: null argument");
+  std::ifstream in(path, std::ios::binary);
+  if (!in) throw std::runtime_error("litnice_b200::read_file2device: failed to open file");
+  in.seekg(static_cast<std::streamoff>(file_offset), std::ios::beg);
+  if (!in) throw std::runtime_error("litnice_b200::read_file2device: failed to seek file");
+  std::vector<char> buf(static_cast<size_t>(size));
+  in.read(buf.data(), static_cast<std::streamsize>(size));
+  if (in.gcount() != static_cast<std::streamsize>(size))
+    throw std::runtime_error("litnice_b200::read_file2device: short read");
+  api_h2d(b, dst, buf.data(), size);
+}
+
+const BackendApiV1 kApi = {
+    LITNICE_BACKEND_ABI_VERSION,
+    api_create,
+    api_destroy,
+    api_device,
+    api_alloc,
+    api_free,
+    api_h2d,
+    api_d2h,
+    api_copy,
+    api_fill,
+    api_add,
+    api_add_inplace,
+    api_add_bias,
+    api_add_bias_relu,
+    api_add_bias_relu_inplace,
+    api_mul_scalar,
+    api_sum_squares,
+    api_relu,
+    api_relu_backward,
+    api_relu_backward_inplace,
+    api_row_sum,
+    api_gemm,
+    api_gemm_ranked_matrix_rhs,
+    api_gemm_ranked_matrix_rhs_t,
+    api_gemm_ranked_reduce_lhs_t,
+    api_gemm_batched,
+    api_gemm_batched_lhs_t,
+    api_gemm_batched_rhs_t,
+    api_transpose,
+    api_layernorm,
+    api_layernorm_backward,
+    api_embedding,
+    api_accumulate_embedding_grads,
+    api_cross_entropy_mean,
+    api_cross_entropy_mean_backward_inplace,
+    api_read_scalar,
+    api_backward_from_logits_targets,
+    api_softmax_rows,
+    api_softmax_backward_rows,
+    api_causal_softmax,
+    api_supports_ctx,
+    api_start_iter,
+    api_finish_iter,
+    api_start_group,
+    api_finish_group,
+    api_gemm_batched_ctx,
+    api_gemm_batched_lhs_t_ctx,
+    api_gemm_batched_rhs_t_ctx,
+    api_causal_softmax_ctx,
+    api_softmax_backward_causal_rows_ctx,
+    api_softmax_backward_causal_rows,
+    api_causal_mask,
+    api_adamw_step,
+    api_file2device_supported,
+    api_read_file2device,
+    api_memory_info,
+};
+
+}  // namespace
+}  // namespace lb
+
+extern "C" const BackendApiV1 *litnice_backend_get_api(void) { return &lb::kApi; }

@@ -1,0 +1,176 @@
+// Shared declarations of the B200 plugin: error handling, strided views as
+// the kernels see them, and the launch functions of every kernel family.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+#include "../../include/litnice_backend_b200.h"
+
+namespace lb {
+
+// ---- errors ---------------------------------------------------------------
+
+struct CudaError : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
+inline void cuda_check(cudaError_t e, const char *what, const char *file, int line) {
+  if (e != cudaSuccess) {
+    throw CudaError(std::string("litnice_b200: ") + what + " failed: " + cudaGetErrorString(e) +
+                    " (" + file + ":" + std::to_string(line) + ")");
+  }
+}
+#define LB_CUDA(expr) ::lb::cuda_check((expr), #expr, __FILE__, __LINE__)
+#define LB_LAUNCH_CHECK() ::lb::cuda_check(cudaGetLastError(), "kernel launch", __FILE__, __LINE__)
+
+// Error word written by kernels into host-mapped memory; the host reads it
+// after the next stream synchronisation. Kernels never trap.
+enum DevErrCode : int {
+  DEVERR_NONE = 0,
+  DEVERR_BAD_TOKEN_ID = 1,   // embedding id outside [0, vocab)
+  DEVERR_WAIT_TIMEOUT = 2,   // a bounded mbarrier / TMEM wait ran out
+  DEVERR_BAD_ARGUMENT = 3,
+};
+struct DevErr {
+  int code;
+  int detail;
+};
+
+// ---- views ----------------------------------------------------------------
+
+// Rows of a tensor: every axis but the last forms the row index ("prefix" in
+// the reference, device_backend.cpp:62-125). Axes of extent 1 are dropped and
+// axes that are dense with their neighbour are merged on the host, so np is 0
+// or 1 for every view the inference path hands over.
+struct RowView {
+  char *data;
+  int np;               // number of prefix axes kept
+  long long pd[5];      // prefix extents, outermost first
+  long long ps[5];      // prefix strides in bytes
+  long long rows;       // product of pd
+  long long cols;
+  long long cs;         // stride of the last axis in bytes
+};
+
+// A batch of matrices: the last two axes are (rows, cols), the rest is batch.
+struct MatView {
+  char *data;
+  int nb;
+  long long bd[4];
+  long long bs[4];
+  long long batch;
+  long long rows, cols;
+  long long rs, cs;     // bytes
+};
+
+__host__ __device__ inline long long row_offset(const RowView &v, long long row) {
+  long long off = 0;
+  for (int i = v.np - 1; i >= 0; --i) {
+    const long long q = row / v.pd[i];
+    off += (row - q * v.pd[i]) * v.ps[i];
+    row = q;
+  }
+  return off;
+}
+
+__host__ __device__ inline long long batch_offset(const MatView &v, long long b) {
+  long long off = 0;
+  for (int i = v.nb - 1; i >= 0; --i) {
+    const long long q = b / v.bd[i];
+    off += (b - q * v.bd[i]) * v.bs[i];
+    b = q;
+  }
+  return off;
+}
+
+RowView make_row_view(const BackendTensorView *t, const char *who);
+MatView make_mat_view(const BackendTensorView *t, const char *who);
+bool view_is_contiguous(const BackendTensorView *t);
+long long view_numel(const BackendTensorView *t);
+
+// ---- kernel families (host launchers) ---------------------------------------
+
+// elementwise.cu
+enum EwOp : int { EW_COPY = 0, EW_ADD, EW_ADD_BIAS, EW_ADD_BIAS_RELU, EW_RELU, EW_MUL_SCALAR, EW_FILL };
+// out[row, c] = op(a[row, c], b[...]); b is a full tensor (EW_ADD), a [rows_b, cols]
+// table indexed by row % rows_b (broadcast add), or a bias row.
+void launch_rowwise(EwOp op, const RowView &a, const RowView *b, long long b_mod_rows,
+                    float scalar, const RowView &out, cudaStream_t st);
+void launch_causal_mask(const MatView &scores, float neg_inf, cudaStream_t st);
+void launch_embedding(const RowView &table, const char *ids_data, int ids_is_f32,
+                      const RowView &ids_rows, const RowView &out, DevErr *err, cudaStream_t st);
+void launch_transpose(const MatView &x, const MatView &out, cudaStream_t st);
+
+// norm_softmax.cu
+void launch_layernorm(const RowView &x, const float *gamma, long long gamma_cs, const float *beta,
+                      long long beta_cs, const RowView &out, cudaStream_t st);
+void launch_softmax_rows(const RowView &x, const RowView &out, int causal, float scale,
+                         cudaStream_t st);
+
+// gemm_simt.cu
+struct GemmOperand {
+  const char *data;
+  long long rs, cs;     // strides in BYTES of the logical (row, col) element
+};
+struct GemmEpilogue {
+  const float *bias = nullptr;      // [n]
+  const float *residual = nullptr;  // same layout as C
+  int relu = 0;
+};
+// C[b] (m x n) = A[b] (m x k) * B[b] (k x n), any strides; batch offsets in bytes
+// come from the three MatViews' batch axes (b_batch may be null for a shared B).
+void launch_gemm_simt(const MatView &a, const MatView &bmat, const MatView &c, long long m,
+                      long long n, long long k, const GemmEpilogue &ep, cudaStream_t st);
+
+// native-loop kernels (dense row-major activations) ---------------------------
+
+struct LoopState {
+  int s;        // current context length of every stream
+  int step;     // tokens generated so far
+  int n_streams;
+  int max_seq;
+};
+
+// embed.cu
+void launch_embed_pos(const float *tok_emb, const float *pos_emb, const int *ids, int ids_ld,
+                      const LoopState *state, int n_streams, int s_host, int d, int vocab,
+                      float *x, DevErr *err, cudaStream_t st);
+void launch_gather_last_ln(const float *x, const float *gamma, const float *beta,
+                           const LoopState *state, int n_streams, int s_host, int d, float *out,
+                           cudaStream_t st);
+void launch_layernorm_dense(const float *x, const float *gamma, const float *beta, long long rows,
+                            int d, float *out, cudaStream_t st);
+
+// gemv.cu: out[m, n] = x[m, :] . W[:, n] for m <= 8 rows; W row-major [k, n].
+// scratch must hold gemv_scratch_floats(m, n, k) floats when the launcher
+// decides to split k across CTAs.
+size_t gemv_scratch_floats(int m, int n, int k);
+void launch_gemv(const float *x, int m, const float *w, int k, int n, const float *bias,
+                 float *out, float *scratch, cudaStream_t st);
+
+// attention.cu: ctx[r, h*dh + :] for rows r = b*s + t of qkv [rows, 3*d].
+void launch_attention(const float *qkv, float *ctx, const LoopState *state, int n_streams,
+                      int s_host, int n_heads, int d_model, cudaStream_t st);
+
+// sampler.cu
+struct SamplerParams {
+  float temp;
+  unsigned top_k;
+  float top_p;
+};
+size_t sampler_scratch_bytes(int vocab);
+void launch_sampler(const float *logits, int vocab, int n_streams, const SamplerParams &sp,
+                    unsigned *mt_state, int *ids, int ids_ld, int *out_tokens, int out_ld,
+                    LoopState *state, void *scratch, cudaStream_t st);
+void launch_sampler_rows(const float *logits, int vocab, int n_rows, const SamplerParams &sp,
+                         unsigned *mt_state, int draws, int *out, void *scratch, cudaStream_t st);
+void launch_mt_seed(unsigned *mt_state, const unsigned *seeds, int n, cudaStream_t st);
+void launch_advance_state(LoopState *state, cudaStream_t st);
+void launch_softmax_probs_f64(const float *logits, int vocab, int n_rows, float *probs,
+                              cudaStream_t st);
+
+}  // namespace lb

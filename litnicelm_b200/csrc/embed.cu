@@ -1,0 +1,103 @@
+// Native-loop kernels around the dense activations: token + position
+// embedding, and the final LayerNorm applied to the last row of every stream.
+// Activations of a step are packed as rows r = stream * s + t of a dense
+// [n_streams * s, d] matrix; s is read from the device-resident LoopState so a
+// launch sized for an upper bound `s_cap` serves every shorter context.
+#include "common.cuh"
+
+namespace lb {
+
+namespace {
+
+// Transformer::forward, litnicelm src/model/algo/transformer.cpp:91-94:
+// X = tok_emb[ids] + pos_emb[0:s].
+__global__ void embed_pos_kernel(const float *__restrict__ tok_emb,
+                                 const float *__restrict__ pos_emb, const int *__restrict__ ids,
+                                 int ids_ld, const LoopState *state, int n_streams, int s_cap, int d,
+                                 int vocab, float *__restrict__ x, DevErr *err) {
+  const int s = state ? state->s : s_cap;
+  const long long r = blockIdx.x;
+  if (r >= (long long)n_streams * s) return;
+  const int b = (int)(r / s), t = (int)(r - (long long)b * s);
+  int id = ids[(long long)b * ids_ld + t];
+  const bool bad = id < 0 || id >= vocab;
+  if (bad) {
+    if (threadIdx.x == 0) {
+      err->code = DEVERR_BAD_TOKEN_ID;
+      err->detail = id;
+    }
+    id = 0;
+  }
+  const float4 *tp = reinterpret_cast<const float4 *>(tok_emb + (long long)id * d);
+  const float4 *pp = reinterpret_cast<const float4 *>(pos_emb + (long long)t * d);
+  float4 *xp = reinterpret_cast<float4 *>(x + r * d);
+  for (int c = threadIdx.x; c < (d >> 2); c += blockDim.x) {
+    const float4 a = tp[c], p = pp[c];
+    xp[c] = make_float4(a.x + p.x, a.y + p.y, a.z + p.z, a.w + p.w);
+  }
+}
+
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// OutputHead::forward (output_head.cpp:58-70) applies LN_f to every row, but
+// the token loop reads only row s-1 of each stream (inference.cpp:109-115), so
+// the final norm runs on those rows alone: out[b, :] = LN_f(x[b*s + s-1, :]).
+__global__ void gather_last_ln_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
+                                      const float *__restrict__ beta, const LoopState *state,
+                                      int n_streams, int s_cap, int d, float *__restrict__ out) {
+  const int s = state ? state->s : s_cap;
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (b >= n_streams) return;
+  const int lane = threadIdx.x & 31;
+  const float *xp = x + ((long long)b * s + (s - 1)) * d;
+  double sum = 0.0;
+  for (int c = lane; c < d; c += 32) sum += (double)xp[c];
+  const double mean = warp_sum_d(sum) / (double)d;
+  double var = 0.0;
+  for (int c = lane; c < d; c += 32) {
+    const double dd = (double)xp[c] - mean;
+    var += dd * dd;
+  }
+  var = warp_sum_d(var) / (double)d;
+  const float inv_std = 1.0f / sqrtf((float)var + 1e-5f);
+  const float fmean = (float)mean;
+  for (int c = lane; c < d; c += 32)
+    out[(long long)b * d + c] = __fadd_rn(__fmul_rn((xp[c] - fmean) * inv_std, gamma[c]), beta[c]);
+}
+
+__global__ void advance_state_kernel(LoopState *state) {
+  state->s += 1;
+  state->step += 1;
+}
+
+}  // namespace
+
+void launch_embed_pos(const float *tok_emb, const float *pos_emb, const int *ids, int ids_ld,
+                      const LoopState *state, int n_streams, int s_host, int d, int vocab,
+                      float *x, DevErr *err, cudaStream_t st) {
+  const long long rows = (long long)n_streams * s_host;
+  if (rows <= 0) return;
+  embed_pos_kernel<<<(unsigned)rows, d >= 512 ? 128 : 32, 0, st>>>(
+      tok_emb, pos_emb, ids, ids_ld, state, n_streams, s_host, d, vocab, x, err);
+  LB_LAUNCH_CHECK();
+}
+
+void launch_gather_last_ln(const float *x, const float *gamma, const float *beta,
+                           const LoopState *state, int n_streams, int s_host, int d, float *out,
+                           cudaStream_t st) {
+  const int warps = 4;
+  gather_last_ln_kernel<<<(n_streams + warps - 1) / warps, warps * 32, 0, st>>>(
+      x, gamma, beta, state, n_streams, s_host, d, out);
+  LB_LAUNCH_CHECK();
+}
+
+void launch_advance_state(LoopState *state, cudaStream_t st) {
+  advance_state_kernel<<<1, 1, 0, st>>>(state);
+  LB_LAUNCH_CHECK();
+}
+
+}  // namespace lb

@@ -1,0 +1,755 @@
+// Native token loop (litnice_b200_* entry points). Replaces the host-driven
+// loop of litnicelm's src/model/inference.cpp:265-296: per generated token the
+// whole context of every stream is recomputed (the reference keeps no KV
+// cache: forward_prompt runs Transformer::forward on all ids, :127-143,278-284),
+// the next token is chosen on the GPU and appended on the GPU. Only token ids
+// cross the host/device boundary.
+//
+// Data layout in HBM
+//   params      the parameter arena image exactly as stored in a checkpoint
+//               (named_layout.cpp:40-161); matrices are row-major [in, out].
+//   ids         [max_streams, max_seq_len] int32, one row per stream.
+//   activations dense row-major, rows r = stream*s + t of the current step:
+//               x, y, ln, ctx [R, d]; qkv [R, 3d]; h [R, d_ff].
+//   last rows   xl [>=8, d] (final LayerNorm of row s-1 of each stream),
+//               logits [>=8, vocab].
+// Work elided because nothing can observe it (the loop reads row s-1 only,
+// inference.cpp:109-115): LN_f and the output head on rows 0..s-2, the dead
+// zero-fill of the attention context, the attention-weights cache.
+#include "common.cuh"
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <string>
+#include <vector>
+
+namespace lb {
+
+namespace {
+
+struct LayerOff {
+  size_t ln1_g, ln1_b, qkv_w, qkv_b, out_w, out_b, ln2_g, ln2_b, w1, b1, w2, b2;
+};
+struct ParamLayout {
+  size_t total = 0, decay = 0, tok_emb = 0, pos_emb = 0, lnf_g = 0, lnf_b = 0, lm_head = 0;
+  std::vector<LayerOff> layer;
+};
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// named_layout.cpp:40-161: weight-decay parameters (embeddings, matrices) first
+// in declaration order, zone padded, then LayerNorm vectors and biases.
+ParamLayout build_layout(const litnice_b200_dims &d) {
+  ParamLayout L;
+  const size_t A = d.alignment_bytes, D = d.d_model, F = d.d_ff, V = d.vocab_size, S = d.max_seq_len;
+  L.layer.resize(d.n_layers);
+  size_t cur = 0;
+  auto put = [&](size_t &field, size_t bytes) {
+    cur = align_up(cur, A);
+    field = cur;
+    cur += bytes;
+  };
+  put(L.tok_emb, 4 * V * D);
+  put(L.pos_emb, 4 * S * D);
+  for (auto &o : L.layer) {
+    put(o.qkv_w, 4 * D * 3 * D);
+    put(o.out_w, 4 * D * D);
+    put(o.w1, 4 * D * F);
+    put(o.w2, 4 * F * D);
+  }
+  put(L.lm_head, 4 * D * V);
+  L.decay = align_up(cur, A);
+  cur = L.decay;
+  for (auto &o : L.layer) {
+    put(o.ln1_g, 4 * D);
+    put(o.ln1_b, 4 * D);
+    put(o.qkv_b, 4 * 3 * D);
+    put(o.out_b, 4 * D);
+    put(o.ln2_g, 4 * D);
+    put(o.ln2_b, 4 * D);
+    put(o.b1, 4 * F);
+    put(o.b2, 4 * D);
+  }
+  put(L.lnf_g, 4 * D);
+  put(L.lnf_b, 4 * D);
+  L.total = align_up(cur, A);
+  return L;
+}
+
+MatView dense(const float *p, long long rows, long long cols) {
+  MatView v{};
+  v.data = reinterpret_cast<char *>(const_cast<float *>(p));
+  v.nb = 0;
+  v.batch = 1;
+  v.rows = rows;
+  v.cols = cols;
+  v.rs = cols * 4;
+  v.cs = 4;
+  return v;
+}
+
+}  // namespace
+}  // namespace lb
+
+using namespace lb;
+
+struct litnice_b200_session {
+  litnice_b200_dims dims{};
+  int max_streams = 0;
+  int device = 0;
+  cudaStream_t st = nullptr;
+  ParamLayout lay;
+  char *params = nullptr;
+  bool params_loaded = false;
+
+  long long cap_rows = 0;
+  float *x = nullptr, *y = nullptr, *ln = nullptr, *ctx = nullptr, *qkv = nullptr, *h = nullptr;
+  float *xl = nullptr, *logits = nullptr, *gemv_scratch = nullptr;
+  float *logits_all = nullptr;
+  long long logits_all_rows = 0;
+  float *probs = nullptr;
+  int *ids = nullptr, *out_tokens = nullptr;
+  int out_cap = 0;
+  unsigned *mt = nullptr;
+  LoopState *state = nullptr;
+  void *sampler_scratch = nullptr;
+  size_t sampler_scratch_bytes_ = 0;
+  DevErr *err_host = nullptr, *err_dev = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+
+  bool keep_logits = false;
+  float *step_logits = nullptr;
+  long long step_logits_cap = 0, step_logits_count = 0;
+
+  int cur_streams = 0, cur_prompt_len = 0, cur_tokens = 0;
+  litnice_b200_stats stats{};
+  long long launches = 0;
+
+  // per-class event timing (profile_step only)
+  bool profiling = false;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> gemm_ev, attn_ev;
+  double gemm_flops = 0;
+
+  std::string error;
+};
+
+namespace {
+
+const float *P(const litnice_b200_session *s, size_t off) {
+  return reinterpret_cast<const float *>(s->params + off);
+}
+
+void free_activations(litnice_b200_session *s) {
+  for (float **p : {&s->x, &s->y, &s->ln, &s->ctx, &s->qkv, &s->h}) {
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+  }
+  s->cap_rows = 0;
+}
+
+void ensure_rows(litnice_b200_session *s, long long rows) {
+  if (rows <= s->cap_rows) return;
+  LB_CUDA(cudaStreamSynchronize(s->st));
+  free_activations(s);
+  const size_t D = s->dims.d_model, F = s->dims.d_ff;
+  auto alloc = [&](float **p, size_t floats) {
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(p), floats * sizeof(float));
+    if (e != cudaSuccess) {
+      free_activations(s);
+      throw std::bad_alloc();
+    }
+  };
+  alloc(&s->x, rows * D);
+  alloc(&s->y, rows * D);
+  alloc(&s->ln, rows * D);
+  alloc(&s->ctx, rows * D);
+  alloc(&s->qkv, rows * 3 * D);
+  alloc(&s->h, rows * F);
+  s->cap_rows = rows;
+}
+
+struct ClassTimer {
+  litnice_b200_session *s;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> *vec;
+  cudaEvent_t a = nullptr, b = nullptr;
+  ClassTimer(litnice_b200_session *s_, std::vector<std::pair<cudaEvent_t, cudaEvent_t>> *v) : s(s_), vec(v) {
+    if (s->profiling) {
+      LB_CUDA(cudaEventCreate(&a));
+      LB_CUDA(cudaEventCreate(&b));
+      LB_CUDA(cudaEventRecord(a, s->st));
+    }
+  }
+  ~ClassTimer() {
+    if (s->profiling) {
+      cudaEventRecord(b, s->st);
+      vec->emplace_back(a, b);
+    }
+  }
+};
+
+// One projection: C[rows, n] = A[rows, k] * W[k, n] + bias (+ residual) (ReLU).
+// gemm_ranked_matrix_rhs + add_bias_rowwise(+relu) + add of the reference
+// (self_attention.cpp:62-63,96-97; ffn.cpp:56-60; transformer_layer.cpp:81,86)
+// in one kernel.
+void projection(litnice_b200_session *s, const float *a, long long rows, int k, const float *w, int n,
+                const float *bias, const float *residual, int relu, float *c) {
+  ClassTimer t(s, &s->gemm_ev);
+  GemmEpilogue ep;
+  ep.bias = bias;
+  ep.residual = residual;
+  ep.relu = relu;
+  launch_gemm_simt(dense(a, rows, k), dense(w, k, n), dense(c, rows, n), rows, n, k, ep, s->st);
+  ++s->launches;
+  if (s->profiling) s->gemm_flops += 2.0 * (double)rows * n * k;
+}
+
+// Transformer::forward over all rows up to the last layer's output
+// (transformer.cpp:70-114, transformer_layer.cpp:50-92); leaves the final
+// hidden state in s->x.
+void enqueue_body(litnice_b200_session *s, int B, int sl) {
+  const litnice_b200_dims &d = s->dims;
+  const long long R = (long long)B * sl;
+  const int D = d.d_model, F = d.d_ff;
+  launch_embed_pos(P(s, s->lay.tok_emb), P(s, s->lay.pos_emb), s->ids, d.max_seq_len, nullptr, B, sl, D,
+                   d.vocab_size, s->x, s->err_dev, s->st);
+  ++s->launches;
+  for (int l = 0; l < d.n_layers; ++l) {
+    const LayerOff &o = s->lay.layer[l];
+    launch_layernorm_dense(s->x, P(s, o.ln1_g), P(s, o.ln1_b), R, D, s->ln, s->st);
+    ++s->launches;
+    projection(s, s->ln, R, D, P(s, o.qkv_w), 3 * D, P(s, o.qkv_b), nullptr, 0, s->qkv);
+    {
+      ClassTimer t(s, &s->attn_ev);
+      launch_attention(s->qkv, s->ctx, nullptr, B, sl, d.n_heads, D, s->st);
+      ++s->launches;
+    }
+    projection(s, s->ctx, R, D, P(s, o.out_w), D, P(s, o.out_b), s->x, 0, s->y);
+    launch_layernorm_dense(s->y, P(s, o.ln2_g), P(s, o.ln2_b), R, D, s->ln, s->st);
+    ++s->launches;
+    projection(s, s->ln, R, D, P(s, o.w1), F, P(s, o.b1), nullptr, 1, s->h);
+    projection(s, s->h, R, F, P(s, o.w2), D, P(s, o.b2), s->y, 0, s->x);
+  }
+}
+
+// LN_f + output head on the last row of each stream (output_head.cpp:58-70
+// restricted to the row the loop reads).
+void enqueue_head_last(litnice_b200_session *s, int B, int sl) {
+  const litnice_b200_dims &d = s->dims;
+  launch_gather_last_ln(s->x, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), nullptr, B, sl, d.d_model, s->xl, s->st);
+  ++s->launches;
+  if (B <= 8) {
+    launch_gemv(s->xl, B, P(s, s->lay.lm_head), d.d_model, d.vocab_size, nullptr, s->logits,
+                s->gemv_scratch, s->st);
+    s->launches += gemv_scratch_floats(B, d.vocab_size, d.d_model) > 0 ? 2 : 1;
+  } else {
+    projection(s, s->xl, B, d.d_model, P(s, s->lay.lm_head), d.vocab_size, nullptr, nullptr, 0, s->logits);
+  }
+}
+
+void check_device_error(litnice_b200_session *s) {
+  if (s->err_host->code == DEVERR_NONE) return;
+  const int code = s->err_host->code, detail = s->err_host->detail;
+  s->err_host->code = DEVERR_NONE;
+  if (code == DEVERR_BAD_TOKEN_ID)
+    throw std::runtime_error("embedding id out of range (id=" + std::to_string(detail) + ")");
+  throw std::runtime_error("device error code " + std::to_string(code));
+}
+
+int fail(litnice_b200_session *s, int code, const std::string &msg) {
+  if (s) s->error = msg;
+  return code;
+}
+
+template <class Fn>
+int guarded(litnice_b200_session *s, Fn fn) {
+  if (s == nullptr) return LITNICE_B200_EINVAL;
+  try {
+    LB_CUDA(cudaSetDevice(s->device));
+    return fn();
+  } catch (const std::bad_alloc &) {
+    return fail(s, LITNICE_B200_ENOMEM, "device allocation failed");
+  } catch (const CudaError &e) {
+    return fail(s, LITNICE_B200_ECUDA, e.what());
+  } catch (const std::invalid_argument &e) {
+    return fail(s, LITNICE_B200_EINVAL, e.what());
+  } catch (const std::exception &e) {
+    return fail(s, LITNICE_B200_EDEVICE, e.what());
+  }
+}
+
+void upload_ids(litnice_b200_session *s, const int32_t *ids, int B, int len) {
+  // rows of `ids` are len long on the host and max_seq_len apart on the device
+  LB_CUDA(cudaMemcpy2DAsync(s->ids, (size_t)s->dims.max_seq_len * 4, ids, (size_t)len * 4, (size_t)len * 4, B,
+                            cudaMemcpyHostToDevice, s->st));
+  s->stats.h2d_bytes += (long long)B * len * 4;
+}
+
+}  // namespace
+
+extern "C" {
+
+int litnice_b200_session_create(const litnice_b200_dims *dims, int32_t max_streams,
+                                litnice_b200_session **out) {
+  if (out == nullptr) return LITNICE_B200_EINVAL;
+  *out = nullptr;
+  if (dims == nullptr || max_streams <= 0) return LITNICE_B200_EINVAL;
+  const litnice_b200_dims &d = *dims;
+  if (d.n_layers <= 0 || d.n_heads <= 0 || d.d_model <= 0 || d.d_ff <= 0 || d.vocab_size <= 0 ||
+      d.max_seq_len <= 0 || d.alignment_bytes == 0 || (d.alignment_bytes & 15) != 0 ||
+      d.d_model % d.n_heads != 0 || d.d_model % 4 != 0 || d.d_ff % 4 != 0)
+    return LITNICE_B200_EINVAL;
+  const int dh = d.d_model / d.n_heads;
+  if (dh != 16 && dh != 32 && dh != 64 && dh != 128) return LITNICE_B200_EINVAL;
+
+  auto *s = new litnice_b200_session();
+  s->dims = d;
+  s->max_streams = max_streams;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+    delete s;
+    return LITNICE_B200_ECUDA;
+  }
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (const char *env = std::getenv("LITNICE_B200_DEVICE")) dev = std::atoi(env);
+  if (dev < 0 || dev >= count) {
+    delete s;
+    return LITNICE_B200_EINVAL;
+  }
+  s->device = dev;
+  *out = s;  // handed out even on failure below so the caller can read the error text
+  return guarded(s, [&]() {
+    cudaDeviceProp prop{};
+    LB_CUDA(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10)
+      throw std::invalid_argument("built for sm_100a (B200) only; found sm_" + std::to_string(prop.major) +
+                                  std::to_string(prop.minor));
+    s->lay = build_layout(d);
+    LB_CUDA(cudaStreamCreateWithFlags(&s->st, cudaStreamNonBlocking));
+    LB_CUDA(cudaEventCreate(&s->ev0));
+    LB_CUDA(cudaEventCreate(&s->ev1));
+    LB_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&s->err_host), sizeof(DevErr), cudaHostAllocMapped));
+    s->err_host->code = DEVERR_NONE;
+    s->err_host->detail = 0;
+    LB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&s->err_dev), s->err_host, 0));
+    auto must = [&](cudaError_t e) { if (e != cudaSuccess) throw std::bad_alloc(); };
+    must(cudaMalloc(reinterpret_cast<void **>(&s->params), s->lay.total));
+    const size_t lr = (size_t)(max_streams < 8 ? 8 : max_streams);
+    must(cudaMalloc(reinterpret_cast<void **>(&s->xl), lr * d.d_model * 4));
+    must(cudaMalloc(reinterpret_cast<void **>(&s->logits), lr * d.vocab_size * 4));
+    must(cudaMalloc(reinterpret_cast<void **>(&s->probs), lr * d.vocab_size * 4));
+    LB_CUDA(cudaMemsetAsync(s->xl, 0, lr * d.d_model * 4, s->st));
+    LB_CUDA(cudaMemsetAsync(s->logits, 0, lr * d.vocab_size * 4, s->st));
+    const size_t gs = gemv_scratch_floats(8, d.vocab_size, d.d_model);
+    if (gs) must(cudaMalloc(reinterpret_cast<void **>(&s->gemv_scratch), gs * 4));
+    must(cudaMalloc(reinterpret_cast<void **>(&s->ids), (size_t)max_streams * d.max_seq_len * 4));
+    LB_CUDA(cudaMemsetAsync(s->ids, 0, (size_t)max_streams * d.max_seq_len * 4, s->st));
+    must(cudaMalloc(reinterpret_cast<void **>(&s->mt), (size_t)max_streams * 625 * 4));
+    must(cudaMalloc(reinterpret_cast<void **>(&s->state), sizeof(LoopState)));
+    LB_CUDA(cudaStreamSynchronize(s->st));
+    return LITNICE_B200_OK;
+  });
+}
+
+void litnice_b200_session_destroy(litnice_b200_session *s) {
+  if (s == nullptr) return;
+  cudaSetDevice(s->device);
+  if (s->st) cudaStreamSynchronize(s->st);
+  free_activations(s);
+  for (void *p : {(void *)s->params, (void *)s->xl, (void *)s->logits, (void *)s->probs, (void *)s->gemv_scratch,
+                  (void *)s->logits_all, (void *)s->ids, (void *)s->out_tokens, (void *)s->mt, (void *)s->state,
+                  s->sampler_scratch, (void *)s->step_logits})
+    if (p) cudaFree(p);
+  if (s->err_host) cudaFreeHost(s->err_host);
+  if (s->ev0) cudaEventDestroy(s->ev0);
+  if (s->ev1) cudaEventDestroy(s->ev1);
+  if (s->st) cudaStreamDestroy(s->st);
+  delete s;
+}
+
+const char *litnice_b200_last_error(const litnice_b200_session *s) {
+  return s ? s->error.c_str() : "null session";
+}
+
+int litnice_b200_load_params(litnice_b200_session *s, const void *host_arena, uint64_t bytes) {
+  return guarded(s, [&]() {
+    if (host_arena == nullptr || bytes != s->lay.total)
+      throw std::invalid_argument("parameter arena must be " + std::to_string(s->lay.total) + " bytes, got " +
+                                  std::to_string(bytes));
+    LB_CUDA(cudaMemcpyAsync(s->params, host_arena, bytes, cudaMemcpyHostToDevice, s->st));
+    LB_CUDA(cudaStreamSynchronize(s->st));
+    s->params_loaded = true;
+    return LITNICE_B200_OK;
+  });
+}
+
+int litnice_b200_load_checkpoint(litnice_b200_session *s, const char *path) {
+  if (s == nullptr || path == nullptr) return LITNICE_B200_EINVAL;
+  // CkptHeaderV6 (checkpoint.cpp:98-116): 136 bytes.
+#pragma pack(push, 1)
+  struct Header {
+    uint32_t magic, version, algo_version;
+    char conf_version[32];
+    uint32_t n_layers, n_heads, d_model, d_ff, vocab_size, max_seq_len, pad;
+    uint64_t alignment_bytes, global_step;
+    uint32_t epoch, reserved;
+    uint64_t data_bytes, adam_bytes;
+    float best_loss, last_epoch_loss;
+    uint32_t best_epoch, epochs_without_improvement, flags, stop_reason;
+  };
+#pragma pack(pop)
+  static_assert(sizeof(Header) == 136, "checkpoint v6 header is 136 bytes");
+  std::ifstream in(path, std::ios::binary);
+  if (!in) return fail(s, LITNICE_B200_EIO, std::string("cannot open checkpoint ") + path);
+  Header hd{};
+  in.read(reinterpret_cast<char *>(&hd), sizeof(hd));
+  if (!in) return fail(s, LITNICE_B200_EIO, "truncated v6 header");
+  if (hd.magic != 0x4C474354u || hd.version != 6u)
+    return fail(s, LITNICE_B200_EIO, "not a version-6 litnicelm checkpoint");
+  const litnice_b200_dims &d = s->dims;
+  // the equality checks of checkpoint.cpp:609-628
+  if (hd.n_layers != (uint32_t)d.n_layers || hd.n_heads != (uint32_t)d.n_heads ||
+      hd.d_model != (uint32_t)d.d_model || hd.d_ff != (uint32_t)d.d_ff ||
+      hd.vocab_size != (uint32_t)d.vocab_size || hd.max_seq_len != (uint32_t)d.max_seq_len ||
+      hd.alignment_bytes != d.alignment_bytes || hd.data_bytes != s->lay.total ||
+      hd.adam_bytes != 2 * s->lay.total)
+    return fail(s, LITNICE_B200_EIO, "incompatible checkpoint: model dimensions or arena sizes differ");
+  std::vector<char> buf(s->lay.total);
+  in.read(buf.data(), (std::streamsize)buf.size());
+  if (in.gcount() != (std::streamsize)buf.size())
+    return fail(s, LITNICE_B200_EIO, "could not read parameter arena payload");
+  // checkpoint.cpp:176-205 rejects non-finite parameters
+  const float *f = reinterpret_cast<const float *>(buf.data());
+  for (size_t i = 0; i < buf.size() / 4; ++i)
+    if (!std::isfinite(f[i])) return fail(s, LITNICE_B200_EIO, "parameter arena holds a non-finite value");
+  return litnice_b200_load_params(s, buf.data(), buf.size());
+}
+
+int litnice_b200_upload_prompts(litnice_b200_session *s, const int32_t *prompts, int32_t n_streams,
+                                int32_t prompt_len, const uint32_t *seeds) {
+  return guarded(s, [&]() {
+    if (!s->params_loaded) throw std::invalid_argument("no parameters loaded");
+    if (prompts == nullptr || n_streams <= 0 || n_streams > s->max_streams || prompt_len <= 0 ||
+        prompt_len > s->dims.max_seq_len)
+      throw std::invalid_argument("bad prompt batch shape");
+    s->stats = litnice_b200_stats{};
+    upload_ids(s, prompts, n_streams, prompt_len);
+    unsigned *dseeds = nullptr;
+    if (seeds) {
+      // staged through the (not yet used) logits buffer
+      dseeds = reinterpret_cast<unsigned *>(s->probs);
+      LB_CUDA(cudaMemcpyAsync(dseeds, seeds, (size_t)n_streams * 4, cudaMemcpyHostToDevice, s->st));
+      s->stats.h2d_bytes += (long long)n_streams * 4;
+    }
+    launch_mt_seed(s->mt, dseeds, n_streams, s->st);
+    LoopState ls{prompt_len, 0, n_streams, s->dims.max_seq_len};
+    LB_CUDA(cudaMemcpyAsync(s->state, &ls, sizeof(ls), cudaMemcpyHostToDevice, s->st));
+    LB_CUDA(cudaStreamSynchronize(s->st));
+    s->cur_streams = n_streams;
+    s->cur_prompt_len = prompt_len;
+    s->cur_tokens = 0;
+    return LITNICE_B200_OK;
+  });
+}
+
+int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b200_sampling *sampling,
+                     int32_t *out_count) {
+  return guarded(s, [&]() {
+    if (s->cur_streams <= 0) throw std::invalid_argument("no prompts uploaded");
+    if (max_new < 0 || sampling == nullptr) throw std::invalid_argument("bad run arguments");
+    if (!(sampling->temp <= 0.0f || sampling->top_k == 1u) &&
+        !(sampling->top_p > 0.0f && sampling->top_p <= 1.0f))
+      throw std::invalid_argument("InferenceConfig.top_p must be in (0,1]");  // inference.cpp:209-211
+    const int B = s->cur_streams, V = s->dims.vocab_size;
+    const int s0 = s->cur_prompt_len + s->cur_tokens;
+    // loop guard of inference.cpp:278
+    int steps = s->dims.max_seq_len - s0;
+    if (steps > max_new) steps = max_new;
+    if (steps < 0) steps = 0;
+    ensure_rows(s, (long long)B * (s0 + (steps > 0 ? steps - 1 : 0)));
+    if (s->out_cap < s->cur_tokens + steps || s->out_tokens == nullptr) {
+      LB_CUDA(cudaStreamSynchronize(s->st));
+      int *n = nullptr;
+      const int cap = s->cur_tokens + steps > 0 ? s->cur_tokens + steps : 1;
+      if (cudaMalloc(reinterpret_cast<void **>(&n), (size_t)s->max_streams * cap * 4) != cudaSuccess)
+        throw std::bad_alloc();
+      if (s->out_tokens) {  // a resumed run keeps the tokens it already produced
+        if (s->cur_tokens > 0)
+          LB_CUDA(cudaMemcpy2D(n, (size_t)cap * 4, s->out_tokens, (size_t)s->out_cap * 4,
+                               (size_t)s->cur_tokens * 4, s->cur_streams, cudaMemcpyDeviceToDevice));
+        cudaFree(s->out_tokens);
+      }
+      s->out_tokens = n;
+      s->out_cap = cap;
+    }
+    SamplerParams sp{sampling->temp, sampling->top_k, sampling->top_p};
+    const bool greedy = sp.temp <= 0.0f || sp.top_k == 1u;
+    const int n_c = (sp.top_k > 0u && sp.top_k < (unsigned)V) ? (int)sp.top_k : V;
+    if (!greedy && V > 2048 && n_c > 2048) {
+      const size_t need = sampler_scratch_bytes(V) * (size_t)B;
+      if (need > s->sampler_scratch_bytes_) {
+        if (s->sampler_scratch) cudaFree(s->sampler_scratch);
+        s->sampler_scratch = nullptr;
+        if (cudaMalloc(&s->sampler_scratch, need) != cudaSuccess) throw std::bad_alloc();
+        s->sampler_scratch_bytes_ = need;
+      }
+    }
+    if (s->keep_logits) {
+      const long long need = (long long)(s->cur_tokens + steps) * B * V;
+      if (need > s->step_logits_cap) {
+        if (s->step_logits) cudaFree(s->step_logits);
+        s->step_logits = nullptr;
+        if (cudaMalloc(reinterpret_cast<void **>(&s->step_logits), (size_t)need * 4) != cudaSuccess)
+          throw std::bad_alloc();
+        s->step_logits_cap = need;
+      }
+      if (s->cur_tokens == 0) s->step_logits_count = 0;
+    }
+
+    const long long launches0 = s->launches;
+    LB_CUDA(cudaEventRecord(s->ev0, s->st));
+    for (int step = 0; step < steps; ++step) {
+      const int sl = s0 + step;
+      enqueue_body(s, B, sl);
+      enqueue_head_last(s, B, sl);
+      if (s->keep_logits) {
+        LB_CUDA(cudaMemcpyAsync(s->step_logits + (long long)(s->cur_tokens + step) * B * V, s->logits,
+                                (size_t)B * V * 4, cudaMemcpyDeviceToDevice, s->st));
+      }
+      launch_sampler(s->logits, V, B, sp, s->mt, s->ids, s->dims.max_seq_len, s->out_tokens, s->out_cap,
+                     s->state, s->sampler_scratch, s->st);
+      launch_advance_state(s->state, s->st);
+      s->launches += 2;
+    }
+    LB_CUDA(cudaEventRecord(s->ev1, s->st));
+    LB_CUDA(cudaStreamSynchronize(s->st));
+    check_device_error(s);
+    float ms = 0.f;
+    LB_CUDA(cudaEventElapsedTime(&ms, s->ev0, s->ev1));
+    s->stats.device_ms = ms;
+    s->stats.kernel_launches = s->launches - launches0;
+    s->stats.tokens = (long long)steps * B;
+    s->cur_tokens += steps;
+    if (s->keep_logits) s->step_logits_count = (long long)s->cur_tokens * B * V;
+    if (out_count) *out_count = s->cur_tokens;
+    return LITNICE_B200_OK;
+  });
+}
+
+int litnice_b200_download_tokens(litnice_b200_session *s, int32_t *out_tokens, int32_t max_new) {
+  return guarded(s, [&]() {
+    if (out_tokens == nullptr || max_new < s->cur_tokens) throw std::invalid_argument("output buffer too small");
+    if (s->cur_tokens > 0) {
+      LB_CUDA(cudaMemcpy2DAsync(out_tokens, (size_t)max_new * 4, s->out_tokens, (size_t)s->out_cap * 4,
+                                (size_t)s->cur_tokens * 4, s->cur_streams, cudaMemcpyDeviceToHost, s->st));
+      LB_CUDA(cudaStreamSynchronize(s->st));
+      s->stats.d2h_bytes += (long long)s->cur_streams * s->cur_tokens * 4;
+    }
+    return LITNICE_B200_OK;
+  });
+}
+
+int litnice_b200_generate(litnice_b200_session *s, const int32_t *prompts, int32_t n_streams,
+                          int32_t prompt_len, int32_t max_new, const litnice_b200_sampling *sampling,
+                          const uint32_t *seeds, int32_t *out_tokens, int32_t *out_count) {
+  int rc = litnice_b200_upload_prompts(s, prompts, n_streams, prompt_len, seeds);
+  if (rc != LITNICE_B200_OK) return rc;
+  rc = litnice_b200_run(s, max_new, sampling, out_count);
+  if (rc != LITNICE_B200_OK) return rc;
+  return litnice_b200_download_tokens(s, out_tokens, max_new);
+}
+
+int litnice_b200_keep_step_logits(litnice_b200_session *s, int32_t enable) {
+  if (s == nullptr) return LITNICE_B200_EINVAL;
+  s->keep_logits = enable != 0;
+  return LITNICE_B200_OK;
+}
+
+int litnice_b200_read_step_logits(litnice_b200_session *s, float *out, int64_t max_floats) {
+  return guarded(s, [&]() {
+    if (out == nullptr || max_floats < s->step_logits_count) throw std::invalid_argument("output buffer too small");
+    if (s->step_logits_count > 0) {
+      LB_CUDA(cudaMemcpyAsync(out, s->step_logits, (size_t)s->step_logits_count * 4, cudaMemcpyDeviceToHost, s->st));
+      LB_CUDA(cudaStreamSynchronize(s->st));
+    }
+    return LITNICE_B200_OK;
+  });
+}
+
+int litnice_b200_forward(litnice_b200_session *s, const int32_t *ids, int32_t n_streams, int32_t seq_len,
+                         int32_t all_rows, float *out_logits) {
+  return guarded(s, [&]() {
+    if (!s->params_loaded) throw std::invalid_argument("no parameters loaded");
+    if (ids == nullptr || out_logits == nullptr || n_streams <= 0 || n_streams > s->max_streams || seq_len <= 0 ||
+        seq_len > s->dims.max_seq_len)
+      throw std::invalid_argument("bad forward shape");
+    const int B = n_streams, V = s->dims.vocab_size, D = s->dims.d_model;
+    const long long R = (long long)B * seq_len;
+    s->stats = litnice_b200_stats{};
+    ensure_rows(s, R);
+    upload_ids(s, ids, B, seq_len);
+    const long long launches0 = s->launches;
+    LB_CUDA(cudaEventRecord(s->ev0, s->st));
+    enqueue_body(s, B, seq_len);
+    if (all_rows) {
+      if (s->logits_all_rows < R) {
+        LB_CUDA(cudaStreamSynchronize(s->st));
+        if (s->logits_all) cudaFree(s->logits_all);
+        s->logits_all = nullptr;
+        s->logits_all_rows = 0;
+        if (cudaMalloc(reinterpret_cast<void **>(&s->logits_all), (size_t)R * V * 4) != cudaSuccess)
+          throw std::bad_alloc();
+        s->logits_all_rows = R;
+      }
+      // OutputHead::forward over every row (output_head.cpp:58-70)
+      launch_layernorm_dense(s->x, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), R, D, s->ln, s->st);
+      ++s->launches;
+      projection(s, s->ln, R, D, P(s, s->lay.lm_head), V, nullptr, nullptr, 0, s->logits_all);
+      LB_CUDA(cudaEventRecord(s->ev1, s->st));
+      LB_CUDA(cudaMemcpyAsync(out_logits, s->logits_all, (size_t)R * V * 4, cudaMemcpyDeviceToHost, s->st));
+      s->stats.d2h_bytes += R * V * 4;
+    } else {
+      enqueue_head_last(s, B, seq_len);
+      LB_CUDA(cudaEventRecord(s->ev1, s->st));
+      LB_CUDA(cudaMemcpyAsync(out_logits, s->logits, (size_t)B * V * 4, cudaMemcpyDeviceToHost, s->st));
+      s->stats.d2h_bytes += (long long)B * V * 4;
+    }
+    LB_CUDA(cudaStreamSynchronize(s->st));
+    check_device_error(s);
+    float ms = 0.f;
+    LB_CUDA(cudaEventElapsedTime(&ms, s->ev0, s->ev1));
+    s->stats.device_ms = ms;
+    s->stats.kernel_launches = s->launches - launches0;
+    return LITNICE_B200_OK;
+  });
+}
+
+int litnice_b200_inspect(litnice_b200_session *s, const int32_t *ids, int32_t n_streams, int32_t seq_len,
+                         float *probs) {
+  return guarded(s, [&]() {
+    if (!s->params_loaded) throw std::invalid_argument("no parameters loaded");
+    if (ids == nullptr || probs == nullptr || n_streams <= 0 || n_streams > s->max_streams || seq_len <= 0 ||
+        seq_len > s->dims.max_seq_len)
+      throw std::invalid_argument("bad inspect shape");
+    const int B = n_streams, V = s->dims.vocab_size;
+    s->stats = litnice_b200_stats{};
+    ensure_rows(s, (long long)B * seq_len);
+    upload_ids(s, ids, B, seq_len);
+    const long long launches0 = s->launches;
+    LB_CUDA(cudaEventRecord(s->ev0, s->st));
+    enqueue_body(s, B, seq_len);
+    enqueue_head_last(s, B, seq_len);
+    launch_softmax_probs_f64(s->logits, V, B, s->probs, s->st);
+    ++s->launches;
+    LB_CUDA(cudaEventRecord(s->ev1, s->st));
+    LB_CUDA(cudaMemcpyAsync(probs, s->probs, (size_t)B * V * 4, cudaMemcpyDeviceToHost, s->st));
+    LB_CUDA(cudaStreamSynchronize(s->st));
+    check_device_error(s);
+    float ms = 0.f;
+    LB_CUDA(cudaEventElapsedTime(&ms, s->ev0, s->ev1));
+    s->stats.device_ms = ms;
+    s->stats.kernel_launches = s->launches - launches0;
+    s->stats.d2h_bytes += (long long)B * V * 4;
+    s->stats.tokens = 0;
+    return LITNICE_B200_OK;
+  });
+}
+
+int litnice_b200_sample_logits(litnice_b200_session *s, const float *logits, int32_t n_rows,
+                               const litnice_b200_sampling *sampling, const uint32_t *seeds, int32_t draws,
+                               int32_t *out) {
+  return guarded(s, [&]() {
+    if (logits == nullptr || sampling == nullptr || out == nullptr || n_rows <= 0 || draws <= 0)
+      throw std::invalid_argument("bad sample_logits arguments");
+    const int V = s->dims.vocab_size;
+    float *dl = nullptr;
+    unsigned *dmt = nullptr, *dseeds = nullptr;
+    int *dout = nullptr;
+    void *scr = nullptr;
+    auto cleanup = [&]() {
+      for (void *p : {(void *)dl, (void *)dmt, (void *)dseeds, (void *)dout, scr})
+        if (p) cudaFree(p);
+    };
+    try {
+      auto must = [&](cudaError_t e) { if (e != cudaSuccess) throw std::bad_alloc(); };
+      must(cudaMalloc(reinterpret_cast<void **>(&dl), (size_t)n_rows * V * 4));
+      must(cudaMalloc(reinterpret_cast<void **>(&dmt), (size_t)n_rows * 625 * 4));
+      must(cudaMalloc(reinterpret_cast<void **>(&dout), (size_t)n_rows * draws * 4));
+      if (seeds) {
+        must(cudaMalloc(reinterpret_cast<void **>(&dseeds), (size_t)n_rows * 4));
+        LB_CUDA(cudaMemcpyAsync(dseeds, seeds, (size_t)n_rows * 4, cudaMemcpyHostToDevice, s->st));
+      }
+      const size_t sb = sampler_scratch_bytes(V) * (size_t)n_rows;
+      if (sb) must(cudaMalloc(&scr, sb));
+      LB_CUDA(cudaMemcpyAsync(dl, logits, (size_t)n_rows * V * 4, cudaMemcpyHostToDevice, s->st));
+      launch_mt_seed(dmt, dseeds, n_rows, s->st);
+      SamplerParams sp{sampling->temp, sampling->top_k, sampling->top_p};
+      launch_sampler_rows(dl, V, n_rows, sp, dmt, draws, dout, scr, s->st);
+      LB_CUDA(cudaMemcpyAsync(out, dout, (size_t)n_rows * draws * 4, cudaMemcpyDeviceToHost, s->st));
+      LB_CUDA(cudaStreamSynchronize(s->st));
+    } catch (...) {
+      cudaStreamSynchronize(s->st);
+      cleanup();
+      throw;
+    }
+    cleanup();
+    return LITNICE_B200_OK;
+  });
+}
+
+int litnice_b200_get_stats(const litnice_b200_session *s, litnice_b200_stats *out) {
+  if (s == nullptr || out == nullptr) return LITNICE_B200_EINVAL;
+  *out = s->stats;
+  return LITNICE_B200_OK;
+}
+
+int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_t seq_len, int32_t repeats) {
+  return guarded(s, [&]() {
+    if (!s->params_loaded) throw std::invalid_argument("no parameters loaded");
+    if (n_streams <= 0 || n_streams > s->max_streams || seq_len <= 0 || seq_len > s->dims.max_seq_len ||
+        repeats <= 0)
+      throw std::invalid_argument("bad profile_step shape");
+    ensure_rows(s, (long long)n_streams * seq_len);
+    s->gemm_ev.clear();
+    s->attn_ev.clear();
+    s->gemm_flops = 0;
+    enqueue_body(s, n_streams, seq_len);  // warm-up, untimed
+    s->profiling = true;
+    try {
+      for (int r = 0; r < repeats; ++r) {
+        enqueue_body(s, n_streams, seq_len);
+        enqueue_head_last(s, n_streams, seq_len);
+      }
+    } catch (...) {
+      s->profiling = false;
+      throw;
+    }
+    s->profiling = false;
+    LB_CUDA(cudaStreamSynchronize(s->st));
+    s->err_host->code = DEVERR_NONE;  // ids may be stale here; this call measures time only
+    auto total = [&](std::vector<std::pair<cudaEvent_t, cudaEvent_t>> &v) {
+      double ms = 0;
+      for (auto &p : v) {
+        float t = 0.f;
+        cudaEventElapsedTime(&t, p.first, p.second);
+        ms += t;
+        cudaEventDestroy(p.first);
+        cudaEventDestroy(p.second);
+      }
+      return ms;
+    };
+    s->stats.gemm_launches = (long long)s->gemm_ev.size();
+    s->stats.attn_launches = (long long)s->attn_ev.size();
+    s->stats.gemm_ms = total(s->gemm_ev);
+    s->stats.attn_ms = total(s->attn_ev);
+    s->stats.gemm_flops = s->gemm_flops;
+    s->gemm_ev.clear();
+    s->attn_ev.clear();
+    return LITNICE_B200_OK;
+  });
+}
+
+}  // extern "C"
