@@ -142,6 +142,7 @@ const BackendApiV1 *litnice_backend_get_api(void);
 #define LITNICE_B200_ENOMEM (-3)   /* device allocation failed */
 #define LITNICE_B200_EIO (-4)      /* checkpoint file unreadable or mismatched */
 #define LITNICE_B200_EDEVICE (-5)  /* a kernel reported an error (bad token id, wait ran out) */
+#define LITNICE_B200_ETOOBIG (-6)  /* litnice_b200_gemv_noalloc: sizes beyond its built-in scratch */
 
 typedef struct litnice_b200_session litnice_b200_session;
 
@@ -241,6 +242,30 @@ int litnice_b200_get_stats(const litnice_b200_session *s, litnice_b200_stats *ou
  * fills the gemm_* / attn_* fields of the stats. Measurement aid. */
 int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_t seq_len,
                               int32_t repeats);
+
+/* No counterpart in the reference. Few-row product out[m, n] = x[m, k] * W[k, n]
+ * (+ bias[n]) for callers that cannot allocate device memory while they run:
+ * a host that has already given all device memory to its own arenas, or a
+ * loop that cannot afford the device-wide stall of an allocation. It calls no
+ * cudaMalloc / cudaFree or any other allocating routine; the split-k partial
+ * sums live in a 1.5 MiB array built into the library image (held by every GPU
+ * that loads the library until the process exits).
+ *   x [m, k], W [k, n] row-major, bias [n] or NULL, out [m, n]: device pointers
+ *   owned by the caller; m must be 1, 2, 4 or 8; stream is a cudaStream_t
+ *   (NULL = default stream). The call only enqueues work on that stream.
+ * Returns 0, LITNICE_B200_EINVAL, LITNICE_B200_ECUDA, or LITNICE_B200_ETOOBIG
+ * when m, k, n would need more than the 393216 floats of built-in scratch
+ * (a line on stderr says how much was needed). In practice only m = 8 with
+ * 16385..18816 columns and k > 128 is refused; shapes with n >= 18944 or
+ * k <= 64 need no scratch at all.
+ * The first call on each device looks up the device address of the built-in
+ * array (and loads the kernels): make that first call before any stream
+ * capture begins. All calls share the one array: it keeps the previous call's
+ * partial sums, which is harmless because each call overwrites every entry it
+ * later reads, but two calls whose kernels overlap on the GPU (different
+ * streams, or different host threads) race on it. */
+int litnice_b200_gemv_noalloc(const float *x, int32_t m, const float *w, int32_t k, int32_t n,
+                              const float *bias, float *out, void *stream);
 
 #ifdef __cplusplus
 }

@@ -13,6 +13,9 @@
 // fixed order, so results do not depend on scheduling.
 #include "common.cuh"
 
+#include <cstdio>
+#include <mutex>
+
 namespace lb {
 
 namespace {
@@ -152,4 +155,79 @@ void launch_gemv(const float *x, int m, const float *w, int k, int n, const floa
   else throw std::invalid_argument("launch_gemv: m must be <= 8");
 }
 
+// ---------------------------------------------------------------------------
+// Few-row product for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc once they are running: a
+// host that sized its own arenas from memory_info at start-up and has handed
+// every remaining byte to them (litnicelm's memory managers do exactly that),
+// or a serving loop in which an allocation would stall the whole device. For
+// them the split-k partial sums of the kernel above live in a fixed array that
+// is part of the library image instead of a buffer from cudaMalloc. Every GPU
+// that loads the library holds these 1.5 MiB until the process exits.
+// ---------------------------------------------------------------------------
+
+namespace {
+
+constexpr size_t NOALLOC_MAX_FLOATS = 384 * 1024;  // 1.5 MiB of partial sums
+static __device__ __align__(256) float g_noalloc_partials[NOALLOC_MAX_FLOATS];
+
+// In host code g_noalloc_partials is only a handle; the address kernels may
+// use is looked up once per device, with that device current.
+float *noalloc_partials_for_current_device(cudaError_t *err) {
+  static float *ptr[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess) return nullptr;
+  if (dev < 0 || dev >= 64) {
+    *err = cudaErrorInvalidDevice;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptr[dev] == nullptr) {
+    void *p = nullptr;
+    *err = cudaGetSymbolAddress(&p, g_noalloc_partials);
+    if (*err != cudaSuccess) return nullptr;
+    ptr[dev] = static_cast<float *>(p);
+  }
+  return ptr[dev];
+}
+
+}  // namespace
 }  // namespace lb
+
+extern "C" int litnice_b200_gemv_noalloc(const float *x, int32_t m, const float *w, int32_t k, int32_t n,
+                                         const float *bias, float *out, void *stream) {
+  using namespace lb;
+  if (x == nullptr || w == nullptr || out == nullptr || k <= 0 || n <= 0) {
+    std::fprintf(stderr, "litnice_b200_gemv_noalloc: null pointer or non-positive size\n");
+    return LITNICE_B200_EINVAL;
+  }
+  if (m != 1 && m != 2 && m != 4 && m != 8) {
+    std::fprintf(stderr, "litnice_b200_gemv_noalloc: m must be 1, 2, 4 or 8 (got %d)\n", m);
+    return LITNICE_B200_EINVAL;
+  }
+  const size_t need = gemv_scratch_floats(m, n, k);
+  if (need > NOALLOC_MAX_FLOATS) {
+    std::fprintf(stderr,
+                 "litnice_b200_gemv_noalloc: m=%d k=%d n=%d needs %zu floats of partial sums, the built-in "
+                 "array holds %zu\n", m, k, n, need, (size_t)NOALLOC_MAX_FLOATS);
+    return LITNICE_B200_ETOOBIG;
+  }
+  cudaError_t e = cudaSuccess;
+  float *partials = noalloc_partials_for_current_device(&e);
+  if (partials == nullptr) {
+    std::fprintf(stderr, "litnice_b200_gemv_noalloc: scratch set-up failed: %s\n", cudaGetErrorString(e));
+    return LITNICE_B200_ECUDA;
+  }
+  try {
+    // Every partial sum the reduction reads is written by the first kernel of
+    // the same call, so nothing left over from an earlier call is ever used.
+    launch_gemv(x, m, w, k, n, bias, out, partials, static_cast<cudaStream_t>(stream));
+  } catch (const std::exception &ex) {
+    std::fprintf(stderr, "litnice_b200_gemv_noalloc: %s\n", ex.what());
+    return LITNICE_B200_ECUDA;
+  }
+  return LITNICE_B200_OK;
+}
