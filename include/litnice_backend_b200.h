@@ -243,6 +243,16 @@ int litnice_b200_get_stats(const litnice_b200_session *s, litnice_b200_stats *ou
 int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_t seq_len,
                               int32_t repeats);
 
+/* One projection on host buffers: c[m,n] = a[m,k] * w[k,n] (+ bias[n]) (+ residual[m,n])
+ * (ReLU when relu != 0), i.e. gemm_ranked_matrix_rhs followed by add_bias_rowwise
+ * / add_bias_relu_rowwise / add (device_backend.cpp:1112-1131, 840-908, 752-813).
+ * engine 0: fp32 SIMT kernel; engine 1: tcgen05 tensor-core kernel with the
+ * three-product TF32 split (needs k % 32 == 0 and n % 64 == 0). Allocates and
+ * frees its own device buffers; meant for checking the two engines against
+ * each other and against the CPU. */
+int litnice_b200_projection_host(int32_t engine, const float *a, int32_t m, int32_t k, const float *w, int32_t n,
+                                 const float *bias, const float *residual, int32_t relu, float *c);
+
 /* No counterpart in the reference. Few-row product out[m, n] = x[m, k] * W[k, n]
  * (+ bias[n]) for callers that cannot allocate device memory while they run:
  * a host that has already given all device memory to its own arenas, or a

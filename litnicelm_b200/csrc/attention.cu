@@ -12,6 +12,7 @@
 // dense [n_streams*s, d]. One CTA of 256 threads handles 64 query rows of one
 // (stream, head) and walks the key tiles up to the diagonal.
 #include "common.cuh"
+#include "gemm_tc.cuh"
 
 namespace lb {
 
@@ -23,8 +24,8 @@ constexpr int AT_PLD = 68;   // row pitch of the probability tile (floats)
 
 template <int DH>
 __global__ void __launch_bounds__(256)
-attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, const LoopState *state,
-                 int s_cap, int d_model, float scale) {
+attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, float *__restrict__ ctx_lo,
+                 const LoopState *state, int s_cap, int d_model, float scale) {
   constexpr int CPT = DH / 16;  // output columns per thread
   extern __shared__ __align__(16) float smem[];
   float (*Qt)[AT_BQ] = reinterpret_cast<float (*)[AT_BQ]>(smem);                 // [DH][64]
@@ -161,14 +162,24 @@ attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, const L
     const int qi = q0 + ty * 4 + i;
     if (qi >= s) continue;
     const float inv = 1.0f / l_run[i];
-    float *op = ctx + ((long long)b * s + qi) * d_model + h * DH + tx * CPT;
+    const long long off = ((long long)b * s + qi) * d_model + h * DH + tx * CPT;
 #pragma unroll
-    for (int c = 0; c < CPT; ++c) op[c] = o[i][c] * inv;
+    for (int c = 0; c < CPT; ++c) {
+      const float v = o[i][c] * inv;
+      if (ctx_lo == nullptr) {
+        ctx[off + c] = v;
+      } else {
+        float hh, ll;
+        split_tf32(v, hh, ll);
+        ctx[off + c] = hh;
+        ctx_lo[off + c] = ll;
+      }
+    }
   }
 }
 
 template <int DH>
-void launch_dh(const float *qkv, float *ctx, const LoopState *state, int n_streams, int s_cap,
+void launch_dh(const float *qkv, float *ctx, float *ctx_lo, const LoopState *state, int n_streams, int s_cap,
                int n_heads, int d_model, cudaStream_t st) {
   const size_t smem = (size_t)(3 * DH * AT_BQ + AT_BQ * AT_PLD) * sizeof(float);
   static bool configured[64] = {};  // the attribute is per device
@@ -181,20 +192,20 @@ void launch_dh(const float *qkv, float *ctx, const LoopState *state, int n_strea
   }
   dim3 grid((s_cap + AT_BQ - 1) / AT_BQ, n_heads, n_streams);
   const float scale = 1.0f / sqrtf((float)DH);
-  attention_kernel<DH><<<grid, 256, smem, st>>>(qkv, ctx, state, s_cap, d_model, scale);
+  attention_kernel<DH><<<grid, 256, smem, st>>>(qkv, ctx, ctx_lo, state, s_cap, d_model, scale);
   LB_LAUNCH_CHECK();
 }
 
 }  // namespace
 
-void launch_attention(const float *qkv, float *ctx, const LoopState *state, int n_streams,
+void launch_attention(const float *qkv, float *ctx, float *ctx_lo, const LoopState *state, int n_streams,
                       int s_host, int n_heads, int d_model, cudaStream_t st) {
   const int dh = d_model / n_heads;
   switch (dh) {
-    case 16: launch_dh<16>(qkv, ctx, state, n_streams, s_host, n_heads, d_model, st); break;
-    case 32: launch_dh<32>(qkv, ctx, state, n_streams, s_host, n_heads, d_model, st); break;
-    case 64: launch_dh<64>(qkv, ctx, state, n_streams, s_host, n_heads, d_model, st); break;
-    case 128: launch_dh<128>(qkv, ctx, state, n_streams, s_host, n_heads, d_model, st); break;
+    case 16: launch_dh<16>(qkv, ctx, ctx_lo, state, n_streams, s_host, n_heads, d_model, st); break;
+    case 32: launch_dh<32>(qkv, ctx, ctx_lo, state, n_streams, s_host, n_heads, d_model, st); break;
+    case 64: launch_dh<64>(qkv, ctx, ctx_lo, state, n_streams, s_host, n_heads, d_model, st); break;
+    case 128: launch_dh<128>(qkv, ctx, ctx_lo, state, n_streams, s_host, n_heads, d_model, st); break;
     default:
       throw std::invalid_argument("litnice_b200: fused attention supports head_dim 16, 32, 64, 128");
   }

@@ -141,9 +141,10 @@ void launch_embed_pos(const float *tok_emb, const float *pos_emb, const int *ids
                       float *x, DevErr *err, cudaStream_t st);
 void launch_gather_last_ln(const float *x, const float *gamma, const float *beta,
                            const LoopState *state, int n_streams, int s_host, int d, float *out,
-                           cudaStream_t st);
+                           float *out_lo, cudaStream_t st);
+// out_lo != nullptr: out receives the TF32 high part and out_lo the low part.
 void launch_layernorm_dense(const float *x, const float *gamma, const float *beta, long long rows,
-                            int d, float *out, cudaStream_t st);
+                            int d, float *out, float *out_lo, cudaStream_t st);
 
 // gemv.cu: out[m, n] = x[m, :] . W[:, n] for m <= 8 rows; W row-major [k, n].
 // scratch must hold gemv_scratch_floats(m, n, k) floats when the launcher
@@ -153,7 +154,8 @@ void launch_gemv(const float *x, int m, const float *w, int k, int n, const floa
                  float *out, float *scratch, cudaStream_t st);
 
 // attention.cu: ctx[r, h*dh + :] for rows r = b*s + t of qkv [rows, 3*d].
-void launch_attention(const float *qkv, float *ctx, const LoopState *state, int n_streams,
+// ctx_lo != nullptr: ctx receives the TF32 high part and ctx_lo the low part.
+void launch_attention(const float *qkv, float *ctx, float *ctx_lo, const LoopState *state, int n_streams,
                       int s_host, int n_heads, int d_model, cudaStream_t st);
 
 // sampler.cu

@@ -4,6 +4,7 @@
 // [n_streams * s, d] matrix; s is read from the device-resident LoopState so a
 // launch sized for an upper bound `s_cap` serves every shorter context.
 #include "common.cuh"
+#include "gemm_tc.cuh"
 
 namespace lb {
 
@@ -48,7 +49,8 @@ __device__ __forceinline__ double warp_sum_d(double v) {
 // the final norm runs on those rows alone: out[b, :] = LN_f(x[b*s + s-1, :]).
 __global__ void gather_last_ln_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
                                       const float *__restrict__ beta, const LoopState *state,
-                                      int n_streams, int s_cap, int d, float *__restrict__ out) {
+                                      int n_streams, int s_cap, int d, float *__restrict__ out,
+                                      float *__restrict__ out_lo) {
   const int s = state ? state->s : s_cap;
   const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (b >= n_streams) return;
@@ -65,8 +67,17 @@ __global__ void gather_last_ln_kernel(const float *__restrict__ x, const float *
   var = warp_sum_d(var) / (double)d;
   const float inv_std = 1.0f / sqrtf((float)var + 1e-5f);
   const float fmean = (float)mean;
-  for (int c = lane; c < d; c += 32)
-    out[(long long)b * d + c] = __fadd_rn(__fmul_rn((xp[c] - fmean) * inv_std, gamma[c]), beta[c]);
+  for (int c = lane; c < d; c += 32) {
+    const float v = __fadd_rn(__fmul_rn((xp[c] - fmean) * inv_std, gamma[c]), beta[c]);
+    if (out_lo == nullptr) {
+      out[(long long)b * d + c] = v;
+    } else {
+      float h, l;
+      split_tf32(v, h, l);
+      out[(long long)b * d + c] = h;
+      out_lo[(long long)b * d + c] = l;
+    }
+  }
 }
 
 __global__ void advance_state_kernel(LoopState *state) {
@@ -88,10 +99,10 @@ void launch_embed_pos(const float *tok_emb, const float *pos_emb, const int *ids
 
 void launch_gather_last_ln(const float *x, const float *gamma, const float *beta,
                            const LoopState *state, int n_streams, int s_host, int d, float *out,
-                           cudaStream_t st) {
+                           float *out_lo, cudaStream_t st) {
   const int warps = 4;
   gather_last_ln_kernel<<<(n_streams + warps - 1) / warps, warps * 32, 0, st>>>(
-      x, gamma, beta, state, n_streams, s_host, d, out);
+      x, gamma, beta, state, n_streams, s_host, d, out, out_lo);
   LB_LAUNCH_CHECK();
 }
 

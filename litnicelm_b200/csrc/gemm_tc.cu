@@ -1,0 +1,453 @@
+// Tensor-core projection GEMM for sm_100a (tcgen05 + TMEM + TMA), fp32 accuracy
+// by the three-product TF32 split. Replaces, on the hot path, the sequence
+// gemm_ranked_matrix_rhs + add_bias_rowwise (+ReLU) + add of the reference
+// (litnicelm src/model/backend/device_backend.cpp:1112-1131, 840-940, 752-813).
+//
+// One CTA computes a 128 x BN tile of C. Warp roles:
+//   warp 0      one lane issues the TMA loads of the four operand tiles
+//               (A_hi, A_lo, B_hi, B_lo; 128-byte swizzle) into a ring of stages
+//   warp 1      allocates tensor memory; one lane issues the tcgen05.mma
+//               instructions (3 products x 4 k-steps per stage) and commits
+//   warps 2..5  epilogue: tcgen05.ld of each finished accumulation chunk (one
+//               TMEM lane quarter each) added into fp32 registers, then bias /
+//               residual / ReLU and the stores (optionally as a hi/lo split for
+//               the next GEMM)
+// Every wait on an mbarrier is bounded (about one second); a wait that runs out
+// sets the error word, lets the pipeline drain and the kernel returns after
+// freeing its tensor memory. No cluster launch and no multicast is used.
+#include "gemm_tc.cuh"
+
+#include <cstdlib>
+#include <mutex>
+
+namespace lb {
+
+namespace {
+
+constexpr int TC_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
+
+// ---- PTX helpers ---------------------------------------------------------------
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) {
+  return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ unsigned mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait: false (and the error word set) if the phase does not complete
+// within WAIT_LIMIT_NS or another role has already given up.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, DevErr *err,
+                                          int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer();
+  unsigned spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        err->code = DEVERR_WAIT_TIMEOUT;
+        err->detail = where;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *map, int x, int y, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
+                                            unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
+// (32 fp32) stored with the 128-byte swizzle: groups of 8 rows are 1024 bytes
+// apart (stride byte offset), the leading byte offset is unused for this layout,
+// descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ unsigned long long umma_desc_k128(unsigned smem_addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+  d |= 1ull << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+// Instruction descriptor: D fp32, A and B TF32, both K-major, M = 128, N = bn.
+__host__ __device__ constexpr unsigned umma_idesc_tf32(int bn) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
+}
+
+template <int BN, int STAGES>
+struct TcSmem {
+  static constexpr int A_BYTES = TC_BM * TC_BK * 4;  // 16 KiB
+  static constexpr int B_BYTES = BN * TC_BK * 4;
+  static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  static constexpr int TILES_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFFSET = TILES_BYTES;          // full[S], empty[S], tmem_full
+  static constexpr int TOTAL = TILES_BYTES + 256 + 1024;  // + barriers/holders + alignment slack
+};
+
+// Tensor-core accumulation rounds toward zero: every tcgen05.mma that adds into
+// a non-zero accumulator loses up to one ulp of it, always in the same
+// direction (measured: ~3e-5 relative at k = 2048 with one long chain). So the
+// k loop is cut into chunks of TC_CHUNK k-blocks: each chunk is accumulated in
+// one of two TMEM buffers starting from zero, and the epilogue warps add the
+// finished chunk into fp32 registers (round to nearest) while the next chunk is
+// multiplied into the other buffer. Inside a k-block the two small products
+// (a_lo*b_hi, a_hi*b_lo) are issued first, while the accumulator is still
+// ~2^-11 of its final size, so only the a_hi*b_hi steps truncate at full scale.
+#ifndef LB_TC_CHUNK
+#define LB_TC_CHUNK 1
+#endif
+constexpr int TC_CHUNK = LB_TC_CHUNK;  // k-blocks (of 32) per TMEM accumulation chain
+
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+               const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+               TcEpilogue ep, int m, int n, int k, DevErr *err) {
+  using L = TcSmem<BN, STAGES>;
+  extern __shared__ unsigned char smem_raw[];
+  const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
+  unsigned char *base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const unsigned bar_base = base + L::BAR_OFFSET;
+  // barriers: full[S], empty[S], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  constexpr int HOLDER_OFFSET = L::BAR_OFFSET + 8 * (2 * STAGES + 4);
+  volatile unsigned *tmem_holder = reinterpret_cast<volatile unsigned *>(base_ptr + HOLDER_OFFSET);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + HOLDER_OFFSET + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * TC_BM;
+  const int kblocks = k / TC_BK;
+  const int nchunks = (kblocks + TC_CHUNK - 1) / TC_CHUNK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tmem_full_bar(b), 1);
+      mbar_init(tmem_empty_bar(b), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {  // whole warp: allocate two accumulators of BN columns each
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_holder)),
+                 "r"((unsigned)(2 * BN))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_holder;
+
+  if (warp == 0 && lane == 0) {
+    // ---- TMA producer ----
+    int issued = 0;
+    for (int kb = 0; kb < kblocks; ++kb) {
+      const int s = kb % STAGES;
+      const unsigned ph = (unsigned)(kb / STAGES) & 1u;
+      if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, err, 1)) break;
+      const unsigned stage = base + (unsigned)s * L::STAGE_BYTES;
+      mbar_expect_tx(full_bar(s), (unsigned)L::STAGE_BYTES);
+      tma_load_2d(stage, &map_a_hi, kb * TC_BK, m0, full_bar(s));
+      tma_load_2d(stage + L::A_BYTES, &map_a_lo, kb * TC_BK, m0, full_bar(s));
+      tma_load_2d(stage + 2 * L::A_BYTES, &map_b_hi, kb * TC_BK, n0, full_bar(s));
+      tma_load_2d(stage + 2 * L::A_BYTES + L::B_BYTES, &map_b_lo, kb * TC_BK, n0, full_bar(s));
+      ++issued;
+    }
+    if (*abort_flag) {
+      // let copies already in flight land before the CTA's shared memory goes away
+      const int first = issued > STAGES ? issued - STAGES : 0;
+      for (int j = first; j < issued; ++j) {
+        const unsigned long long t0 = global_timer();
+        while (!mbar_try_wait(full_bar(j % STAGES), (unsigned)(j / STAGES) & 1u))
+          if (global_timer() - t0 > WAIT_LIMIT_NS) break;
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer ----
+    const unsigned idesc = umma_idesc_tf32(BN);
+    bool ok = true;
+    int committed = -1;  // last chunk whose completion was committed to a tmem_full barrier
+    for (int c = 0; c < nchunks && ok; ++c) {
+      const int buf = c & 1;
+      const unsigned tmem_d = tmem_base + (unsigned)(buf * BN);
+      // the epilogue must have drained this buffer's previous chunk
+      ok = mbar_wait(tmem_empty_bar(buf), ((unsigned)(c >> 1) & 1u) ^ 1u, abort_flag, err, 4);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int kb_end = min(kblocks, (c + 1) * TC_CHUNK);
+      for (int kb = c * TC_CHUNK; kb < kb_end && ok; ++kb) {
+        const int s = kb % STAGES;
+        const unsigned ph = (unsigned)(kb / STAGES) & 1u;
+        ok = mbar_wait(full_bar(s), ph, abort_flag, err, 2);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned stage = base + (unsigned)s * L::STAGE_BYTES;
+        const unsigned long long a_hi = umma_desc_k128(stage);
+        const unsigned long long a_lo = umma_desc_k128(stage + L::A_BYTES);
+        const unsigned long long b_hi = umma_desc_k128(stage + 2 * L::A_BYTES);
+        const unsigned long long b_lo = umma_desc_k128(stage + 2 * L::A_BYTES + L::B_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < TC_BK / 8; ++ks) {
+          const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);  // 8 fp32 = 32 bytes along k
+          const unsigned first = (kb == c * TC_CHUNK && ks == 0) ? 0u : 1u;   // a chunk starts from zero
+          tc_mma_tf32(tmem_d, a_lo + adv, b_hi + adv, idesc, first);
+          tc_mma_tf32(tmem_d, a_hi + adv, b_lo + adv, idesc, 1u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < TC_BK / 8; ++ks) {
+          const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);
+          tc_mma_tf32(tmem_d, a_hi + adv, b_hi + adv, idesc, 1u);
+        }
+        tc_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+      }
+      if (ok) {
+        tc_commit(tmem_full_bar(buf));  // arrives when every MMA of this chunk has completed
+        committed = c;
+      }
+    }
+    if (!ok) {  // give the tensor pipe a bounded chance to finish before TMEM is freed
+      const int buf = (committed + 1) & 1;
+      tc_commit(tmem_full_bar(buf));
+      const unsigned long long t0 = global_timer();
+      while (!mbar_try_wait(tmem_full_bar(buf), (unsigned)((committed + 1) >> 1) & 1u))
+        if (global_timer() - t0 > WAIT_LIMIT_NS) break;
+    }
+  } else if (warp >= 2) {
+    // ---- epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 ----
+    const int q = warp & 3;
+    const int row = m0 + q * 32 + lane;
+    float acc[BN];
+#pragma unroll
+    for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+    bool ok = true;
+    for (int c = 0; c < nchunks && ok; ++c) {
+      const int buf = c & 1;
+      ok = mbar_wait(tmem_full_bar(buf), (unsigned)(c >> 1) & 1u, abort_flag, err, 3);
+      __syncwarp();
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        unsigned r[32];
+        tc_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN + c0), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[c0 + j] = __fadd_rn(acc[c0 + j], __uint_as_float(r[j]));
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
+    }
+    if (ok && !*abort_flag && row < m) {
+      const long long off = (long long)row * n + n0;
+#pragma unroll
+      for (int j = 0; j < BN; j += 4) {
+        float v[4] = {acc[j], acc[j + 1], acc[j + 2], acc[j + 3]};
+        if (ep.bias) {
+          const float4 b = *reinterpret_cast<const float4 *>(ep.bias + n0 + j);
+          v[0] += b.x; v[1] += b.y; v[2] += b.z; v[3] += b.w;
+        }
+        if (ep.residual) {
+          const float4 rr = *reinterpret_cast<const float4 *>(ep.residual + off + j);
+          v[0] += rr.x; v[1] += rr.y; v[2] += rr.z; v[3] += rr.w;
+        }
+        if (ep.relu) {
+#pragma unroll
+          for (int t = 0; t < 4; ++t) v[t] = v[t] > 0.f ? v[t] : 0.f;
+        }
+        if (ep.c) *reinterpret_cast<float4 *>(ep.c + off + j) = make_float4(v[0], v[1], v[2], v[3]);
+        if (ep.c_hi) {
+          float h[4], l[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) split_tf32(v[t], h[t], l[t]);
+          *reinterpret_cast<float4 *>(ep.c_hi + off + j) = make_float4(h[0], h[1], h[2], h[3]);
+          *reinterpret_cast<float4 *>(ep.c_lo + off + j) = make_float4(l[0], l[1], l[2], l[3]);
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)(2 * BN)) : "memory");
+  }
+}
+
+// ---- operand preparation ---------------------------------------------------------
+
+__global__ void split_tf32_kernel(const float *__restrict__ x, float *__restrict__ hi, float *__restrict__ lo,
+                                  long long count) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
+       i += (long long)gridDim.x * blockDim.x) {
+    float h, l;
+    split_tf32(x[i], h, l);
+    hi[i] = h;
+    lo[i] = l;
+  }
+}
+
+// W [k, n] row-major -> wt_hi, wt_lo [n, k] (K-major), 32 x 32 tiles through shared memory.
+__global__ void transpose_split_kernel(const float *__restrict__ w, int k, int n, float *__restrict__ wt_hi,
+                                       float *__restrict__ wt_lo) {
+  __shared__ float tile[32][33];
+  const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int kk = k0 + r, nn = n0 + threadIdx.x;
+    tile[r][threadIdx.x] = (kk < k && nn < n) ? w[(long long)kk * n + nn] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int nn = n0 + r, kk = k0 + threadIdx.x;
+    if (nn < n && kk < k) {
+      float h, l;
+      split_tf32(tile[threadIdx.x][r], h, l);
+      wt_hi[(long long)nn * k + kk] = h;
+      wt_lo[(long long)nn * k + kk] = l;
+    }
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      (void)cudaGetLastError();
+  });
+  return fn;
+}
+
+template <int BN, int STAGES>
+void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const TcEpilogue &ep, DevErr *err,
+                cudaStream_t st) {
+  using L = TcSmem<BN, STAGES>;
+  static bool configured[64] = {};
+  int dev = 0;
+  LB_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    LB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    configured[dev] = true;
+  }
+  dim3 grid(n / BN, (m + TC_BM - 1) / TC_BM);
+  gemm_tc_kernel<BN, STAGES><<<grid, TC_THREADS, L::TOTAL, st>>>(a.hi, a.lo, b.hi, b.lo, ep, m, n, k, err);
+  LB_LAUNCH_CHECK();
+}
+
+}  // namespace
+
+bool tc_runtime_available() { return encode_tiled_fn() != nullptr; }
+
+void tc_make_map(CUtensorMap *map, const float *base, unsigned long long rows, unsigned long long k,
+                 unsigned box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) throw std::runtime_error("litnice_b200: cuTensorMapEncodeTiled is not available");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (k * 4) % 16 != 0 || box_rows == 0 || box_rows > 256)
+    throw std::invalid_argument("litnice_b200: tensor map operand must be 16-byte aligned with k % 4 == 0");
+  const cuuint64_t dims[2] = {k, rows};
+  const cuuint64_t strides[1] = {k * 4};  // bytes between rows
+  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw std::runtime_error("litnice_b200: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+}
+
+void launch_gemm_tc(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, int bn, const TcEpilogue &ep,
+                    DevErr *err, cudaStream_t st) {
+  if (m <= 0) return;
+  if (k < TC_BK || k % TC_BK != 0 || (bn != 64 && bn != 128) || n % bn != 0)
+    throw std::invalid_argument("litnice_b200: tensor-core GEMM needs k % 32 == 0 and n % bn == 0");
+  if (bn == 128) launch_cfg<128, 3>(a, b, m, n, k, ep, err, st);
+  else launch_cfg<64, 4>(a, b, m, n, k, ep, err, st);
+}
+
+void launch_split_tf32(const float *x, float *hi, float *lo, long long count, cudaStream_t st) {
+  if (count <= 0) return;
+  const long long blocks = (count + 255) / 256;
+  split_tf32_kernel<<<(unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, st>>>(x, hi, lo, count);
+  LB_LAUNCH_CHECK();
+}
+
+void launch_transpose_split(const float *w, int k, int n, float *wt_hi, float *wt_lo, cudaStream_t st) {
+  dim3 grid((n + 31) / 32, (k + 31) / 32), block(32, 8);
+  transpose_split_kernel<<<grid, block, 0, st>>>(w, k, n, wt_hi, wt_lo);
+  LB_LAUNCH_CHECK();
+}
+
+}  // namespace lb

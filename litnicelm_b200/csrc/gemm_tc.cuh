@@ -1,0 +1,61 @@
+// Tensor-core projection GEMM for sm_100a: interface.
+//
+// C[M,N] = A[M,K] * W[K,N] (+ bias, + residual, ReLU) with fp32 accuracy on the
+// 5th-generation tensor cores by the three-product TF32 split
+//     a*b ~= a_hi*b_hi + a_lo*b_hi + a_hi*b_lo,   x_hi = tf32(x), x_lo = tf32(x - x_hi)
+// accumulated in fp32 in tensor memory. Operands are stored already split:
+// activations as two dense [rows, K] arrays written by the producing kernel,
+// weights as two K-major [N, K] arrays built once when parameters are loaded.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace lb {
+
+constexpr int TC_BM = 128;  // rows per CTA (one UMMA M=128 tile)
+constexpr int TC_BK = 32;   // fp32 elements per k-block = one 128-byte swizzle row
+
+struct TcMatrix {  // one split operand: two tensor maps over K-major fp32 arrays
+  CUtensorMap hi, lo;
+};
+
+struct TcEpilogue {
+  const float *bias = nullptr;      // [N]
+  const float *residual = nullptr;  // [M, N] dense, added after the bias
+  int relu = 0;
+  float *c = nullptr;               // [M, N] dense fp32 result (may be null)
+  float *c_hi = nullptr;            // optional split result for a following GEMM
+  float *c_lo = nullptr;
+};
+
+// True when the driver exposes cuTensorMapEncodeTiled (resolved at run time so
+// that the library loads on machines without a GPU driver).
+bool tc_runtime_available();
+
+// Tensor map over a dense row-major fp32 array [rows, k] with boxes of
+// box_rows x 32 elements and the 128-byte swizzle the UMMA descriptors expect.
+void tc_make_map(CUtensorMap *map, const float *base, unsigned long long rows, unsigned long long k,
+                 unsigned box_rows);
+
+// bn is 64 or 128; requires n % bn == 0, k % 32 == 0; a maps must use box rows
+// 128, b maps box rows bn.
+void launch_gemm_tc(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, int bn,
+                    const TcEpilogue &ep, DevErr *err, cudaStream_t st);
+
+// x -> (hi, lo) elementwise.
+void launch_split_tf32(const float *x, float *hi, float *lo, long long count, cudaStream_t st);
+// Row-major W [k, n] -> K-major split copies wt_hi, wt_lo [n, k].
+void launch_transpose_split(const float *w, int k, int n, float *wt_hi, float *wt_lo, cudaStream_t st);
+
+__device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
+  unsigned h, l;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+  hi = __uint_as_float(h);
+  const float rest = x - hi;  // exact: x and hi agree in their leading 11 bits
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
+  lo = __uint_as_float(l);
+}
+
+}  // namespace lb

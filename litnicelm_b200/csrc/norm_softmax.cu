@@ -4,6 +4,7 @@
 // in float (:1247-1279); softmax takes an fp32 maximum, exp in fp32, the sum in
 // double and scales by float(1/sum) (:1466-1494, causal form :1554-1592).
 #include "common.cuh"
+#include "gemm_tc.cuh"
 
 namespace lb {
 
@@ -47,7 +48,7 @@ __global__ void layernorm_kernel(RowView x, const char *gamma, long long gcs, co
 // Dense rows of d floats (d % 4 == 0), one warp per row, float4 traffic.
 __global__ void layernorm_dense_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
                                        const float *__restrict__ beta, long long rows, int d,
-                                       float *__restrict__ out) {
+                                       float *__restrict__ out, float *__restrict__ out_lo) {
   const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -78,7 +79,17 @@ __global__ void layernorm_dense_kernel(const float *__restrict__ x, const float 
     r.y = __fadd_rn(__fmul_rn((v.y - fmean) * inv_std, g.y), b.y);
     r.z = __fadd_rn(__fmul_rn((v.z - fmean) * inv_std, g.z), b.z);
     r.w = __fadd_rn(__fmul_rn((v.w - fmean) * inv_std, g.w), b.w);
-    op[c] = r;
+    if (out_lo == nullptr) {
+      op[c] = r;
+    } else {  // TF32 hi/lo split for the tensor-core projection that follows
+      float4 h, l;
+      split_tf32(r.x, h.x, l.x);
+      split_tf32(r.y, h.y, l.y);
+      split_tf32(r.z, h.z, l.z);
+      split_tf32(r.w, h.w, l.w);
+      op[c] = h;
+      reinterpret_cast<float4 *>(out_lo + row * d)[c] = l;
+    }
   }
 }
 
@@ -144,11 +155,11 @@ void launch_layernorm(const RowView &x, const float *gamma, long long gamma_cs, 
 }
 
 void launch_layernorm_dense(const float *x, const float *gamma, const float *beta, long long rows,
-                            int d, float *out, cudaStream_t st) {
+                            int d, float *out, float *out_lo, cudaStream_t st) {
   if (rows <= 0) return;
   const int warps = 4;
   const long long blocks = (rows + warps - 1) / warps;
-  layernorm_dense_kernel<<<(unsigned)blocks, warps * 32, 0, st>>>(x, gamma, beta, rows, d, out);
+  layernorm_dense_kernel<<<(unsigned)blocks, warps * 32, 0, st>>>(x, gamma, beta, rows, d, out, out_lo);
   LB_LAUNCH_CHECK();
 }
 

@@ -17,7 +17,9 @@
 // inference.cpp:109-115): LN_f and the output head on rows 0..s-2, the dead
 // zero-fill of the attention context, the attention-weights cache.
 #include "common.cuh"
+#include "gemm_tc.cuh"
 
+#include <array>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -91,6 +93,18 @@ MatView dense(const float *p, long long rows, long long cols) {
   return v;
 }
 
+// One weight matrix prepared for the tensor-core GEMM: K-major hi/lo copies
+// [n, k] and tensor maps for both tile widths.
+struct TcWeight {
+  float *hi = nullptr, *lo = nullptr;
+  int k = 0, n = 0;
+  bool has64 = false, has128 = false;
+  TcMatrix m64{}, m128{};
+  bool usable() const { return has64 || has128; }
+};
+
+enum AKind { A_LN = 0, A_CTX = 1, A_H = 2, A_XL = 3 };
+
 }  // namespace
 }  // namespace lb
 
@@ -108,6 +122,13 @@ struct litnice_b200_session {
   long long cap_rows = 0;
   float *x = nullptr, *y = nullptr, *ln = nullptr, *ctx = nullptr, *qkv = nullptr, *h = nullptr;
   float *xl = nullptr, *logits = nullptr, *gemv_scratch = nullptr;
+  // tensor-core path: low parts of the split activations (ln/ctx/h/xl hold the high parts)
+  bool tc = false;
+  float *ln_lo = nullptr, *ctx_lo = nullptr, *h_lo = nullptr, *xl_lo = nullptr;
+  long long xl_rows = 0;
+  std::vector<std::array<TcWeight, 4>> tcw;  // per layer: qkv, out, w1, w2
+  TcWeight tc_head;
+  TcMatrix a_map[4]{};
   float *logits_all = nullptr;
   long long logits_all_rows = 0;
   float *probs = nullptr;
@@ -143,14 +164,20 @@ const float *P(const litnice_b200_session *s, size_t off) {
 }
 
 void free_activations(litnice_b200_session *s) {
-  for (float **p : {&s->x, &s->y, &s->ln, &s->ctx, &s->qkv, &s->h}) {
+  for (float **p : {&s->x, &s->y, &s->ln, &s->ctx, &s->qkv, &s->h, &s->ln_lo, &s->ctx_lo, &s->h_lo}) {
     if (*p) cudaFree(*p);
     *p = nullptr;
   }
   s->cap_rows = 0;
 }
 
+void make_activation_map(TcMatrix *m, const float *hi, const float *lo, long long rows, int k) {
+  tc_make_map(&m->hi, hi, (unsigned long long)rows, (unsigned long long)k, TC_BM);
+  tc_make_map(&m->lo, lo, (unsigned long long)rows, (unsigned long long)k, TC_BM);
+}
+
 void ensure_rows(litnice_b200_session *s, long long rows) {
+  if (s->tc) rows = (rows + TC_BM - 1) / TC_BM * TC_BM;  // whole TMA boxes
   if (rows <= s->cap_rows) return;
   LB_CUDA(cudaStreamSynchronize(s->st));
   free_activations(s);
@@ -168,7 +195,20 @@ void ensure_rows(litnice_b200_session *s, long long rows) {
   alloc(&s->ctx, rows * D);
   alloc(&s->qkv, rows * 3 * D);
   alloc(&s->h, rows * F);
+  if (s->tc) {
+    alloc(&s->ln_lo, rows * D);
+    alloc(&s->ctx_lo, rows * D);
+    alloc(&s->h_lo, rows * F);
+    make_activation_map(&s->a_map[A_LN], s->ln, s->ln_lo, rows, (int)D);
+    make_activation_map(&s->a_map[A_CTX], s->ctx, s->ctx_lo, rows, (int)D);
+    make_activation_map(&s->a_map[A_H], s->h, s->h_lo, rows, (int)F);
+  }
   s->cap_rows = rows;
+}
+
+int pick_bn(const TcWeight &w, long long m) {
+  if (w.has128 && (!w.has64 || ((m + TC_BM - 1) / TC_BM) * (w.n / 128) >= 120)) return 128;
+  return 64;
 }
 
 struct ClassTimer {
@@ -193,17 +233,35 @@ struct ClassTimer {
 // One projection: C[rows, n] = A[rows, k] * W[k, n] + bias (+ residual) (ReLU).
 // gemm_ranked_matrix_rhs + add_bias_rowwise(+relu) + add of the reference
 // (self_attention.cpp:62-63,96-97; ffn.cpp:56-60; transformer_layer.cpp:81,86)
-// in one kernel.
-void projection(litnice_b200_session *s, const float *a, long long rows, int k, const float *w, int n,
-                const float *bias, const float *residual, int relu, float *c) {
+// in one kernel: on the tensor cores when the weight was prepared for them,
+// else the fp32 SIMT kernel. split_out: store the result as a TF32 hi/lo pair
+// (c, c_lo) for a tensor-core projection that follows.
+void projection(litnice_b200_session *s, AKind ak, long long rows, int k, const float *w, const TcWeight *tw,
+                int n, const float *bias, const float *residual, int relu, float *c, float *c_lo) {
   ClassTimer t(s, &s->gemm_ev);
+  if (s->profiling) s->gemm_flops += 2.0 * (double)rows * n * k;
+  ++s->launches;
+  if (s->tc && tw != nullptr && tw->usable()) {
+    TcEpilogue ep;
+    ep.bias = bias;
+    ep.residual = residual;
+    ep.relu = relu;
+    if (c_lo) {
+      ep.c_hi = c;
+      ep.c_lo = c_lo;
+    } else {
+      ep.c = c;
+    }
+    const int bn = pick_bn(*tw, rows);
+    launch_gemm_tc(s->a_map[ak], bn == 128 ? tw->m128 : tw->m64, (int)rows, n, k, bn, ep, s->err_dev, s->st);
+    return;
+  }
+  const float *a = ak == A_LN ? s->ln : ak == A_CTX ? s->ctx : ak == A_H ? s->h : s->xl;
   GemmEpilogue ep;
   ep.bias = bias;
   ep.residual = residual;
   ep.relu = relu;
   launch_gemm_simt(dense(a, rows, k), dense(w, k, n), dense(c, rows, n), rows, n, k, ep, s->st);
-  ++s->launches;
-  if (s->profiling) s->gemm_flops += 2.0 * (double)rows * n * k;
 }
 
 // Transformer::forward over all rows up to the last layer's output
@@ -218,19 +276,22 @@ void enqueue_body(litnice_b200_session *s, int B, int sl) {
   ++s->launches;
   for (int l = 0; l < d.n_layers; ++l) {
     const LayerOff &o = s->lay.layer[l];
-    launch_layernorm_dense(s->x, P(s, o.ln1_g), P(s, o.ln1_b), R, D, s->ln, s->st);
+    const std::array<TcWeight, 4> *tw = s->tc ? &s->tcw[l] : nullptr;
+    launch_layernorm_dense(s->x, P(s, o.ln1_g), P(s, o.ln1_b), R, D, s->ln, s->tc ? s->ln_lo : nullptr, s->st);
     ++s->launches;
-    projection(s, s->ln, R, D, P(s, o.qkv_w), 3 * D, P(s, o.qkv_b), nullptr, 0, s->qkv);
+    projection(s, A_LN, R, D, P(s, o.qkv_w), tw ? &(*tw)[0] : nullptr, 3 * D, P(s, o.qkv_b), nullptr, 0, s->qkv,
+               nullptr);
     {
       ClassTimer t(s, &s->attn_ev);
-      launch_attention(s->qkv, s->ctx, nullptr, B, sl, d.n_heads, D, s->st);
+      launch_attention(s->qkv, s->ctx, s->tc ? s->ctx_lo : nullptr, nullptr, B, sl, d.n_heads, D, s->st);
       ++s->launches;
     }
-    projection(s, s->ctx, R, D, P(s, o.out_w), D, P(s, o.out_b), s->x, 0, s->y);
-    launch_layernorm_dense(s->y, P(s, o.ln2_g), P(s, o.ln2_b), R, D, s->ln, s->st);
+    projection(s, A_CTX, R, D, P(s, o.out_w), tw ? &(*tw)[1] : nullptr, D, P(s, o.out_b), s->x, 0, s->y, nullptr);
+    launch_layernorm_dense(s->y, P(s, o.ln2_g), P(s, o.ln2_b), R, D, s->ln, s->tc ? s->ln_lo : nullptr, s->st);
     ++s->launches;
-    projection(s, s->ln, R, D, P(s, o.w1), F, P(s, o.b1), nullptr, 1, s->h);
-    projection(s, s->h, R, F, P(s, o.w2), D, P(s, o.b2), s->y, 0, s->x);
+    projection(s, A_LN, R, D, P(s, o.w1), tw ? &(*tw)[2] : nullptr, F, P(s, o.b1), nullptr, 1, s->h,
+               s->tc ? s->h_lo : nullptr);
+    projection(s, A_H, R, F, P(s, o.w2), tw ? &(*tw)[3] : nullptr, D, P(s, o.b2), s->y, 0, s->x, nullptr);
   }
 }
 
@@ -238,15 +299,56 @@ void enqueue_body(litnice_b200_session *s, int B, int sl) {
 // restricted to the row the loop reads).
 void enqueue_head_last(litnice_b200_session *s, int B, int sl) {
   const litnice_b200_dims &d = s->dims;
-  launch_gather_last_ln(s->x, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), nullptr, B, sl, d.d_model, s->xl, s->st);
+  const bool head_tc = s->tc && B > 8 && s->tc_head.usable();
+  launch_gather_last_ln(s->x, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), nullptr, B, sl, d.d_model, s->xl,
+                        head_tc ? s->xl_lo : nullptr, s->st);
   ++s->launches;
   if (B <= 8) {
     launch_gemv(s->xl, B, P(s, s->lay.lm_head), d.d_model, d.vocab_size, nullptr, s->logits,
                 s->gemv_scratch, s->st);
     s->launches += gemv_scratch_floats(B, d.vocab_size, d.d_model) > 0 ? 2 : 1;
   } else {
-    projection(s, s->xl, B, d.d_model, P(s, s->lay.lm_head), d.vocab_size, nullptr, nullptr, 0, s->logits);
+    projection(s, A_XL, B, d.d_model, P(s, s->lay.lm_head), head_tc ? &s->tc_head : nullptr, d.vocab_size,
+               nullptr, nullptr, 0, s->logits, nullptr);
   }
+}
+
+// Weights are immutable during inference: build, once per load, the K-major
+// TF32 hi/lo copies [n, k] the tensor-core GEMM reads, and their tensor maps.
+void prepare_one(litnice_b200_session *s, TcWeight *tw, const float *w, int k, int n) {
+  tw->k = k;
+  tw->n = n;
+  tw->has64 = (k % TC_BK == 0) && (n % 64 == 0);
+  tw->has128 = (k % TC_BK == 0) && (n % 128 == 0);
+  if (!tw->usable()) return;
+  const size_t bytes = (size_t)k * n * 4;
+  if (tw->hi == nullptr) {
+    if (cudaMalloc(reinterpret_cast<void **>(&tw->hi), bytes) != cudaSuccess) throw std::bad_alloc();
+    if (cudaMalloc(reinterpret_cast<void **>(&tw->lo), bytes) != cudaSuccess) throw std::bad_alloc();
+  }
+  launch_transpose_split(w, k, n, tw->hi, tw->lo, s->st);
+  if (tw->has64) {
+    tc_make_map(&tw->m64.hi, tw->hi, (unsigned long long)n, (unsigned long long)k, 64);
+    tc_make_map(&tw->m64.lo, tw->lo, (unsigned long long)n, (unsigned long long)k, 64);
+  }
+  if (tw->has128) {
+    tc_make_map(&tw->m128.hi, tw->hi, (unsigned long long)n, (unsigned long long)k, 128);
+    tc_make_map(&tw->m128.lo, tw->lo, (unsigned long long)n, (unsigned long long)k, 128);
+  }
+}
+
+void prepare_tc_weights(litnice_b200_session *s) {
+  const litnice_b200_dims &d = s->dims;
+  const int D = d.d_model, F = d.d_ff;
+  s->tcw.resize(d.n_layers);
+  for (int l = 0; l < d.n_layers; ++l) {
+    const LayerOff &o = s->lay.layer[l];
+    prepare_one(s, &s->tcw[l][0], P(s, o.qkv_w), D, 3 * D);
+    prepare_one(s, &s->tcw[l][1], P(s, o.out_w), D, D);
+    prepare_one(s, &s->tcw[l][2], P(s, o.w1), D, F);
+    prepare_one(s, &s->tcw[l][3], P(s, o.w2), F, D);
+  }
+  prepare_one(s, &s->tc_head, P(s, s->lay.lm_head), D, d.vocab_size);
 }
 
 void check_device_error(litnice_b200_session *s) {
@@ -255,6 +357,9 @@ void check_device_error(litnice_b200_session *s) {
   s->err_host->code = DEVERR_NONE;
   if (code == DEVERR_BAD_TOKEN_ID)
     throw std::runtime_error("embedding id out of range (id=" + std::to_string(detail) + ")");
+  if (code == DEVERR_WAIT_TIMEOUT)
+    throw std::runtime_error("a bounded wait inside the tensor-core GEMM ran out (role " + std::to_string(detail) +
+                             ")");
   throw std::runtime_error("device error code " + std::to_string(code));
 }
 
@@ -337,8 +442,19 @@ int litnice_b200_session_create(const litnice_b200_dims *dims, int32_t max_strea
     LB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&s->err_dev), s->err_host, 0));
     auto must = [&](cudaError_t e) { if (e != cudaSuccess) throw std::bad_alloc(); };
     must(cudaMalloc(reinterpret_cast<void **>(&s->params), s->lay.total));
-    const size_t lr = (size_t)(max_streams < 8 ? 8 : max_streams);
+    // Tensor-core projections need k % 32 == 0 and n % 64 == 0 for all four
+    // layer matrices; LITNICE_B200_TC=0 forces the fp32 SIMT kernels.
+    const char *tc_env = std::getenv("LITNICE_B200_TC");
+    s->tc = !(tc_env && tc_env[0] == '0') && tc_runtime_available() && d.d_model % 64 == 0 && d.d_ff % 64 == 0;
+    size_t lr = (size_t)(max_streams < 8 ? 8 : max_streams);
+    if (s->tc) lr = (lr + TC_BM - 1) / TC_BM * TC_BM;
+    s->xl_rows = (long long)lr;
     must(cudaMalloc(reinterpret_cast<void **>(&s->xl), lr * d.d_model * 4));
+    if (s->tc) {
+      must(cudaMalloc(reinterpret_cast<void **>(&s->xl_lo), lr * d.d_model * 4));
+      LB_CUDA(cudaMemsetAsync(s->xl_lo, 0, lr * d.d_model * 4, s->st));
+      make_activation_map(&s->a_map[A_XL], s->xl, s->xl_lo, (long long)lr, d.d_model);
+    }
     must(cudaMalloc(reinterpret_cast<void **>(&s->logits), lr * d.vocab_size * 4));
     must(cudaMalloc(reinterpret_cast<void **>(&s->probs), lr * d.vocab_size * 4));
     LB_CUDA(cudaMemsetAsync(s->xl, 0, lr * d.d_model * 4, s->st));
@@ -363,6 +479,14 @@ void litnice_b200_session_destroy(litnice_b200_session *s) {
                   (void *)s->logits_all, (void *)s->ids, (void *)s->out_tokens, (void *)s->mt, (void *)s->state,
                   s->sampler_scratch, (void *)s->step_logits})
     if (p) cudaFree(p);
+  if (s->xl_lo) cudaFree(s->xl_lo);
+  for (auto &layer : s->tcw)
+    for (auto &w : layer) {
+      if (w.hi) cudaFree(w.hi);
+      if (w.lo) cudaFree(w.lo);
+    }
+  if (s->tc_head.hi) cudaFree(s->tc_head.hi);
+  if (s->tc_head.lo) cudaFree(s->tc_head.lo);
   if (s->err_host) cudaFreeHost(s->err_host);
   if (s->ev0) cudaEventDestroy(s->ev0);
   if (s->ev1) cudaEventDestroy(s->ev1);
@@ -380,6 +504,7 @@ int litnice_b200_load_params(litnice_b200_session *s, const void *host_arena, ui
       throw std::invalid_argument("parameter arena must be " + std::to_string(s->lay.total) + " bytes, got " +
                                   std::to_string(bytes));
     LB_CUDA(cudaMemcpyAsync(s->params, host_arena, bytes, cudaMemcpyHostToDevice, s->st));
+    if (s->tc) prepare_tc_weights(s);
     LB_CUDA(cudaStreamSynchronize(s->st));
     s->params_loaded = true;
     return LITNICE_B200_OK;
@@ -605,9 +730,12 @@ int litnice_b200_forward(litnice_b200_session *s, const int32_t *ids, int32_t n_
         s->logits_all_rows = R;
       }
       // OutputHead::forward over every row (output_head.cpp:58-70)
-      launch_layernorm_dense(s->x, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), R, D, s->ln, s->st);
+      const bool head_tc = s->tc && s->tc_head.usable();
+      launch_layernorm_dense(s->x, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), R, D, s->ln,
+                             head_tc ? s->ln_lo : nullptr, s->st);
       ++s->launches;
-      projection(s, s->ln, R, D, P(s, s->lay.lm_head), V, nullptr, nullptr, 0, s->logits_all);
+      projection(s, A_LN, R, D, P(s, s->lay.lm_head), head_tc ? &s->tc_head : nullptr, V, nullptr, nullptr, 0,
+                 s->logits_all, nullptr);
       LB_CUDA(cudaEventRecord(s->ev1, s->st));
       LB_CUDA(cudaMemcpyAsync(out_logits, s->logits_all, (size_t)R * V * 4, cudaMemcpyDeviceToHost, s->st));
       s->stats.d2h_bytes += R * V * 4;
@@ -729,7 +857,8 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
     }
     s->profiling = false;
     LB_CUDA(cudaStreamSynchronize(s->st));
-    s->err_host->code = DEVERR_NONE;  // ids may be stale here; this call measures time only
+    if (s->err_host->code == DEVERR_BAD_TOKEN_ID) s->err_host->code = DEVERR_NONE;  // stale ids: timing only
+    check_device_error(s);
     auto total = [&](std::vector<std::pair<cudaEvent_t, cudaEvent_t>> &v) {
       double ms = 0;
       for (auto &p : v) {
@@ -750,6 +879,87 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
     s->attn_ev.clear();
     return LITNICE_B200_OK;
   });
+}
+
+int litnice_b200_projection_host(int32_t engine, const float *a, int32_t m, int32_t k, const float *w, int32_t n,
+                                 const float *bias, const float *residual, int32_t relu, float *c) {
+  if (a == nullptr || w == nullptr || c == nullptr || m <= 0 || k <= 0 || n <= 0 || (engine != 0 && engine != 1)) {
+    std::fprintf(stderr, "litnice_b200_projection_host: bad argument\n");
+    return LITNICE_B200_EINVAL;
+  }
+  if (engine == 1 && (k % TC_BK != 0 || n % 64 != 0 || !tc_runtime_available())) {
+    std::fprintf(stderr, "litnice_b200_projection_host: the tensor-core engine needs k %% 32 == 0 and n %% 64 == 0\n");
+    return LITNICE_B200_EINVAL;
+  }
+  std::vector<void *> owned;
+  DevErr *err_host = nullptr;
+  cudaStream_t st = nullptr;
+  int rc = LITNICE_B200_OK;
+  try {
+    auto dev_alloc = [&](size_t bytes) {
+      void *p = nullptr;
+      if (cudaMalloc(&p, bytes) != cudaSuccess) throw std::bad_alloc();
+      owned.push_back(p);
+      return static_cast<float *>(p);
+    };
+    LB_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    LB_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&err_host), sizeof(DevErr), cudaHostAllocMapped));
+    err_host->code = DEVERR_NONE;
+    err_host->detail = 0;
+    DevErr *err_dev = nullptr;
+    LB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&err_dev), err_host, 0));
+    const long long mp = ((long long)m + TC_BM - 1) / TC_BM * TC_BM;
+    float *da = dev_alloc((size_t)mp * k * 4), *dw = dev_alloc((size_t)k * n * 4), *dc = dev_alloc((size_t)m * n * 4);
+    float *db = bias ? dev_alloc((size_t)n * 4) : nullptr, *dr = residual ? dev_alloc((size_t)m * n * 4) : nullptr;
+    LB_CUDA(cudaMemsetAsync(da, 0, (size_t)mp * k * 4, st));
+    LB_CUDA(cudaMemcpyAsync(da, a, (size_t)m * k * 4, cudaMemcpyHostToDevice, st));
+    LB_CUDA(cudaMemcpyAsync(dw, w, (size_t)k * n * 4, cudaMemcpyHostToDevice, st));
+    if (db) LB_CUDA(cudaMemcpyAsync(db, bias, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+    if (dr) LB_CUDA(cudaMemcpyAsync(dr, residual, (size_t)m * n * 4, cudaMemcpyHostToDevice, st));
+    if (engine == 0) {
+      GemmEpilogue ep;
+      ep.bias = db;
+      ep.residual = dr;
+      ep.relu = relu;
+      launch_gemm_simt(dense(da, m, k), dense(dw, k, n), dense(dc, m, n), m, n, k, ep, st);
+    } else {
+      float *a_hi = dev_alloc((size_t)mp * k * 4), *a_lo = dev_alloc((size_t)mp * k * 4);
+      float *w_hi = dev_alloc((size_t)k * n * 4), *w_lo = dev_alloc((size_t)k * n * 4);
+      launch_split_tf32(da, a_hi, a_lo, mp * k, st);
+      launch_transpose_split(dw, k, n, w_hi, w_lo, st);
+      const int bn = (n % 128 == 0 && (mp / TC_BM) * (n / 128) >= 120) ? 128 : 64;
+      TcMatrix ma{}, mb{};
+      tc_make_map(&ma.hi, a_hi, (unsigned long long)mp, (unsigned long long)k, TC_BM);
+      tc_make_map(&ma.lo, a_lo, (unsigned long long)mp, (unsigned long long)k, TC_BM);
+      tc_make_map(&mb.hi, w_hi, (unsigned long long)n, (unsigned long long)k, (unsigned)bn);
+      tc_make_map(&mb.lo, w_lo, (unsigned long long)n, (unsigned long long)k, (unsigned)bn);
+      TcEpilogue ep;
+      ep.bias = db;
+      ep.residual = dr;
+      ep.relu = relu;
+      ep.c = dc;
+      launch_gemm_tc(ma, mb, m, n, k, bn, ep, err_dev, st);
+    }
+    LB_CUDA(cudaMemcpyAsync(c, dc, (size_t)m * n * 4, cudaMemcpyDeviceToHost, st));
+    LB_CUDA(cudaStreamSynchronize(st));
+    if (err_host->code != DEVERR_NONE) {
+      std::fprintf(stderr, "litnice_b200_projection_host: device error %d (detail %d)\n", err_host->code,
+                   err_host->detail);
+      rc = LITNICE_B200_EDEVICE;
+    }
+  } catch (const std::bad_alloc &) {
+    rc = LITNICE_B200_ENOMEM;
+  } catch (const std::exception &e) {
+    std::fprintf(stderr, "litnice_b200_projection_host: %s\n", e.what());
+    rc = LITNICE_B200_ECUDA;
+  }
+  if (st) {
+    cudaStreamSynchronize(st);
+    cudaStreamDestroy(st);
+  }
+  for (void *p : owned) cudaFree(p);
+  if (err_host) cudaFreeHost(err_host);
+  return rc;
 }
 
 }  // extern "C"
