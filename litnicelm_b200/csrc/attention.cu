@@ -10,7 +10,14 @@
 // Layout: qkv is the dense [n_streams*s, 3*d] output of the QKV projection
 // (columns [0,d) Q, [d,2d) K, [2d,3d) V; head h owns columns h*dh..), ctx is
 // dense [n_streams*s, d]. One CTA of 256 threads handles 64 query rows of one
-// (stream, head) and walks the key tiles up to the diagonal.
+// (stream, head).
+//
+// Causal work is triangular: query tile t needs key tiles 0..t. When streams x
+// heads x tiles alone cannot fill the GPU (one short stream), a query tile's
+// key range is cut into chunks of `kc` tiles handled by separate CTAs. Each CTA
+// leaves its unnormalised partial output with its running maximum and sum in
+// scratch; the CTA that finishes last for a query tile (atomic counter) merges
+// the partials in chunk order, so the result does not depend on scheduling.
 #include "common.cuh"
 #include "gemm_tc.cuh"
 
@@ -21,22 +28,35 @@ namespace {
 constexpr int AT_BQ = 64;    // query rows per CTA
 constexpr int AT_BK = 64;    // keys per tile
 constexpr int AT_PLD = 68;   // row pitch of the probability tile (floats)
+constexpr float AT_NEG = -3.402823466e+38f;
+
+__host__ __device__ inline int chunks_of(int qt, int kc) { return (qt + kc) / kc; }  // ceil((qt+1)/kc)
 
 template <int DH>
 __global__ void __launch_bounds__(256)
-attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, float *__restrict__ ctx_lo,
-                 const LoopState *state, int s_cap, int d_model, float scale) {
+attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, float *__restrict__ ctx_lo, int s,
+                 int d_model, float scale, int kc, float *__restrict__ part, int *__restrict__ counters) {
   constexpr int CPT = DH / 16;  // output columns per thread
+  constexpr int PART = AT_BQ * (DH + 2);  // floats of one partial: o[64][DH], m[64], l[64]
   extern __shared__ __align__(16) float smem[];
   float (*Qt)[AT_BQ] = reinterpret_cast<float (*)[AT_BQ]>(smem);                 // [DH][64]
   float (*Kt)[AT_BK] = reinterpret_cast<float (*)[AT_BK]>(smem + DH * AT_BQ);    // [DH][64]
   float (*Vs)[DH] = reinterpret_cast<float (*)[DH]>(smem + 2 * DH * AT_BQ);      // [64][DH]
   float (*Ps)[AT_PLD] = reinterpret_cast<float (*)[AT_PLD]>(smem + 3 * DH * AT_BQ);  // [64][68]
+  __shared__ int s_last;
 
-  const int s = state ? state->s : s_cap;
-  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // blockIdx.x enumerates (query tile, chunk) pairs, longest query tiles first.
+  const int tiles = (s + AT_BQ - 1) / AT_BQ;
+  int idx = blockIdx.x, qt = tiles - 1;
+  for (; qt > 0; --qt) {
+    const int nc = chunks_of(qt, kc);
+    if (idx < nc) break;
+    idx -= nc;
+  }
+  const int chunk = idx, nchunks = chunks_of(qt, kc);
+  const int kt_begin = chunk * kc, kt_end = min(qt + 1, kt_begin + kc);
+  const int h = blockIdx.y, b = blockIdx.z;
   const int q0 = qt * AT_BQ;
-  if (q0 >= s) return;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const long long ld = 3LL * d_model;
   const float *base = qkv + (long long)b * s * ld + (long long)h * DH;
@@ -56,13 +76,13 @@ attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, float *
   float m_run[4], l_run[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    m_run[i] = -3.402823466e+38f;
+    m_run[i] = AT_NEG;
     l_run[i] = 0.f;
 #pragma unroll
     for (int c = 0; c < CPT; ++c) o[i][c] = 0.f;
   }
 
-  for (int kt = 0; kt <= qt; ++kt) {
+  for (int kt = kt_begin; kt < kt_end; ++kt) {
     const int k0 = kt * AT_BK;
     __syncthreads();  // previous tile fully consumed (and Qt written, first time)
     for (int f = tid; f < AT_BK * DH / 4; f += 256) {
@@ -106,7 +126,7 @@ attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, float *
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int qi = q0 + ty * 4 + i;
-      float mx = -3.402823466e+38f;
+      float mx = AT_NEG;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int kj = k0 + tx * 4 + j;
@@ -157,6 +177,52 @@ attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, float *
     }
   }
 
+  if (nchunks > 1) {
+    // Leave this chunk's partial in scratch; the last CTA of the query tile merges.
+    const long long bh = (long long)b * gridDim.y + h;
+    const long long first_item = bh * gridDim.x + (blockIdx.x - chunk);
+    float *mine = part + (first_item + chunk) * PART;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = ty * 4 + i;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) mine[r * DH + tx * CPT + c] = o[i][c];
+      if (tx == 0) {
+        mine[AT_BQ * DH + r] = m_run[i];
+        mine[AT_BQ * DH + AT_BQ + r] = l_run[i];
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    int *counter = counters + bh * tiles + qt;
+    if (tid == 0) {
+      const int prev = atomicAdd(counter, 1);
+      s_last = (prev == nchunks - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (tid == 0) *counter = 0;  // ready for the next launch
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = ty * 4 + i;
+      float mm = AT_NEG;
+      for (int j = 0; j < nchunks; ++j)
+        mm = fmaxf(mm, __ldcg(part + (first_item + j) * PART + AT_BQ * DH + r));
+      float ll = 0.f;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) o[i][c] = 0.f;
+      for (int j = 0; j < nchunks; ++j) {
+        const float *pj = part + (first_item + j) * PART;
+        const float w = expf(__ldcg(pj + AT_BQ * DH + r) - mm);
+        ll += __ldcg(pj + AT_BQ * DH + AT_BQ + r) * w;
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) o[i][c] = fmaf(__ldcg(pj + r * DH + tx * CPT + c), w, o[i][c]);
+      }
+      l_run[i] = ll;
+    }
+  }
+
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int qi = q0 + ty * 4 + i;
@@ -179,8 +245,8 @@ attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, float *
 }
 
 template <int DH>
-void launch_dh(const float *qkv, float *ctx, float *ctx_lo, const LoopState *state, int n_streams, int s_cap,
-               int n_heads, int d_model, cudaStream_t st) {
+void launch_dh(const float *qkv, float *ctx, float *ctx_lo, int n_streams, int s, int n_heads, int d_model,
+               const AttentionPlan &plan, float *scratch, int *counters, cudaStream_t st) {
   const size_t smem = (size_t)(3 * DH * AT_BQ + AT_BQ * AT_PLD) * sizeof(float);
   static bool configured[64] = {};  // the attribute is per device
   int dev = 0;
@@ -190,22 +256,51 @@ void launch_dh(const float *qkv, float *ctx, float *ctx_lo, const LoopState *sta
                                  (int)smem));
     configured[dev] = true;
   }
-  dim3 grid((s_cap + AT_BQ - 1) / AT_BQ, n_heads, n_streams);
+  dim3 grid(plan.ctas_per_head, n_heads, n_streams);
   const float scale = 1.0f / sqrtf((float)DH);
-  attention_kernel<DH><<<grid, 256, smem, st>>>(qkv, ctx, ctx_lo, state, s_cap, d_model, scale);
+  attention_kernel<DH><<<grid, 256, smem, st>>>(qkv, ctx, ctx_lo, s, d_model, scale, plan.kc, scratch, counters);
   LB_LAUNCH_CHECK();
 }
 
 }  // namespace
 
-void launch_attention(const float *qkv, float *ctx, float *ctx_lo, const LoopState *state, int n_streams,
-                      int s_host, int n_heads, int d_model, cudaStream_t st) {
+AttentionPlan attention_plan(int n_streams, int s, int n_heads, int dh) {
+  AttentionPlan p{};
+  const int tiles = (s + AT_BQ - 1) / AT_BQ;
+  const long long bh = (long long)n_streams * n_heads;
+  const long long units = bh * tiles * (tiles + 1) / 2;  // (query tile, key tile) pairs
+  // No split when the unsplit grid already gives every SM two CTAs; otherwise
+  // aim at about two CTAs per SM of equal length.
+  int kc = tiles;
+  if (bh * tiles < 2 * 148) {
+    long long per_cta = (units + 2 * 148 - 1) / (2 * 148);
+    if (per_cta < 1) per_cta = 1;
+    if (per_cta < tiles) kc = (int)per_cta;
+  }
+  p.kc = kc;
+  int ctas = 0;
+  bool split = false;
+  for (int qt = 0; qt < tiles; ++qt) {
+    ctas += chunks_of(qt, kc);
+    split = split || chunks_of(qt, kc) > 1;
+  }
+  p.ctas_per_head = ctas;
+  p.scratch_floats = split ? (size_t)bh * ctas * AT_BQ * (dh + 2) : 0;
+  p.counters = split ? (size_t)bh * tiles : 0;
+  return p;
+}
+
+void launch_attention(const float *qkv, float *ctx, float *ctx_lo, int n_streams, int s, int n_heads, int d_model,
+                      float *scratch, int *counters, cudaStream_t st) {
   const int dh = d_model / n_heads;
+  const AttentionPlan plan = attention_plan(n_streams, s, n_heads, dh);
+  if (plan.scratch_floats > 0 && (scratch == nullptr || counters == nullptr))
+    throw std::invalid_argument("litnice_b200: attention needs scratch for this shape");
   switch (dh) {
-    case 16: launch_dh<16>(qkv, ctx, ctx_lo, state, n_streams, s_host, n_heads, d_model, st); break;
-    case 32: launch_dh<32>(qkv, ctx, ctx_lo, state, n_streams, s_host, n_heads, d_model, st); break;
-    case 64: launch_dh<64>(qkv, ctx, ctx_lo, state, n_streams, s_host, n_heads, d_model, st); break;
-    case 128: launch_dh<128>(qkv, ctx, ctx_lo, state, n_streams, s_host, n_heads, d_model, st); break;
+    case 16: launch_dh<16>(qkv, ctx, ctx_lo, n_streams, s, n_heads, d_model, plan, scratch, counters, st); break;
+    case 32: launch_dh<32>(qkv, ctx, ctx_lo, n_streams, s, n_heads, d_model, plan, scratch, counters, st); break;
+    case 64: launch_dh<64>(qkv, ctx, ctx_lo, n_streams, s, n_heads, d_model, plan, scratch, counters, st); break;
+    case 128: launch_dh<128>(qkv, ctx, ctx_lo, n_streams, s, n_heads, d_model, plan, scratch, counters, st); break;
     default:
       throw std::invalid_argument("litnice_b200: fused attention supports head_dim 16, 32, 64, 128");
   }

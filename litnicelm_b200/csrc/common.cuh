@@ -155,8 +155,17 @@ void launch_gemv(const float *x, int m, const float *w, int k, int n, const floa
 
 // attention.cu: ctx[r, h*dh + :] for rows r = b*s + t of qkv [rows, 3*d].
 // ctx_lo != nullptr: ctx receives the TF32 high part and ctx_lo the low part.
-void launch_attention(const float *qkv, float *ctx, float *ctx_lo, const LoopState *state, int n_streams,
-                      int s_host, int n_heads, int d_model, cudaStream_t st);
+// attention_plan says how the triangular work is cut for a shape and how much
+// scratch (floats of partial outputs, zero-initialised int counters) it needs.
+struct AttentionPlan {
+  int kc;              // key tiles per CTA
+  int ctas_per_head;   // grid.x
+  size_t scratch_floats;
+  size_t counters;
+};
+AttentionPlan attention_plan(int n_streams, int s, int n_heads, int dh);
+void launch_attention(const float *qkv, float *ctx, float *ctx_lo, int n_streams, int s, int n_heads, int d_model,
+                      float *scratch, int *counters, cudaStream_t st);
 
 // sampler.cu
 struct SamplerParams {

@@ -129,6 +129,9 @@ struct litnice_b200_session {
   std::vector<std::array<TcWeight, 4>> tcw;  // per layer: qkv, out, w1, w2
   TcWeight tc_head;
   TcMatrix a_map[4]{};
+  float *attn_scratch = nullptr;
+  int *attn_counters = nullptr;
+  size_t attn_scratch_floats = 0, attn_counter_count = 0;
   float *logits_all = nullptr;
   long long logits_all_rows = 0;
   float *probs = nullptr;
@@ -204,6 +207,34 @@ void ensure_rows(litnice_b200_session *s, long long rows) {
     make_activation_map(&s->a_map[A_H], s->h, s->h_lo, rows, (int)F);
   }
   s->cap_rows = rows;
+}
+
+// Scratch of the attention kernel's key-split mode for contexts s_lo..s_hi.
+void ensure_attention_scratch(litnice_b200_session *s, int B, int s_lo, int s_hi) {
+  size_t need_f = 0, need_c = 0;
+  const int dh = s->dims.d_model / s->dims.n_heads;
+  for (int sl = s_lo; sl <= s_hi; ++sl) {
+    const AttentionPlan p = attention_plan(B, sl, s->dims.n_heads, dh);
+    if (p.scratch_floats > need_f) need_f = p.scratch_floats;
+    if (p.counters > need_c) need_c = p.counters;
+  }
+  if (need_f > s->attn_scratch_floats) {
+    LB_CUDA(cudaStreamSynchronize(s->st));
+    if (s->attn_scratch) cudaFree(s->attn_scratch);
+    s->attn_scratch = nullptr;
+    s->attn_scratch_floats = 0;
+    if (cudaMalloc(reinterpret_cast<void **>(&s->attn_scratch), need_f * 4) != cudaSuccess) throw std::bad_alloc();
+    s->attn_scratch_floats = need_f;
+  }
+  if (need_c > s->attn_counter_count) {
+    LB_CUDA(cudaStreamSynchronize(s->st));
+    if (s->attn_counters) cudaFree(s->attn_counters);
+    s->attn_counters = nullptr;
+    s->attn_counter_count = 0;
+    if (cudaMalloc(reinterpret_cast<void **>(&s->attn_counters), need_c * 4) != cudaSuccess) throw std::bad_alloc();
+    LB_CUDA(cudaMemsetAsync(s->attn_counters, 0, need_c * 4, s->st));  // kernels leave them at zero
+    s->attn_counter_count = need_c;
+  }
 }
 
 int pick_bn(const TcWeight &w, long long m) {
@@ -283,7 +314,8 @@ void enqueue_body(litnice_b200_session *s, int B, int sl) {
                nullptr);
     {
       ClassTimer t(s, &s->attn_ev);
-      launch_attention(s->qkv, s->ctx, s->tc ? s->ctx_lo : nullptr, nullptr, B, sl, d.n_heads, D, s->st);
+      launch_attention(s->qkv, s->ctx, s->tc ? s->ctx_lo : nullptr, B, sl, d.n_heads, D, s->attn_scratch,
+                       s->attn_counters, s->st);
       ++s->launches;
     }
     projection(s, A_CTX, R, D, P(s, o.out_w), tw ? &(*tw)[1] : nullptr, D, P(s, o.out_b), s->x, 0, s->y, nullptr);
@@ -480,6 +512,8 @@ void litnice_b200_session_destroy(litnice_b200_session *s) {
                   s->sampler_scratch, (void *)s->step_logits})
     if (p) cudaFree(p);
   if (s->xl_lo) cudaFree(s->xl_lo);
+  if (s->attn_scratch) cudaFree(s->attn_scratch);
+  if (s->attn_counters) cudaFree(s->attn_counters);
   for (auto &layer : s->tcw)
     for (auto &w : layer) {
       if (w.hi) cudaFree(w.hi);
@@ -595,6 +629,7 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
     if (steps > max_new) steps = max_new;
     if (steps < 0) steps = 0;
     ensure_rows(s, (long long)B * (s0 + (steps > 0 ? steps - 1 : 0)));
+    if (steps > 0) ensure_attention_scratch(s, B, s0, s0 + steps - 1);
     if (s->out_cap < s->cur_tokens + steps || s->out_tokens == nullptr) {
       LB_CUDA(cudaStreamSynchronize(s->st));
       int *n = nullptr;
@@ -715,6 +750,7 @@ int litnice_b200_forward(litnice_b200_session *s, const int32_t *ids, int32_t n_
     const long long R = (long long)B * seq_len;
     s->stats = litnice_b200_stats{};
     ensure_rows(s, R);
+    ensure_attention_scratch(s, B, seq_len, seq_len);
     upload_ids(s, ids, B, seq_len);
     const long long launches0 = s->launches;
     LB_CUDA(cudaEventRecord(s->ev0, s->st));
@@ -765,6 +801,7 @@ int litnice_b200_inspect(litnice_b200_session *s, const int32_t *ids, int32_t n_
     const int B = n_streams, V = s->dims.vocab_size;
     s->stats = litnice_b200_stats{};
     ensure_rows(s, (long long)B * seq_len);
+    ensure_attention_scratch(s, B, seq_len, seq_len);
     upload_ids(s, ids, B, seq_len);
     const long long launches0 = s->launches;
     LB_CUDA(cudaEventRecord(s->ev0, s->st));
@@ -841,6 +878,7 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
         repeats <= 0)
       throw std::invalid_argument("bad profile_step shape");
     ensure_rows(s, (long long)n_streams * seq_len);
+    ensure_attention_scratch(s, n_streams, seq_len, seq_len);
     s->gemm_ev.clear();
     s->attn_ev.clear();
     s->gemm_flops = 0;
