@@ -155,7 +155,8 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-               TcEpilogue ep, int m, int n, int k, DevErr *err) {
+               TcEpilogue ep, int m, int n, int k, int splits, float *__restrict__ part,
+               int *__restrict__ counters, DevErr *err) {
   using L = TcSmem<BN, STAGES>;
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
@@ -169,10 +170,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   constexpr int HOLDER_OFFSET = L::BAR_OFFSET + 8 * (2 * STAGES + 4);
   volatile unsigned *tmem_holder = reinterpret_cast<volatile unsigned *>(base_ptr + HOLDER_OFFSET);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + HOLDER_OFFSET + 4);
+  volatile int *last_flag = reinterpret_cast<volatile int *>(base_ptr + HOLDER_OFFSET + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * TC_BM;
-  const int kblocks = k / TC_BK;
+  // With split-k (gridDim.z CTAs per tile) this CTA owns k-blocks [kb0, kb0 + kblocks).
+  const int kb_total = k / TC_BK;
+  const int kb_per = (kb_total + splits - 1) / splits;
+  const int kb0 = blockIdx.z * kb_per;
+  const int kblocks = min(kb_per, kb_total - kb0);
   const int nchunks = (kblocks + TC_CHUNK - 1) / TC_CHUNK;
 
   if (threadIdx.x == 0) {
@@ -208,10 +214,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
       if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, err, 1)) break;
       const unsigned stage = base + (unsigned)s * L::STAGE_BYTES;
       mbar_expect_tx(full_bar(s), (unsigned)L::STAGE_BYTES);
-      tma_load_2d(stage, &map_a_hi, kb * TC_BK, m0, full_bar(s));
-      tma_load_2d(stage + L::A_BYTES, &map_a_lo, kb * TC_BK, m0, full_bar(s));
-      tma_load_2d(stage + 2 * L::A_BYTES, &map_b_hi, kb * TC_BK, n0, full_bar(s));
-      tma_load_2d(stage + 2 * L::A_BYTES + L::B_BYTES, &map_b_lo, kb * TC_BK, n0, full_bar(s));
+      const int kx = (kb0 + kb) * TC_BK;
+      tma_load_2d(stage, &map_a_hi, kx, m0, full_bar(s));
+      tma_load_2d(stage + L::A_BYTES, &map_a_lo, kx, m0, full_bar(s));
+      tma_load_2d(stage + 2 * L::A_BYTES, &map_b_hi, kx, n0, full_bar(s));
+      tma_load_2d(stage + 2 * L::A_BYTES + L::B_BYTES, &map_b_lo, kx, n0, full_bar(s));
       ++issued;
     }
     if (*abort_flag) {
@@ -299,7 +306,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
     }
-    if (ok && !*abort_flag && row < m) {
+    bool finish = ok && !*abort_flag;
+    if (splits > 1) {
+      // Split-k: leave the partial tile in scratch; the CTA that arrives last at
+      // the tile's counter adds all partials in split order and stores C.
+      const long long tile = (long long)blockIdx.y * gridDim.x + blockIdx.x;
+      float *mine = part + ((tile * splits + blockIdx.z) * TC_BM + (q * 32 + lane)) * BN;
+#pragma unroll
+      for (int j = 0; j < BN; j += 4)
+        *reinterpret_cast<float4 *>(mine + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        const int prev = atomicAdd(counters + tile, 1);
+        const int last = (prev == splits - 1) ? 1 : 0;
+        if (last) counters[tile] = 0;  // ready for the next launch
+        *last_flag = last;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      finish = finish && (*last_flag != 0);
+      if (finish) {
+        __threadfence();
+#pragma unroll
+        for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+        for (int z = 0; z < splits; ++z) {
+          const float *pz = part + ((tile * splits + z) * TC_BM + (q * 32 + lane)) * BN;
+#pragma unroll
+          for (int j = 0; j < BN; j += 4) {
+            const float4 t = __ldcg(reinterpret_cast<const float4 *>(pz + j));
+            acc[j] += t.x; acc[j + 1] += t.y; acc[j + 2] += t.z; acc[j + 3] += t.w;
+          }
+        }
+      }
+    }
+    if (finish && row < m) {
       const long long off = (long long)row * n + n0;
 #pragma unroll
       for (int j = 0; j < BN; j += 4) {
@@ -392,8 +432,8 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 template <int BN, int STAGES>
-void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const TcEpilogue &ep, DevErr *err,
-                cudaStream_t st) {
+void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const TcEpilogue &ep, int splits,
+                float *part, int *counters, DevErr *err, cudaStream_t st) {
   using L = TcSmem<BN, STAGES>;
   static bool configured[64] = {};
   int dev = 0;
@@ -402,8 +442,9 @@ void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const
     LB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     configured[dev] = true;
   }
-  dim3 grid(n / BN, (m + TC_BM - 1) / TC_BM);
-  gemm_tc_kernel<BN, STAGES><<<grid, TC_THREADS, L::TOTAL, st>>>(a.hi, a.lo, b.hi, b.lo, ep, m, n, k, err);
+  dim3 grid(n / BN, (m + TC_BM - 1) / TC_BM, splits);
+  gemm_tc_kernel<BN, STAGES><<<grid, TC_THREADS, L::TOTAL, st>>>(a.hi, a.lo, b.hi, b.lo, ep, m, n, k, splits, part,
+                                                                 counters, err);
   LB_LAUNCH_CHECK();
 }
 
@@ -428,13 +469,39 @@ void tc_make_map(CUtensorMap *map, const float *base, unsigned long long rows, u
     throw std::runtime_error("litnice_b200: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
 }
 
-void launch_gemm_tc(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, int bn, const TcEpilogue &ep,
-                    DevErr *err, cudaStream_t st) {
+TcPlan tc_plan(int m, int n, int k, bool has64, bool has128) {
+  TcPlan p{};
+  const long long mt = (m + TC_BM - 1) / TC_BM;
+  // Wide tiles when they still give one full wave; narrow tiles otherwise.
+  p.bn = (has128 && (!has64 || mt * (n / 128) >= 74)) ? 128 : 64;
+  const long long ctas = mt * (n / p.bn);
+  const int kb = k / TC_BK;
+  // Few tiles (a short single stream): cut k over several CTAs per tile so the
+  // serial k loop shortens, keeping one wave and at least 4 k-blocks per CTA.
+  int splits = 1;
+  if (ctas < 74) {
+    splits = (int)(148 / ctas);
+    if (splits > kb / 4) splits = kb / 4;
+    if (splits < 1) splits = 1;
+    const int per = (kb + splits - 1) / splits;
+    splits = (kb + per - 1) / per;  // no empty split
+  }
+  p.splits = splits;
+  p.scratch_floats = splits > 1 ? (size_t)ctas * splits * TC_BM * p.bn : 0;
+  p.counters = splits > 1 ? (size_t)ctas : 0;
+  return p;
+}
+
+void launch_gemm_tc(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const TcPlan &plan,
+                    const TcEpilogue &ep, float *scratch, int *counters, DevErr *err, cudaStream_t st) {
   if (m <= 0) return;
+  const int bn = plan.bn;
   if (k < TC_BK || k % TC_BK != 0 || (bn != 64 && bn != 128) || n % bn != 0)
     throw std::invalid_argument("litnice_b200: tensor-core GEMM needs k % 32 == 0 and n % bn == 0");
-  if (bn == 128) launch_cfg<128, 3>(a, b, m, n, k, ep, err, st);
-  else launch_cfg<64, 4>(a, b, m, n, k, ep, err, st);
+  if (plan.splits > 1 && (scratch == nullptr || counters == nullptr))
+    throw std::invalid_argument("litnice_b200: split-k tensor-core GEMM needs scratch");
+  if (bn == 128) launch_cfg<128, 3>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st);
+  else launch_cfg<64, 4>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st);
 }
 
 void launch_split_tf32(const float *x, float *hi, float *lo, long long count, cudaStream_t st) {

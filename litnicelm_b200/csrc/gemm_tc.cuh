@@ -39,10 +39,22 @@ bool tc_runtime_available();
 void tc_make_map(CUtensorMap *map, const float *base, unsigned long long rows, unsigned long long k,
                  unsigned box_rows);
 
-// bn is 64 or 128; requires n % bn == 0, k % 32 == 0; a maps must use box rows
-// 128, b maps box rows bn.
-void launch_gemm_tc(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, int bn,
-                    const TcEpilogue &ep, DevErr *err, cudaStream_t st);
+// How one product is tiled: tile width (64 or 128 columns), how many CTAs share
+// the k range of a tile, and the scratch that sharing needs (floats of partial
+// tiles; int counters that must be zero before the first launch and are left
+// at zero by every launch).
+struct TcPlan {
+  int bn;
+  int splits;
+  size_t scratch_floats;
+  size_t counters;
+};
+TcPlan tc_plan(int m, int n, int k, bool has64, bool has128);
+
+// Requires n % plan.bn == 0, k % 32 == 0; a maps must use box rows 128, b maps
+// box rows plan.bn.
+void launch_gemm_tc(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const TcPlan &plan,
+                    const TcEpilogue &ep, float *scratch, int *counters, DevErr *err, cudaStream_t st);
 
 // x -> (hi, lo) elementwise.
 void launch_split_tf32(const float *x, float *hi, float *lo, long long count, cudaStream_t st);

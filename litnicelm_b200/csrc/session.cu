@@ -129,6 +129,8 @@ struct litnice_b200_session {
   std::vector<std::array<TcWeight, 4>> tcw;  // per layer: qkv, out, w1, w2
   TcWeight tc_head;
   TcMatrix a_map[4]{};
+  float *tc_scratch = nullptr;   // split-k partial tiles of the tensor-core GEMM
+  int *tc_counters = nullptr;
   float *attn_scratch = nullptr;
   int *attn_counters = nullptr;
   size_t attn_scratch_floats = 0, attn_counter_count = 0;
@@ -237,10 +239,6 @@ void ensure_attention_scratch(litnice_b200_session *s, int B, int s_lo, int s_hi
   }
 }
 
-int pick_bn(const TcWeight &w, long long m) {
-  if (w.has128 && (!w.has64 || ((m + TC_BM - 1) / TC_BM) * (w.n / 128) >= 120)) return 128;
-  return 64;
-}
 
 struct ClassTimer {
   litnice_b200_session *s;
@@ -283,8 +281,9 @@ void projection(litnice_b200_session *s, AKind ak, long long rows, int k, const 
     } else {
       ep.c = c;
     }
-    const int bn = pick_bn(*tw, rows);
-    launch_gemm_tc(s->a_map[ak], bn == 128 ? tw->m128 : tw->m64, (int)rows, n, k, bn, ep, s->err_dev, s->st);
+    const TcPlan plan = tc_plan((int)rows, n, k, tw->has64, tw->has128);
+    launch_gemm_tc(s->a_map[ak], plan.bn == 128 ? tw->m128 : tw->m64, (int)rows, n, k, plan, ep, s->tc_scratch,
+                   s->tc_counters, s->err_dev, s->st);
     return;
   }
   const float *a = ak == A_LN ? s->ln : ak == A_CTX ? s->ctx : ak == A_H ? s->h : s->xl;
@@ -486,6 +485,10 @@ int litnice_b200_session_create(const litnice_b200_dims *dims, int32_t max_strea
       must(cudaMalloc(reinterpret_cast<void **>(&s->xl_lo), lr * d.d_model * 4));
       LB_CUDA(cudaMemsetAsync(s->xl_lo, 0, lr * d.d_model * 4, s->st));
       make_activation_map(&s->a_map[A_XL], s->xl, s->xl_lo, (long long)lr, d.d_model);
+      // A split product never uses more than 148 CTAs of at most 128 x 128 floats.
+      must(cudaMalloc(reinterpret_cast<void **>(&s->tc_scratch), (size_t)148 * TC_BM * 128 * 4));
+      must(cudaMalloc(reinterpret_cast<void **>(&s->tc_counters), 148 * 4));
+      LB_CUDA(cudaMemsetAsync(s->tc_counters, 0, 148 * 4, s->st));
     }
     must(cudaMalloc(reinterpret_cast<void **>(&s->logits), lr * d.vocab_size * 4));
     must(cudaMalloc(reinterpret_cast<void **>(&s->probs), lr * d.vocab_size * 4));
@@ -512,6 +515,8 @@ void litnice_b200_session_destroy(litnice_b200_session *s) {
                   s->sampler_scratch, (void *)s->step_logits})
     if (p) cudaFree(p);
   if (s->xl_lo) cudaFree(s->xl_lo);
+  if (s->tc_scratch) cudaFree(s->tc_scratch);
+  if (s->tc_counters) cudaFree(s->tc_counters);
   if (s->attn_scratch) cudaFree(s->attn_scratch);
   if (s->attn_counters) cudaFree(s->attn_counters);
   for (auto &layer : s->tcw)
@@ -965,7 +970,14 @@ int litnice_b200_projection_host(int32_t engine, const float *a, int32_t m, int3
       float *w_hi = dev_alloc((size_t)k * n * 4), *w_lo = dev_alloc((size_t)k * n * 4);
       launch_split_tf32(da, a_hi, a_lo, mp * k, st);
       launch_transpose_split(dw, k, n, w_hi, w_lo, st);
-      const int bn = (n % 128 == 0 && (mp / TC_BM) * (n / 128) >= 120) ? 128 : 64;
+      const TcPlan plan = tc_plan(m, n, k, n % 64 == 0, n % 128 == 0);
+      const int bn = plan.bn;
+      float *scr = plan.scratch_floats ? dev_alloc(plan.scratch_floats * 4) : nullptr;
+      int *cnt = nullptr;
+      if (plan.counters) {
+        cnt = reinterpret_cast<int *>(dev_alloc(plan.counters * 4));
+        LB_CUDA(cudaMemsetAsync(cnt, 0, plan.counters * 4, st));
+      }
       TcMatrix ma{}, mb{};
       tc_make_map(&ma.hi, a_hi, (unsigned long long)mp, (unsigned long long)k, TC_BM);
       tc_make_map(&ma.lo, a_lo, (unsigned long long)mp, (unsigned long long)k, TC_BM);
@@ -976,7 +988,7 @@ int litnice_b200_projection_host(int32_t engine, const float *a, int32_t m, int3
       ep.residual = dr;
       ep.relu = relu;
       ep.c = dc;
-      launch_gemm_tc(ma, mb, m, n, k, bn, ep, err_dev, st);
+      launch_gemm_tc(ma, mb, m, n, k, plan, ep, scr, cnt, err_dev, st);
     }
     LB_CUDA(cudaMemcpyAsync(c, dc, (size_t)m * n * 4, cudaMemcpyDeviceToHost, st));
     LB_CUDA(cudaStreamSynchronize(st));
