@@ -253,6 +253,12 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
 int litnice_b200_projection_host(int32_t engine, const float *a, int32_t m, int32_t k, const float *w, int32_t n,
                                  const float *bias, const float *residual, int32_t relu, float *c);
 
+/* Measurement aid: the same projection (no epilogue terms) launched `repeats`
+ * times back to back on one stream; *avg_us receives the mean device time per
+ * launch after the first (CUDA events on that stream). */
+int litnice_b200_projection_time(int32_t engine, const float *a, int32_t m, int32_t k, const float *w, int32_t n,
+                                 float *c, int32_t repeats, double *avg_us);
+
 /* No counterpart in the reference. Few-row product out[m, n] = x[m, k] * W[k, n]
  * (+ bias[n]) for callers that cannot allocate device memory while they run:
  * a host that has already given all device memory to its own arenas, or a

@@ -34,8 +34,9 @@ __host__ __device__ inline int chunks_of(int qt, int kc) { return (qt + kc) / kc
 
 template <int DH>
 __global__ void __launch_bounds__(256)
-attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, float *__restrict__ ctx_lo, int s,
-                 int d_model, float scale, int kc, float *__restrict__ part, int *__restrict__ counters) {
+attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, float *__restrict__ ctx_lo, int s_cap,
+                 int d_model, float scale, int kc, float *__restrict__ part, int *__restrict__ counters,
+                 const LoopState *state) {
   constexpr int CPT = DH / 16;  // output columns per thread
   constexpr int PART = AT_BQ * (DH + 2);  // floats of one partial: o[64][DH], m[64], l[64]
   extern __shared__ __align__(16) float smem[];
@@ -44,9 +45,13 @@ attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, float *
   float (*Vs)[DH] = reinterpret_cast<float (*)[DH]>(smem + 2 * DH * AT_BQ);      // [64][DH]
   float (*Ps)[AT_PLD] = reinterpret_cast<float (*)[AT_PLD]>(smem + 3 * DH * AT_BQ);  // [64][68]
   __shared__ int s_last;
+  pdl_launch_dependents();
+  pdl_wait();
 
+  // The grid is laid out for s_cap; the actual length shares its tile count.
+  const int s = state ? state->s : s_cap;
   // blockIdx.x enumerates (query tile, chunk) pairs, longest query tiles first.
-  const int tiles = (s + AT_BQ - 1) / AT_BQ;
+  const int tiles = (s_cap + AT_BQ - 1) / AT_BQ;
   int idx = blockIdx.x, qt = tiles - 1;
   for (; qt > 0; --qt) {
     const int nc = chunks_of(qt, kc);
@@ -246,7 +251,7 @@ attention_kernel(const float *__restrict__ qkv, float *__restrict__ ctx, float *
 
 template <int DH>
 void launch_dh(const float *qkv, float *ctx, float *ctx_lo, int n_streams, int s, int n_heads, int d_model,
-               const AttentionPlan &plan, float *scratch, int *counters, cudaStream_t st) {
+               const AttentionPlan &plan, float *scratch, int *counters, const LoopState *state, cudaStream_t st) {
   const size_t smem = (size_t)(3 * DH * AT_BQ + AT_BQ * AT_PLD) * sizeof(float);
   static bool configured[64] = {};  // the attribute is per device
   int dev = 0;
@@ -258,8 +263,8 @@ void launch_dh(const float *qkv, float *ctx, float *ctx_lo, int n_streams, int s
   }
   dim3 grid(plan.ctas_per_head, n_heads, n_streams);
   const float scale = 1.0f / sqrtf((float)DH);
-  attention_kernel<DH><<<grid, 256, smem, st>>>(qkv, ctx, ctx_lo, s, d_model, scale, plan.kc, scratch, counters);
-  LB_LAUNCH_CHECK();
+  launch_pdl(attention_kernel<DH>, grid, dim3(256), smem, st, g_pdl_enabled, qkv, ctx, ctx_lo, s, d_model, scale, plan.kc,
+             scratch, counters, state);
 }
 
 }  // namespace
@@ -291,16 +296,16 @@ AttentionPlan attention_plan(int n_streams, int s, int n_heads, int dh) {
 }
 
 void launch_attention(const float *qkv, float *ctx, float *ctx_lo, int n_streams, int s, int n_heads, int d_model,
-                      float *scratch, int *counters, cudaStream_t st) {
+                      float *scratch, int *counters, const LoopState *state, cudaStream_t st) {
   const int dh = d_model / n_heads;
   const AttentionPlan plan = attention_plan(n_streams, s, n_heads, dh);
   if (plan.scratch_floats > 0 && (scratch == nullptr || counters == nullptr))
     throw std::invalid_argument("litnice_b200: attention needs scratch for this shape");
   switch (dh) {
-    case 16: launch_dh<16>(qkv, ctx, ctx_lo, n_streams, s, n_heads, d_model, plan, scratch, counters, st); break;
-    case 32: launch_dh<32>(qkv, ctx, ctx_lo, n_streams, s, n_heads, d_model, plan, scratch, counters, st); break;
-    case 64: launch_dh<64>(qkv, ctx, ctx_lo, n_streams, s, n_heads, d_model, plan, scratch, counters, st); break;
-    case 128: launch_dh<128>(qkv, ctx, ctx_lo, n_streams, s, n_heads, d_model, plan, scratch, counters, st); break;
+    case 16: launch_dh<16>(qkv, ctx, ctx_lo, n_streams, s, n_heads, d_model, plan, scratch, counters, state, st); break;
+    case 32: launch_dh<32>(qkv, ctx, ctx_lo, n_streams, s, n_heads, d_model, plan, scratch, counters, state, st); break;
+    case 64: launch_dh<64>(qkv, ctx, ctx_lo, n_streams, s, n_heads, d_model, plan, scratch, counters, state, st); break;
+    case 128: launch_dh<128>(qkv, ctx, ctx_lo, n_streams, s, n_heads, d_model, plan, scratch, counters, state, st); break;
     default:
       throw std::invalid_argument("litnice_b200: fused attention supports head_dim 16, 32, 64, 128");
   }

@@ -40,6 +40,48 @@ struct DevErr {
   int detail;
 };
 
+// ---- programmatic dependent launch ----------------------------------------------
+// Kernels of the native token loop are launched so that a kernel may start
+// (set up barriers, allocate tensor memory, prefetch weights) while its
+// predecessor on the stream is still draining. pdl_wait() blocks until every
+// earlier kernel has completed and its writes are visible; nothing produced or
+// consumed by earlier kernels may be touched before it. Launched the ordinary
+// way, both calls are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() {
+#if defined(__CUDA_ARCH__)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void pdl_wait() {
+#if defined(__CUDA_ARCH__)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#endif
+}
+
+// Whether native-loop launchers on this host thread use the early-launch attribute.
+extern thread_local bool g_pdl_enabled;
+struct PdlScope {
+  bool prev;
+  explicit PdlScope(bool on) : prev(g_pdl_enabled) { g_pdl_enabled = on; }
+  ~PdlScope() { g_pdl_enabled = prev; }
+};
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                       Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cuda_check(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...), "cudaLaunchKernelEx", __FILE__, __LINE__);
+}
+
 // ---- views ----------------------------------------------------------------
 
 // Rows of a tensor: every axis but the last forms the row index ("prefix" in
@@ -143,8 +185,11 @@ void launch_gather_last_ln(const float *x, const float *gamma, const float *beta
                            const LoopState *state, int n_streams, int s_host, int d, float *out,
                            float *out_lo, cudaStream_t st);
 // out_lo != nullptr: out receives the TF32 high part and out_lo the low part.
+// state != nullptr: the launch covers `rows` as an upper bound and the kernel
+// takes n_streams * state->s as the actual row count.
 void launch_layernorm_dense(const float *x, const float *gamma, const float *beta, long long rows,
-                            int d, float *out, float *out_lo, cudaStream_t st);
+                            int d, float *out, float *out_lo, const LoopState *state, int n_streams,
+                            cudaStream_t st);
 
 // gemv.cu: out[m, n] = x[m, :] . W[:, n] for m <= 8 rows; W row-major [k, n].
 // scratch must hold gemv_scratch_floats(m, n, k) floats when the launcher
@@ -164,8 +209,10 @@ struct AttentionPlan {
   size_t counters;
 };
 AttentionPlan attention_plan(int n_streams, int s, int n_heads, int dh);
+// state != nullptr: s is an upper bound with the same number of 64-row tiles
+// as the actual context length state->s.
 void launch_attention(const float *qkv, float *ctx, float *ctx_lo, int n_streams, int s, int n_heads, int d_model,
-                      float *scratch, int *counters, cudaStream_t st);
+                      float *scratch, int *counters, const LoopState *state, cudaStream_t st);
 
 // sampler.cu
 struct SamplerParams {

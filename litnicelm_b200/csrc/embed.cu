@@ -16,6 +16,8 @@ __global__ void embed_pos_kernel(const float *__restrict__ tok_emb,
                                  const float *__restrict__ pos_emb, const int *__restrict__ ids,
                                  int ids_ld, const LoopState *state, int n_streams, int s_cap, int d,
                                  int vocab, float *__restrict__ x, DevErr *err) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int s = state ? state->s : s_cap;
   const long long r = blockIdx.x;
   if (r >= (long long)n_streams * s) return;
@@ -51,6 +53,8 @@ __global__ void gather_last_ln_kernel(const float *__restrict__ x, const float *
                                       const float *__restrict__ beta, const LoopState *state,
                                       int n_streams, int s_cap, int d, float *__restrict__ out,
                                       float *__restrict__ out_lo) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int s = state ? state->s : s_cap;
   const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (b >= n_streams) return;
@@ -81,6 +85,8 @@ __global__ void gather_last_ln_kernel(const float *__restrict__ x, const float *
 }
 
 __global__ void advance_state_kernel(LoopState *state) {
+  pdl_launch_dependents();
+  pdl_wait();
   state->s += 1;
   state->step += 1;
 }
@@ -92,23 +98,20 @@ void launch_embed_pos(const float *tok_emb, const float *pos_emb, const int *ids
                       float *x, DevErr *err, cudaStream_t st) {
   const long long rows = (long long)n_streams * s_host;
   if (rows <= 0) return;
-  embed_pos_kernel<<<(unsigned)rows, d >= 512 ? 128 : 32, 0, st>>>(
-      tok_emb, pos_emb, ids, ids_ld, state, n_streams, s_host, d, vocab, x, err);
-  LB_LAUNCH_CHECK();
+  launch_pdl(embed_pos_kernel, dim3((unsigned)rows), dim3(d >= 512 ? 128 : 32), 0, st, g_pdl_enabled, tok_emb, pos_emb,
+             ids, ids_ld, state, n_streams, s_host, d, vocab, x, err);
 }
 
 void launch_gather_last_ln(const float *x, const float *gamma, const float *beta,
                            const LoopState *state, int n_streams, int s_host, int d, float *out,
                            float *out_lo, cudaStream_t st) {
   const int warps = 4;
-  gather_last_ln_kernel<<<(n_streams + warps - 1) / warps, warps * 32, 0, st>>>(
-      x, gamma, beta, state, n_streams, s_host, d, out, out_lo);
-  LB_LAUNCH_CHECK();
+  launch_pdl(gather_last_ln_kernel, dim3((n_streams + warps - 1) / warps), dim3(warps * 32), 0, st, g_pdl_enabled, x,
+             gamma, beta, state, n_streams, s_host, d, out, out_lo);
 }
 
 void launch_advance_state(LoopState *state, cudaStream_t st) {
-  advance_state_kernel<<<1, 1, 0, st>>>(state);
-  LB_LAUNCH_CHECK();
+  launch_pdl(advance_state_kernel, dim3(1), dim3(1), 0, st, g_pdl_enabled, state);
 }
 
 }  // namespace lb

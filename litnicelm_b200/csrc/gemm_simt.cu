@@ -132,6 +132,8 @@ gemm_simt_kernel(GemmArgs g) {
   constexpr int NT = (BM / TM) * (BN / TN);
   __shared__ __align__(16) float As[2][BK][BM];
   __shared__ __align__(16) float Bs[2][BK][BN];
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int tid = threadIdx.x;
   const int tx = tid % (BN / TN), ty = tid / (BN / TN);
@@ -248,8 +250,7 @@ bool batch_aligned16(const MatView &v) {
 template <int BM, int BN, int TM, int TN, int AMODE, int BMODE>
 void launch_cfg(const GemmArgs &g, long long batch, cudaStream_t st) {
   dim3 grid((g.n + BN - 1) / BN, (g.m + BM - 1) / BM, (unsigned)batch);
-  gemm_simt_kernel<BM, BN, TM, TN, AMODE, BMODE><<<grid, (BM / TM) * (BN / TN), 0, st>>>(g);
-  LB_LAUNCH_CHECK();
+  launch_pdl(gemm_simt_kernel<BM, BN, TM, TN, AMODE, BMODE>, grid, dim3((BM / TM) * (BN / TN)), 0, st, g_pdl_enabled, g);
 }
 
 template <int AMODE, int BMODE>

@@ -34,7 +34,7 @@ __device__ __forceinline__ unsigned smem_u32(const void *p) {
 }
 __device__ __forceinline__ unsigned long long global_timer() {
   unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)::"memory");
   return t;
 }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
@@ -137,9 +137,11 @@ struct TcSmem {
 // a non-zero accumulator loses up to one ulp of it, always in the same
 // direction (measured: ~3e-5 relative at k = 2048 with one long chain). So the
 // k loop is cut into chunks of TC_CHUNK k-blocks: each chunk is accumulated in
-// one of two TMEM buffers starting from zero, and the epilogue warps add the
-// finished chunk into fp32 registers (round to nearest) while the next chunk is
-// multiplied into the other buffer. Inside a k-block the two small products
+// one of the TMEM buffers starting from zero, and the epilogue warps add the
+// finished chunk into fp32 registers (round to nearest) while the next chunks
+// are multiplied into the other buffers. All 512 TMEM columns are used as a
+// ring of 512/BN buffers, which hides the MMA -> epilogue -> MMA hand-over
+// latency (about a microsecond per round trip). Inside a k-block the two small products
 // (a_lo*b_hi, a_hi*b_lo) are issued first, while the accumulator is still
 // ~2^-11 of its final size, so only the a_hi*b_hi steps truncate at full scale.
 #ifndef LB_TC_CHUNK
@@ -162,12 +164,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
   unsigned char *base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const unsigned bar_base = base + L::BAR_OFFSET;
-  // barriers: full[S], empty[S], tmem_full[2], tmem_empty[2]
+  // barriers: full[S], empty[S], tmem_full[NBUF], tmem_empty[NBUF]
+  constexpr int NBUF = 512 / BN;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
-  auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
-  constexpr int HOLDER_OFFSET = L::BAR_OFFSET + 8 * (2 * STAGES + 4);
+  auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + NBUF + b); };
+  constexpr int HOLDER_OFFSET = L::BAR_OFFSET + 8 * (2 * STAGES + 2 * NBUF);
+  static_assert(HOLDER_OFFSET + 16 <= L::BAR_OFFSET + 256, "barrier area too small");
   volatile unsigned *tmem_holder = reinterpret_cast<volatile unsigned *>(base_ptr + HOLDER_OFFSET);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + HOLDER_OFFSET + 4);
   volatile int *last_flag = reinterpret_cast<volatile int *>(base_ptr + HOLDER_OFFSET + 8);
@@ -181,12 +185,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   const int kblocks = min(kb_per, kb_total - kb0);
   const int nchunks = (kblocks + TC_CHUNK - 1) / TC_CHUNK;
 
+  pdl_launch_dependents();
+  const bool stamp = ep.timeline != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  if (stamp && threadIdx.x == 0) ep.timeline[0] = global_timer();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < NBUF; ++b) {
       mbar_init(tmem_full_bar(b), 1);
       mbar_init(tmem_empty_bar(b), 4);  // one arrival per epilogue warp
     }
@@ -194,9 +201,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) {  // whole warp: allocate two accumulators of BN columns each
+  if (warp == 1) {  // whole warp: allocate all 512 columns (NBUF accumulators of BN columns)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_holder)),
-                 "r"((unsigned)(2 * BN))
+                 "r"(512u)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -204,21 +211,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_holder;
+  if (stamp && threadIdx.x == 0) ep.timeline[1] = global_timer();
 
-  if (warp == 0 && lane == 0) {
+  // Whole warps take a role and stay converged (block-wide barriers count
+  // warps, so a warp must never reach one in pieces); one lane issues.
+  if (warp == 0) {
     // ---- TMA producer ----
-    int issued = 0;
-    for (int kb = 0; kb < kblocks; ++kb) {
+    // Weights do not depend on earlier kernels: their tiles of the first
+    // stages are requested before waiting for the predecessor to finish.
+    const int pre = min(STAGES, kblocks);
+    if (lane == 0) {
+      for (int kb = 0; kb < pre; ++kb) {
+        const unsigned stage = base + (unsigned)kb * L::STAGE_BYTES;
+        const int kx = (kb0 + kb) * TC_BK;
+        mbar_expect_tx(full_bar(kb), (unsigned)L::STAGE_BYTES);
+        tma_load_2d(stage + 2 * L::A_BYTES, &map_b_hi, kx, n0, full_bar(kb));
+        tma_load_2d(stage + 2 * L::A_BYTES + L::B_BYTES, &map_b_lo, kx, n0, full_bar(kb));
+      }
+    }
+    pdl_wait();
+    if (lane == 0) {
+      for (int kb = 0; kb < pre; ++kb) {
+        const unsigned stage = base + (unsigned)kb * L::STAGE_BYTES;
+        const int kx = (kb0 + kb) * TC_BK;
+        tma_load_2d(stage, &map_a_hi, kx, m0, full_bar(kb));
+        tma_load_2d(stage + L::A_BYTES, &map_a_lo, kx, m0, full_bar(kb));
+      }
+      if (stamp) ep.timeline[2] = global_timer();
+    }
+    __syncwarp();
+    int issued = pre;
+    for (int kb = pre; kb < kblocks; ++kb) {
       const int s = kb % STAGES;
       const unsigned ph = (unsigned)(kb / STAGES) & 1u;
-      if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, err, 1)) break;
-      const unsigned stage = base + (unsigned)s * L::STAGE_BYTES;
-      mbar_expect_tx(full_bar(s), (unsigned)L::STAGE_BYTES);
-      const int kx = (kb0 + kb) * TC_BK;
-      tma_load_2d(stage, &map_a_hi, kx, m0, full_bar(s));
-      tma_load_2d(stage + L::A_BYTES, &map_a_lo, kx, m0, full_bar(s));
-      tma_load_2d(stage + 2 * L::A_BYTES, &map_b_hi, kx, n0, full_bar(s));
-      tma_load_2d(stage + 2 * L::A_BYTES + L::B_BYTES, &map_b_lo, kx, n0, full_bar(s));
+      const bool ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, err, 1);
+      __syncwarp();
+      if (!ok) break;
+      if (lane == 0) {
+        const unsigned stage = base + (unsigned)s * L::STAGE_BYTES;
+        mbar_expect_tx(full_bar(s), (unsigned)L::STAGE_BYTES);
+        const int kx = (kb0 + kb) * TC_BK;
+        tma_load_2d(stage, &map_a_hi, kx, m0, full_bar(s));
+        tma_load_2d(stage + L::A_BYTES, &map_a_lo, kx, m0, full_bar(s));
+        tma_load_2d(stage + 2 * L::A_BYTES, &map_b_hi, kx, n0, full_bar(s));
+        tma_load_2d(stage + 2 * L::A_BYTES + L::B_BYTES, &map_b_lo, kx, n0, full_bar(s));
+      }
+      __syncwarp();
       ++issued;
     }
     if (*abort_flag) {
@@ -230,16 +268,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
           if (global_timer() - t0 > WAIT_LIMIT_NS) break;
       }
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1) {
     // ---- MMA issuer ----
     const unsigned idesc = umma_idesc_tf32(BN);
     bool ok = true;
     int committed = -1;  // last chunk whose completion was committed to a tmem_full barrier
     for (int c = 0; c < nchunks && ok; ++c) {
-      const int buf = c & 1;
+      const int buf = c % NBUF;
       const unsigned tmem_d = tmem_base + (unsigned)(buf * BN);
       // the epilogue must have drained this buffer's previous chunk
-      ok = mbar_wait(tmem_empty_bar(buf), ((unsigned)(c >> 1) & 1u) ^ 1u, abort_flag, err, 4);
+      ok = mbar_wait(tmem_empty_bar(buf), ((unsigned)(c / NBUF) & 1u) ^ 1u, abort_flag, err, 4);
+      __syncwarp();
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int kb_end = min(kblocks, (c + 1) * TC_CHUNK);
@@ -247,41 +286,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
         const int s = kb % STAGES;
         const unsigned ph = (unsigned)(kb / STAGES) & 1u;
         ok = mbar_wait(full_bar(s), ph, abort_flag, err, 2);
+        __syncwarp();
         if (!ok) break;
+        if (stamp && kb == 0 && lane == 0) ep.timeline[3] = global_timer();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned stage = base + (unsigned)s * L::STAGE_BYTES;
         const unsigned long long a_hi = umma_desc_k128(stage);
         const unsigned long long a_lo = umma_desc_k128(stage + L::A_BYTES);
         const unsigned long long b_hi = umma_desc_k128(stage + 2 * L::A_BYTES);
         const unsigned long long b_lo = umma_desc_k128(stage + 2 * L::A_BYTES + L::B_BYTES);
+        if (lane == 0) {
 #pragma unroll
-        for (int ks = 0; ks < TC_BK / 8; ++ks) {
-          const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);  // 8 fp32 = 32 bytes along k
-          const unsigned first = (kb == c * TC_CHUNK && ks == 0) ? 0u : 1u;   // a chunk starts from zero
-          tc_mma_tf32(tmem_d, a_lo + adv, b_hi + adv, idesc, first);
-          tc_mma_tf32(tmem_d, a_hi + adv, b_lo + adv, idesc, 1u);
-        }
+          for (int ks = 0; ks < TC_BK / 8; ++ks) {
+            const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);  // 8 fp32 = 32 bytes along k
+            const unsigned first = (kb == c * TC_CHUNK && ks == 0) ? 0u : 1u;   // a chunk starts from zero
+            tc_mma_tf32(tmem_d, a_lo + adv, b_hi + adv, idesc, first);
+            tc_mma_tf32(tmem_d, a_hi + adv, b_lo + adv, idesc, 1u);
+          }
 #pragma unroll
-        for (int ks = 0; ks < TC_BK / 8; ++ks) {
-          const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);
-          tc_mma_tf32(tmem_d, a_hi + adv, b_hi + adv, idesc, 1u);
+          for (int ks = 0; ks < TC_BK / 8; ++ks) {
+            const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);
+            tc_mma_tf32(tmem_d, a_hi + adv, b_hi + adv, idesc, 1u);
+          }
+          tc_commit(empty_bar(s));  // the stage is free once these MMAs have read it
         }
-        tc_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+        __syncwarp();
       }
       if (ok) {
-        tc_commit(tmem_full_bar(buf));  // arrives when every MMA of this chunk has completed
+        if (lane == 0) tc_commit(tmem_full_bar(buf));  // arrives when every MMA of this chunk has completed
+        __syncwarp();
         committed = c;
       }
     }
+    if (stamp && lane == 0) ep.timeline[4] = global_timer();
     if (!ok) {  // give the tensor pipe a bounded chance to finish before TMEM is freed
-      const int buf = (committed + 1) & 1;
-      tc_commit(tmem_full_bar(buf));
+      const int buf = (committed + 1) % NBUF;
+      if (lane == 0) tc_commit(tmem_full_bar(buf));
+      __syncwarp();
       const unsigned long long t0 = global_timer();
-      while (!mbar_try_wait(tmem_full_bar(buf), (unsigned)((committed + 1) >> 1) & 1u))
+      while (!mbar_try_wait(tmem_full_bar(buf), (unsigned)((committed + 1) / NBUF) & 1u))
         if (global_timer() - t0 > WAIT_LIMIT_NS) break;
     }
+    __syncwarp();
   } else if (warp >= 2) {
     // ---- epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 ----
+    pdl_wait();  // residual reads, C and scratch writes must follow the predecessor
     const int q = warp & 3;
     const int row = m0 + q * 32 + lane;
     float acc[BN];
@@ -289,8 +338,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     for (int j = 0; j < BN; ++j) acc[j] = 0.f;
     bool ok = true;
     for (int c = 0; c < nchunks && ok; ++c) {
-      const int buf = c & 1;
-      ok = mbar_wait(tmem_full_bar(buf), (unsigned)(c >> 1) & 1u, abort_flag, err, 3);
+      const int buf = c % NBUF;
+      ok = mbar_wait(tmem_full_bar(buf), (unsigned)(c / NBUF) & 1u, abort_flag, err, 3);
       __syncwarp();
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -306,6 +355,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
     }
+    if (stamp && warp == 2 && lane == 0) ep.timeline[5] = global_timer();
     bool finish = ok && !*abort_flag;
     if (splits > 1) {
       // Split-k: leave the partial tile in scratch; the CTA that arrives last at
@@ -367,12 +417,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
       }
     }
   }
+  if (stamp && warp == 2 && lane == 0) ep.timeline[6] = global_timer();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (stamp && threadIdx.x == 0) ep.timeline[7] = global_timer();
   if (warp == 1) {
     __syncwarp();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)(2 * BN)) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
@@ -443,9 +495,8 @@ void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const
     configured[dev] = true;
   }
   dim3 grid(n / BN, (m + TC_BM - 1) / TC_BM, splits);
-  gemm_tc_kernel<BN, STAGES><<<grid, TC_THREADS, L::TOTAL, st>>>(a.hi, a.lo, b.hi, b.lo, ep, m, n, k, splits, part,
-                                                                 counters, err);
-  LB_LAUNCH_CHECK();
+  launch_pdl(gemm_tc_kernel<BN, STAGES>, grid, dim3(TC_THREADS), (size_t)L::TOTAL, st, g_pdl_enabled, a.hi, a.lo, b.hi,
+             b.lo, ep, m, n, k, splits, part, counters, err);
 }
 
 }  // namespace

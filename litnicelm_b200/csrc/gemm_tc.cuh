@@ -28,6 +28,9 @@ struct TcEpilogue {
   float *c = nullptr;               // [M, N] dense fp32 result (may be null)
   float *c_hi = nullptr;            // optional split result for a following GEMM
   float *c_lo = nullptr;
+  // Measurement aid: when set, CTA (0,0,0) stores %globaltimer stamps of its
+  // pipeline milestones here (8 entries).
+  unsigned long long *timeline = nullptr;
 };
 
 // True when the driver exposes cuTensorMapEncodeTiled (resolved at run time so

@@ -31,6 +31,8 @@ gemv_kernel(const float *__restrict__ x, const float *__restrict__ w, int k, int
             float *__restrict__ partial) {
   __shared__ __align__(16) float xs[M][GV_XCHUNK];
   __shared__ __align__(16) float red[GV_WARPS][M][GV_COLS];
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int n0 = blockIdx.x * GV_COLS + lane * 4;
   const int kb = blockIdx.y * k_per_split;
@@ -98,6 +100,8 @@ gemv_kernel(const float *__restrict__ x, const float *__restrict__ w, int k, int
 
 __global__ void gemv_reduce_kernel(const float *__restrict__ partial, int splits, int m, int n,
                                    const float *__restrict__ bias, float *__restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (idx >= (long long)m * n) return;
   float v = 0.f;
@@ -125,14 +129,15 @@ void launch_m(const float *x, const float *w, int k, int n, const float *bias, f
   float *partial = splits > 1 ? scratch : nullptr;
   const bool vec = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
   if (vec)
-    gemv_kernel<M, true><<<grid, GV_WARPS * 32, 0, st>>>(x, w, k, n, k_per_split, bias, out, partial);
+    launch_pdl(gemv_kernel<M, true>, grid, dim3(GV_WARPS * 32), 0, st, g_pdl_enabled, x, w, k, n, k_per_split, bias, out,
+               partial);
   else
-    gemv_kernel<M, false><<<grid, GV_WARPS * 32, 0, st>>>(x, w, k, n, k_per_split, bias, out, partial);
-  LB_LAUNCH_CHECK();
+    launch_pdl(gemv_kernel<M, false>, grid, dim3(GV_WARPS * 32), 0, st, g_pdl_enabled, x, w, k, n, k_per_split, bias, out,
+               partial);
   if (splits > 1) {
     const long long total = (long long)M * n;
-    gemv_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partial, splits, M, n, bias, out);
-    LB_LAUNCH_CHECK();
+    launch_pdl(gemv_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, g_pdl_enabled,
+               (const float *)partial, splits, M, n, bias, out);
   }
 }
 

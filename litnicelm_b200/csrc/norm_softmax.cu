@@ -48,7 +48,11 @@ __global__ void layernorm_kernel(RowView x, const char *gamma, long long gcs, co
 // Dense rows of d floats (d % 4 == 0), one warp per row, float4 traffic.
 __global__ void layernorm_dense_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
                                        const float *__restrict__ beta, long long rows, int d,
-                                       float *__restrict__ out, float *__restrict__ out_lo) {
+                                       float *__restrict__ out, float *__restrict__ out_lo,
+                                       const LoopState *state, int n_streams) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (state) rows = (long long)n_streams * state->s;  // launch sized for an upper bound
   const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -155,12 +159,13 @@ void launch_layernorm(const RowView &x, const float *gamma, long long gamma_cs, 
 }
 
 void launch_layernorm_dense(const float *x, const float *gamma, const float *beta, long long rows,
-                            int d, float *out, float *out_lo, cudaStream_t st) {
+                            int d, float *out, float *out_lo, const LoopState *state, int n_streams,
+                            cudaStream_t st) {
   if (rows <= 0) return;
   const int warps = 4;
   const long long blocks = (rows + warps - 1) / warps;
-  layernorm_dense_kernel<<<(unsigned)blocks, warps * 32, 0, st>>>(x, gamma, beta, rows, d, out, out_lo);
-  LB_LAUNCH_CHECK();
+  launch_pdl(layernorm_dense_kernel, dim3((unsigned)blocks), dim3(warps * 32), 0, st, g_pdl_enabled, x, gamma, beta, rows,
+             d, out, out_lo, state, n_streams);
 }
 
 void launch_softmax_rows(const RowView &x, const RowView &out, int causal, float scale,

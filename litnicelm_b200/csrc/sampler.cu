@@ -179,6 +179,8 @@ sampler_kernel(const float *__restrict__ logits, int vocab, SamplerParams sp,
   __shared__ int s_idx[32];
   __shared__ unsigned long long s_prefix;
   __shared__ int s_count, s_keep, s_token;
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int row = blockIdx.x;
   const float *lr = logits + (long long)row * vocab;
@@ -361,9 +363,8 @@ static void run_sampler(const float *logits, int vocab, int n_rows, const Sample
     sk = static_cast<unsigned long long *>(scratch);
     sw = reinterpret_cast<double *>(sk + (size_t)n_rows * p2);
   }
-  sampler_kernel<<<n_rows, SM_THREADS, 0, st>>>(logits, vocab, sp, mt_state, draws, ids, ids_ld,
-                                                 out, out_ld, state, sk, sw, p2);
-  LB_LAUNCH_CHECK();
+  launch_pdl(sampler_kernel, dim3(n_rows), dim3(SM_THREADS), 0, st, g_pdl_enabled, logits, vocab, sp, mt_state, draws, ids,
+             ids_ld, out, out_ld, state, sk, sw, p2);
 }
 
 void launch_sampler(const float *logits, int vocab, int n_streams, const SamplerParams &sp,

@@ -124,6 +124,17 @@ struct litnice_b200_session {
   float *xl = nullptr, *logits = nullptr, *gemv_scratch = nullptr;
   // tensor-core path: low parts of the split activations (ln/ctx/h/xl hold the high parts)
   bool tc = false;
+  bool pdl = false;        // early launch of dependent kernels (LITNICE_B200_PDL=1 enables)
+  bool use_graphs = true;  // replay one captured step per 64-token context bucket (LITNICE_B200_GRAPHS=0 disables)
+  struct StepGraph {
+    cudaGraphExec_t exec = nullptr;
+    int streams = 0;
+    SamplerParams sp{};
+    unsigned long long generation = 0;
+  };
+  std::vector<StepGraph> graphs;       // indexed by context bucket (tiles of 64)
+  unsigned long long generation = 1;   // bumped whenever a buffer a graph points at is replaced
+  long long graph_launches_per_step = 0;
   float *ln_lo = nullptr, *ctx_lo = nullptr, *h_lo = nullptr, *xl_lo = nullptr;
   long long xl_rows = 0;
   std::vector<std::array<TcWeight, 4>> tcw;  // per layer: qkv, out, w1, w2
@@ -209,6 +220,7 @@ void ensure_rows(litnice_b200_session *s, long long rows) {
     make_activation_map(&s->a_map[A_H], s->h, s->h_lo, rows, (int)F);
   }
   s->cap_rows = rows;
+  ++s->generation;
 }
 
 // Scratch of the attention kernel's key-split mode for contexts s_lo..s_hi.
@@ -227,6 +239,7 @@ void ensure_attention_scratch(litnice_b200_session *s, int B, int s_lo, int s_hi
     s->attn_scratch_floats = 0;
     if (cudaMalloc(reinterpret_cast<void **>(&s->attn_scratch), need_f * 4) != cudaSuccess) throw std::bad_alloc();
     s->attn_scratch_floats = need_f;
+    ++s->generation;
   }
   if (need_c > s->attn_counter_count) {
     LB_CUDA(cudaStreamSynchronize(s->st));
@@ -236,6 +249,7 @@ void ensure_attention_scratch(litnice_b200_session *s, int B, int s_lo, int s_hi
     if (cudaMalloc(reinterpret_cast<void **>(&s->attn_counters), need_c * 4) != cudaSuccess) throw std::bad_alloc();
     LB_CUDA(cudaMemsetAsync(s->attn_counters, 0, need_c * 4, s->st));  // kernels leave them at zero
     s->attn_counter_count = need_c;
+    ++s->generation;
   }
 }
 
@@ -297,28 +311,30 @@ void projection(litnice_b200_session *s, AKind ak, long long rows, int k, const 
 // Transformer::forward over all rows up to the last layer's output
 // (transformer.cpp:70-114, transformer_layer.cpp:50-92); leaves the final
 // hidden state in s->x.
-void enqueue_body(litnice_b200_session *s, int B, int sl) {
+void enqueue_body(litnice_b200_session *s, int B, int sl, const LoopState *dstate = nullptr) {
   const litnice_b200_dims &d = s->dims;
   const long long R = (long long)B * sl;
   const int D = d.d_model, F = d.d_ff;
-  launch_embed_pos(P(s, s->lay.tok_emb), P(s, s->lay.pos_emb), s->ids, d.max_seq_len, nullptr, B, sl, D,
+  launch_embed_pos(P(s, s->lay.tok_emb), P(s, s->lay.pos_emb), s->ids, d.max_seq_len, dstate, B, sl, D,
                    d.vocab_size, s->x, s->err_dev, s->st);
   ++s->launches;
   for (int l = 0; l < d.n_layers; ++l) {
     const LayerOff &o = s->lay.layer[l];
     const std::array<TcWeight, 4> *tw = s->tc ? &s->tcw[l] : nullptr;
-    launch_layernorm_dense(s->x, P(s, o.ln1_g), P(s, o.ln1_b), R, D, s->ln, s->tc ? s->ln_lo : nullptr, s->st);
+    launch_layernorm_dense(s->x, P(s, o.ln1_g), P(s, o.ln1_b), R, D, s->ln, s->tc ? s->ln_lo : nullptr, dstate, B,
+                           s->st);
     ++s->launches;
     projection(s, A_LN, R, D, P(s, o.qkv_w), tw ? &(*tw)[0] : nullptr, 3 * D, P(s, o.qkv_b), nullptr, 0, s->qkv,
                nullptr);
     {
       ClassTimer t(s, &s->attn_ev);
       launch_attention(s->qkv, s->ctx, s->tc ? s->ctx_lo : nullptr, B, sl, d.n_heads, D, s->attn_scratch,
-                       s->attn_counters, s->st);
+                       s->attn_counters, dstate, s->st);
       ++s->launches;
     }
     projection(s, A_CTX, R, D, P(s, o.out_w), tw ? &(*tw)[1] : nullptr, D, P(s, o.out_b), s->x, 0, s->y, nullptr);
-    launch_layernorm_dense(s->y, P(s, o.ln2_g), P(s, o.ln2_b), R, D, s->ln, s->tc ? s->ln_lo : nullptr, s->st);
+    launch_layernorm_dense(s->y, P(s, o.ln2_g), P(s, o.ln2_b), R, D, s->ln, s->tc ? s->ln_lo : nullptr, dstate, B,
+                           s->st);
     ++s->launches;
     projection(s, A_LN, R, D, P(s, o.w1), tw ? &(*tw)[2] : nullptr, F, P(s, o.b1), nullptr, 1, s->h,
                s->tc ? s->h_lo : nullptr);
@@ -328,10 +344,10 @@ void enqueue_body(litnice_b200_session *s, int B, int sl) {
 
 // LN_f + output head on the last row of each stream (output_head.cpp:58-70
 // restricted to the row the loop reads).
-void enqueue_head_last(litnice_b200_session *s, int B, int sl) {
+void enqueue_head_last(litnice_b200_session *s, int B, int sl, const LoopState *dstate = nullptr) {
   const litnice_b200_dims &d = s->dims;
   const bool head_tc = s->tc && B > 8 && s->tc_head.usable();
-  launch_gather_last_ln(s->x, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), nullptr, B, sl, d.d_model, s->xl,
+  launch_gather_last_ln(s->x, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), dstate, B, sl, d.d_model, s->xl,
                         head_tc ? s->xl_lo : nullptr, s->st);
   ++s->launches;
   if (B <= 8) {
@@ -475,6 +491,10 @@ int litnice_b200_session_create(const litnice_b200_dims *dims, int32_t max_strea
     must(cudaMalloc(reinterpret_cast<void **>(&s->params), s->lay.total));
     // Tensor-core projections need k % 32 == 0 and n % 64 == 0 for all four
     // layer matrices; LITNICE_B200_TC=0 forces the fp32 SIMT kernels.
+    const char *pdl_env = std::getenv("LITNICE_B200_PDL");
+    s->pdl = pdl_env && pdl_env[0] == '1';
+    const char *graph_env = std::getenv("LITNICE_B200_GRAPHS");
+    s->use_graphs = !(graph_env && graph_env[0] == '0');
     const char *tc_env = std::getenv("LITNICE_B200_TC");
     s->tc = !(tc_env && tc_env[0] == '0') && tc_runtime_available() && d.d_model % 64 == 0 && d.d_ff % 64 == 0;
     size_t lr = (size_t)(max_streams < 8 ? 8 : max_streams);
@@ -514,6 +534,8 @@ void litnice_b200_session_destroy(litnice_b200_session *s) {
                   (void *)s->logits_all, (void *)s->ids, (void *)s->out_tokens, (void *)s->mt, (void *)s->state,
                   s->sampler_scratch, (void *)s->step_logits})
     if (p) cudaFree(p);
+  for (auto &g : s->graphs)
+    if (g.exec) cudaGraphExecDestroy(g.exec);
   if (s->xl_lo) cudaFree(s->xl_lo);
   if (s->tc_scratch) cudaFree(s->tc_scratch);
   if (s->tc_counters) cudaFree(s->tc_counters);
@@ -622,6 +644,7 @@ int litnice_b200_upload_prompts(litnice_b200_session *s, const int32_t *prompts,
 int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b200_sampling *sampling,
                      int32_t *out_count) {
   return guarded(s, [&]() {
+    PdlScope pdl_scope(s->pdl);
     if (s->cur_streams <= 0) throw std::invalid_argument("no prompts uploaded");
     if (max_new < 0 || sampling == nullptr) throw std::invalid_argument("bad run arguments");
     if (!(sampling->temp <= 0.0f || sampling->top_k == 1u) &&
@@ -633,8 +656,10 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
     int steps = s->dims.max_seq_len - s0;
     if (steps > max_new) steps = max_new;
     if (steps < 0) steps = 0;
-    ensure_rows(s, (long long)B * (s0 + (steps > 0 ? steps - 1 : 0)));
-    if (steps > 0) ensure_attention_scratch(s, B, s0, s0 + steps - 1);
+    const int s_last = s0 + (steps > 0 ? steps - 1 : 0);
+    const int s_last_cap = (s_last + 63) / 64 * 64;  // graph replay sizes launches per 64-token bucket
+    ensure_rows(s, (long long)B * s_last_cap);
+    if (steps > 0) ensure_attention_scratch(s, B, s0, s_last_cap);
     if (s->out_cap < s->cur_tokens + steps || s->out_tokens == nullptr) {
       LB_CUDA(cudaStreamSynchronize(s->st));
       int *n = nullptr;
@@ -648,6 +673,7 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
         cudaFree(s->out_tokens);
       }
       s->out_tokens = n;
+      ++s->generation;
       s->out_cap = cap;
     }
     SamplerParams sp{sampling->temp, sampling->top_k, sampling->top_p};
@@ -660,6 +686,7 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
         s->sampler_scratch = nullptr;
         if (cudaMalloc(&s->sampler_scratch, need) != cudaSuccess) throw std::bad_alloc();
         s->sampler_scratch_bytes_ = need;
+        ++s->generation;
       }
     }
     if (s->keep_logits) {
@@ -675,11 +702,15 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
     }
 
     const long long launches0 = s->launches;
-    LB_CUDA(cudaEventRecord(s->ev0, s->st));
-    for (int step = 0; step < steps; ++step) {
-      const int sl = s0 + step;
-      enqueue_body(s, B, sl);
-      enqueue_head_last(s, B, sl);
+    // One step = whole-context forward + head + selector + state advance. With
+    // graph replay the step of a 64-token context bucket is captured once (its
+    // launches sized for the bucket's upper bound, the actual length read from
+    // the device-side LoopState) and replayed for every step in the bucket, so
+    // the host issues one launch per token instead of ~50.
+    const bool graphs = s->use_graphs && !s->keep_logits;
+    auto enqueue_step = [&](int sl_cap, const LoopState *dstate, int step) {
+      enqueue_body(s, B, sl_cap, dstate);
+      enqueue_head_last(s, B, sl_cap, dstate);
       if (s->keep_logits) {
         LB_CUDA(cudaMemcpyAsync(s->step_logits + (long long)(s->cur_tokens + step) * B * V, s->logits,
                                 (size_t)B * V * 4, cudaMemcpyDeviceToDevice, s->st));
@@ -688,6 +719,46 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
                      s->state, s->sampler_scratch, s->st);
       launch_advance_state(s->state, s->st);
       s->launches += 2;
+    };
+    LB_CUDA(cudaEventRecord(s->ev0, s->st));
+    for (int step = 0; step < steps; ++step) {
+      const int sl = s0 + step;
+      if (!graphs) {
+        enqueue_step(sl, nullptr, step);
+        continue;
+      }
+      const int bucket = (sl + 63) / 64;
+      if ((int)s->graphs.size() <= bucket) s->graphs.resize(bucket + 1);
+      litnice_b200_session::StepGraph &g = s->graphs[bucket];
+      const bool valid = g.exec != nullptr && g.streams == B && g.generation == s->generation &&
+                         g.sp.temp == sp.temp && g.sp.top_k == sp.top_k && g.sp.top_p == sp.top_p;
+      if (!valid) {
+        if (g.exec) {
+          cudaGraphExecDestroy(g.exec);
+          g.exec = nullptr;
+        }
+        const long long before = s->launches;
+        cudaGraph_t graph = nullptr;
+        LB_CUDA(cudaStreamBeginCapture(s->st, cudaStreamCaptureModeRelaxed));
+        try {
+          enqueue_step(bucket * 64, s->state, step);
+        } catch (...) {
+          cudaStreamEndCapture(s->st, &graph);
+          if (graph) cudaGraphDestroy(graph);
+          throw;
+        }
+        LB_CUDA(cudaStreamEndCapture(s->st, &graph));
+        const cudaError_t ie = cudaGraphInstantiate(&g.exec, graph, 0);
+        cudaGraphDestroy(graph);
+        LB_CUDA(ie);
+        g.streams = B;
+        g.sp = sp;
+        g.generation = s->generation;
+        s->graph_launches_per_step = s->launches - before;
+        s->launches = before;  // capturing enqueued nothing
+      }
+      LB_CUDA(cudaGraphLaunch(g.exec, s->st));
+      s->launches += s->graph_launches_per_step;
     }
     LB_CUDA(cudaEventRecord(s->ev1, s->st));
     LB_CUDA(cudaStreamSynchronize(s->st));
@@ -751,6 +822,7 @@ int litnice_b200_forward(litnice_b200_session *s, const int32_t *ids, int32_t n_
     if (ids == nullptr || out_logits == nullptr || n_streams <= 0 || n_streams > s->max_streams || seq_len <= 0 ||
         seq_len > s->dims.max_seq_len)
       throw std::invalid_argument("bad forward shape");
+    PdlScope pdl_scope(s->pdl);
     const int B = n_streams, V = s->dims.vocab_size, D = s->dims.d_model;
     const long long R = (long long)B * seq_len;
     s->stats = litnice_b200_stats{};
@@ -773,7 +845,7 @@ int litnice_b200_forward(litnice_b200_session *s, const int32_t *ids, int32_t n_
       // OutputHead::forward over every row (output_head.cpp:58-70)
       const bool head_tc = s->tc && s->tc_head.usable();
       launch_layernorm_dense(s->x, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), R, D, s->ln,
-                             head_tc ? s->ln_lo : nullptr, s->st);
+                             head_tc ? s->ln_lo : nullptr, nullptr, B, s->st);
       ++s->launches;
       projection(s, A_LN, R, D, P(s, s->lay.lm_head), head_tc ? &s->tc_head : nullptr, V, nullptr, nullptr, 0,
                  s->logits_all, nullptr);
@@ -803,6 +875,7 @@ int litnice_b200_inspect(litnice_b200_session *s, const int32_t *ids, int32_t n_
     if (ids == nullptr || probs == nullptr || n_streams <= 0 || n_streams > s->max_streams || seq_len <= 0 ||
         seq_len > s->dims.max_seq_len)
       throw std::invalid_argument("bad inspect shape");
+    PdlScope pdl_scope(s->pdl);
     const int B = n_streams, V = s->dims.vocab_size;
     s->stats = litnice_b200_stats{};
     ensure_rows(s, (long long)B * seq_len);
@@ -882,6 +955,7 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
     if (n_streams <= 0 || n_streams > s->max_streams || seq_len <= 0 || seq_len > s->dims.max_seq_len ||
         repeats <= 0)
       throw std::invalid_argument("bad profile_step shape");
+    PdlScope pdl_scope(s->pdl);
     ensure_rows(s, (long long)n_streams * seq_len);
     ensure_attention_scratch(s, n_streams, seq_len, seq_len);
     s->gemm_ev.clear();
@@ -924,8 +998,24 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
   });
 }
 
+static int projection_impl(int32_t engine, const float *a, int32_t m, int32_t k, const float *w, int32_t n,
+                           const float *bias, const float *residual, int32_t relu, float *c, int32_t repeats,
+                           double *avg_us);
+
 int litnice_b200_projection_host(int32_t engine, const float *a, int32_t m, int32_t k, const float *w, int32_t n,
                                  const float *bias, const float *residual, int32_t relu, float *c) {
+  return projection_impl(engine, a, m, k, w, n, bias, residual, relu, c, 1, nullptr);
+}
+
+int litnice_b200_projection_time(int32_t engine, const float *a, int32_t m, int32_t k, const float *w, int32_t n,
+                                 float *c, int32_t repeats, double *avg_us) {
+  if (repeats <= 0 || avg_us == nullptr) return LITNICE_B200_EINVAL;
+  return projection_impl(engine, a, m, k, w, n, nullptr, nullptr, 0, c, repeats, avg_us);
+}
+
+static int projection_impl(int32_t engine, const float *a, int32_t m, int32_t k, const float *w, int32_t n,
+                           const float *bias, const float *residual, int32_t relu, float *c, int32_t repeats,
+                           double *avg_us) {
   if (a == nullptr || w == nullptr || c == nullptr || m <= 0 || k <= 0 || n <= 0 || (engine != 0 && engine != 1)) {
     std::fprintf(stderr, "litnice_b200_projection_host: bad argument\n");
     return LITNICE_B200_EINVAL;
@@ -964,7 +1054,20 @@ int litnice_b200_projection_host(int32_t engine, const float *a, int32_t m, int3
       ep.bias = db;
       ep.residual = dr;
       ep.relu = relu;
+      cudaEvent_t e0, e1;
+      LB_CUDA(cudaEventCreate(&e0));
+      LB_CUDA(cudaEventCreate(&e1));
       launch_gemm_simt(dense(da, m, k), dense(dw, k, n), dense(dc, m, n), m, n, k, ep, st);
+      LB_CUDA(cudaEventRecord(e0, st));
+      for (int r = 1; r < repeats; ++r)
+        launch_gemm_simt(dense(da, m, k), dense(dw, k, n), dense(dc, m, n), m, n, k, ep, st);
+      LB_CUDA(cudaEventRecord(e1, st));
+      LB_CUDA(cudaStreamSynchronize(st));
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, e0, e1);
+      if (avg_us && repeats > 1) *avg_us = 1e3 * ms / (repeats - 1);
+      cudaEventDestroy(e0);
+      cudaEventDestroy(e1);
     } else {
       float *a_hi = dev_alloc((size_t)mp * k * 4), *a_lo = dev_alloc((size_t)mp * k * 4);
       float *w_hi = dev_alloc((size_t)k * n * 4), *w_lo = dev_alloc((size_t)k * n * 4);
@@ -988,7 +1091,34 @@ int litnice_b200_projection_host(int32_t engine, const float *a, int32_t m, int3
       ep.residual = dr;
       ep.relu = relu;
       ep.c = dc;
+      const bool want_timeline = std::getenv("LITNICE_B200_TC_TIMELINE") != nullptr;
+      if (want_timeline) {
+        ep.timeline = reinterpret_cast<unsigned long long *>(dev_alloc(8 * 8));
+        LB_CUDA(cudaMemsetAsync(ep.timeline, 0, 64, st));
+      }
+      cudaEvent_t e0, e1;
+      LB_CUDA(cudaEventCreate(&e0));
+      LB_CUDA(cudaEventCreate(&e1));
       launch_gemm_tc(ma, mb, m, n, k, plan, ep, scr, cnt, err_dev, st);
+      LB_CUDA(cudaEventRecord(e0, st));
+      for (int r = 1; r < repeats; ++r) launch_gemm_tc(ma, mb, m, n, k, plan, ep, scr, cnt, err_dev, st);
+      LB_CUDA(cudaEventRecord(e1, st));
+      LB_CUDA(cudaStreamSynchronize(st));
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, e0, e1);
+      if (avg_us && repeats > 1) *avg_us = 1e3 * ms / (repeats - 1);
+      cudaEventDestroy(e0);
+      cudaEventDestroy(e1);
+      if (want_timeline) {
+        unsigned long long t[8];
+        LB_CUDA(cudaMemcpy(t, ep.timeline, 64, cudaMemcpyDeviceToHost));
+        std::fprintf(stderr,
+                     "tc timeline (ns from start): setup %lld, loads issued %lld, first stage full %lld, mma issued %lld, "
+                     "chunks drained %lld, stored %lld, end %lld\n",
+                     (long long)(t[1] - t[0]), (long long)(t[2] - t[0]), (long long)(t[3] - t[0]),
+                     (long long)(t[4] - t[0]), (long long)(t[5] - t[0]), (long long)(t[6] - t[0]),
+                     (long long)(t[7] - t[0]));
+      }
     }
     LB_CUDA(cudaMemcpyAsync(c, dc, (size_t)m * n * 4, cudaMemcpyDeviceToHost, st));
     LB_CUDA(cudaStreamSynchronize(st));

@@ -4,6 +4,8 @@
 
 namespace lb {
 
+thread_local bool g_pdl_enabled = false;
+
 static void check_view(const BackendTensorView *t, const char *who) {
   if (t == nullptr) throw std::invalid_argument(std::string(who) + ": null tensor view");
   if (t->rank == 0 || t->rank > LITNICE_TENSOR_MAX_RANK)
