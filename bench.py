@@ -57,6 +57,11 @@ def reference_flops(d: formats.ModelDims, s: int) -> float:
     return 2.0 * s * L * (4 * D * D + 2 * D * F) + 4.0 * L * s * s * D + 2.0 * s * D * V
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per projection launch from the ncu
+# capture summarised under profiles/ (mean over the four projections of a layer).
+NCU_DRAM_BYTES_PER_GEMM_LAUNCH = {"c2": 11.6e6}
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -309,10 +314,13 @@ def run_b200_arm(args, rank, local_rank, world):
         prof = sess.profile_step(streams, s_mid, 3)
         gemm_tflops = prof.gemm_flops / (prof.gemm_ms * 1e-3) / 1e12 if prof.gemm_ms > 0 else 0.0
         roofline = {
-            "bound": "tensor", "kernel": "projection GEMM (gemm_simt_kernel)",
+            "bound": "tensor", "kernel": "projection GEMM (gemm_tc_kernel: tcgen05 + TMEM, 3xTF32 split)",
             "achieved": gemm_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
             "frac": gemm_tflops / peaks["bf16_tflops"], "peak_source": f"bf16 burst, {peaks['source']}",
-            "traffic": None,
+            # fp32-accurate products execute 3 TF32 MMAs per algorithmic flop and TF32 runs at
+            # half the bf16 rate, so algorithmic flops cannot exceed 1/6 of the bf16 peak
+            "ceiling_frac_3xtf32": 1.0 / 6.0,
+            "traffic": NCU_DRAM_BYTES_PER_GEMM_LAUNCH.get(args.workload),
             "note": (f"algorithmic 2*M*N*K flops of {prof.gemm_launches} launches at context {s_mid} / "
                      f"{prof.gemm_ms:.3f} ms (CUDA events around each launch on the session stream); "
                      f"attention: {prof.attn_launches} launches, {prof.attn_ms:.3f} ms"),

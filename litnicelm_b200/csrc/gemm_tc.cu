@@ -24,7 +24,8 @@ namespace lb {
 
 namespace {
 
-constexpr int TC_THREADS = 192;
+// 2 role warps (TMA, MMA) + 4 drain warps per 128 accumulator columns.
+__host__ __device__ constexpr int tc_threads(int bn) { return 64 + 128 * (bn > 128 ? bn / 128 : 1); }
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
 
 // ---- PTX helpers ---------------------------------------------------------------
@@ -154,7 +155,7 @@ __device__ __forceinline__ void mbar_arrive(unsigned bar) {
 }
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(tc_threads(BN), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                TcEpilogue ep, int m, int n, int k, int splits, float *__restrict__ part,
@@ -195,7 +196,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     }
     for (int b = 0; b < NBUF; ++b) {
       mbar_init(tmem_full_bar(b), 1);
-      mbar_init(tmem_empty_bar(b), 4);  // one arrival per epilogue warp
+      mbar_init(tmem_empty_bar(b), (tc_threads(BN) - 64) / 32);  // one arrival per drain warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -331,11 +332,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   } else if (warp >= 2) {
     // ---- epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 ----
     pdl_wait();  // residual reads, C and scratch writes must follow the predecessor
+    // Tiles wider than 128 columns use two warps per lane quarter, each taking
+    // 128 columns, so the per-thread accumulators stay in registers.
+    constexpr int CW = BN > 128 ? 128 : BN;          // columns per drain warp
+    constexpr int DRAIN_THREADS = tc_threads(BN) - 64;
     const int q = warp & 3;
+    const int col0 = ((warp - 2) >> 2) * CW;          // first column of this warp inside the tile
     const int row = m0 + q * 32 + lane;
-    float acc[BN];
+    float acc[CW];
 #pragma unroll
-    for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+    for (int j = 0; j < CW; ++j) acc[j] = 0.f;
     bool ok = true;
     for (int c = 0; c < nchunks && ok; ++c) {
       const int buf = c % NBUF;
@@ -344,9 +350,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < CW; c0 += 32) {
         unsigned r[32];
-        tc_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN + c0), r);
+        __syncwarp();
+        tc_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN + col0 + c0), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[c0 + j] = __fadd_rn(acc[c0 + j], __uint_as_float(r[j]));
@@ -361,28 +368,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
       // Split-k: leave the partial tile in scratch; the CTA that arrives last at
       // the tile's counter adds all partials in split order and stores C.
       const long long tile = (long long)blockIdx.y * gridDim.x + blockIdx.x;
-      float *mine = part + ((tile * splits + blockIdx.z) * TC_BM + (q * 32 + lane)) * BN;
+      float *mine = part + ((tile * splits + blockIdx.z) * TC_BM + (q * 32 + lane)) * BN + col0;
 #pragma unroll
-      for (int j = 0; j < BN; j += 4)
+      for (int j = 0; j < CW; j += 4)
         *reinterpret_cast<float4 *>(mine + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
       __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
       if (warp == 2 && lane == 0) {
         const int prev = atomicAdd(counters + tile, 1);
         const int last = (prev == splits - 1) ? 1 : 0;
         if (last) counters[tile] = 0;  // ready for the next launch
         *last_flag = last;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
       finish = finish && (*last_flag != 0);
       if (finish) {
         __threadfence();
 #pragma unroll
-        for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+        for (int j = 0; j < CW; ++j) acc[j] = 0.f;
         for (int z = 0; z < splits; ++z) {
-          const float *pz = part + ((tile * splits + z) * TC_BM + (q * 32 + lane)) * BN;
+          const float *pz = part + ((tile * splits + z) * TC_BM + (q * 32 + lane)) * BN + col0;
 #pragma unroll
-          for (int j = 0; j < BN; j += 4) {
+          for (int j = 0; j < CW; j += 4) {
             const float4 t = __ldcg(reinterpret_cast<const float4 *>(pz + j));
             acc[j] += t.x; acc[j + 1] += t.y; acc[j + 2] += t.z; acc[j + 3] += t.w;
           }
@@ -390,12 +397,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
       }
     }
     if (finish && row < m) {
-      const long long off = (long long)row * n + n0;
+      const long long off = (long long)row * n + n0 + col0;
 #pragma unroll
-      for (int j = 0; j < BN; j += 4) {
+      for (int j = 0; j < CW; j += 4) {
         float v[4] = {acc[j], acc[j + 1], acc[j + 2], acc[j + 3]};
         if (ep.bias) {
-          const float4 b = *reinterpret_cast<const float4 *>(ep.bias + n0 + j);
+          const float4 b = *reinterpret_cast<const float4 *>(ep.bias + n0 + col0 + j);
           v[0] += b.x; v[1] += b.y; v[2] += b.z; v[3] += b.w;
         }
         if (ep.residual) {
@@ -495,7 +502,7 @@ void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const
     configured[dev] = true;
   }
   dim3 grid(n / BN, (m + TC_BM - 1) / TC_BM, splits);
-  launch_pdl(gemm_tc_kernel<BN, STAGES>, grid, dim3(TC_THREADS), (size_t)L::TOTAL, st, g_pdl_enabled, a.hi, a.lo, b.hi,
+  launch_pdl(gemm_tc_kernel<BN, STAGES>, grid, dim3(tc_threads(BN)), (size_t)L::TOTAL, st, g_pdl_enabled, a.hi, a.lo, b.hi,
              b.lo, ep, m, n, k, splits, part, counters, err);
 }
 
@@ -520,11 +527,15 @@ void tc_make_map(CUtensorMap *map, const float *base, unsigned long long rows, u
     throw std::runtime_error("litnice_b200: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
 }
 
-TcPlan tc_plan(int m, int n, int k, bool has64, bool has128) {
+TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256) {
   TcPlan p{};
   const long long mt = (m + TC_BM - 1) / TC_BM;
-  // Wide tiles when they still give one full wave; narrow tiles otherwise.
+  // One thread issues every tcgen05.mma of a CTA, at most one per ~40 ns, and a
+  // TF32 instruction covers only 8 of k: the widest tile that still fills the
+  // GPU keeps the tensor pipe busy per issue slot; narrow tiles serve short
+  // single-stream shapes.
   p.bn = (has128 && (!has64 || mt * (n / 128) >= 74)) ? 128 : 64;
+  if (has256 && mt * (n / 256) >= 2 * 148) p.bn = 256;
   const long long ctas = mt * (n / p.bn);
   const int kb = k / TC_BK;
   // Few tiles (a short single stream): cut k over several CTAs per tile so the
@@ -547,11 +558,12 @@ void launch_gemm_tc(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, c
                     const TcEpilogue &ep, float *scratch, int *counters, DevErr *err, cudaStream_t st) {
   if (m <= 0) return;
   const int bn = plan.bn;
-  if (k < TC_BK || k % TC_BK != 0 || (bn != 64 && bn != 128) || n % bn != 0)
+  if (k < TC_BK || k % TC_BK != 0 || (bn != 64 && bn != 128 && bn != 256) || n % bn != 0)
     throw std::invalid_argument("litnice_b200: tensor-core GEMM needs k % 32 == 0 and n % bn == 0");
   if (plan.splits > 1 && (scratch == nullptr || counters == nullptr))
     throw std::invalid_argument("litnice_b200: split-k tensor-core GEMM needs scratch");
-  if (bn == 128) launch_cfg<128, 3>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st);
+  if (bn == 256) launch_cfg<256, 2>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st);
+  else if (bn == 128) launch_cfg<128, 3>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st);
   else launch_cfg<64, 4>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st);
 }
 

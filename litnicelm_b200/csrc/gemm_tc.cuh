@@ -42,7 +42,7 @@ bool tc_runtime_available();
 void tc_make_map(CUtensorMap *map, const float *base, unsigned long long rows, unsigned long long k,
                  unsigned box_rows);
 
-// How one product is tiled: tile width (64 or 128 columns), how many CTAs share
+// How one product is tiled: tile width (64, 128 or 256 columns), how many CTAs share
 // the k range of a tile, and the scratch that sharing needs (floats of partial
 // tiles; int counters that must be zero before the first launch and are left
 // at zero by every launch).
@@ -52,7 +52,7 @@ struct TcPlan {
   size_t scratch_floats;
   size_t counters;
 };
-TcPlan tc_plan(int m, int n, int k, bool has64, bool has128);
+TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256);
 
 // Requires n % plan.bn == 0, k % 32 == 0; a maps must use box rows 128, b maps
 // box rows plan.bn.

@@ -98,8 +98,8 @@ MatView dense(const float *p, long long rows, long long cols) {
 struct TcWeight {
   float *hi = nullptr, *lo = nullptr;
   int k = 0, n = 0;
-  bool has64 = false, has128 = false;
-  TcMatrix m64{}, m128{};
+  bool has64 = false, has128 = false, has256 = false;
+  TcMatrix m64{}, m128{}, m256{};
   bool usable() const { return has64 || has128; }
 };
 
@@ -295,8 +295,8 @@ void projection(litnice_b200_session *s, AKind ak, long long rows, int k, const 
     } else {
       ep.c = c;
     }
-    const TcPlan plan = tc_plan((int)rows, n, k, tw->has64, tw->has128);
-    launch_gemm_tc(s->a_map[ak], plan.bn == 128 ? tw->m128 : tw->m64, (int)rows, n, k, plan, ep, s->tc_scratch,
+    const TcPlan plan = tc_plan((int)rows, n, k, tw->has64, tw->has128, tw->has256);
+    launch_gemm_tc(s->a_map[ak], plan.bn == 256 ? tw->m256 : plan.bn == 128 ? tw->m128 : tw->m64, (int)rows, n, k, plan, ep, s->tc_scratch,
                    s->tc_counters, s->err_dev, s->st);
     return;
   }
@@ -367,6 +367,7 @@ void prepare_one(litnice_b200_session *s, TcWeight *tw, const float *w, int k, i
   tw->n = n;
   tw->has64 = (k % TC_BK == 0) && (n % 64 == 0);
   tw->has128 = (k % TC_BK == 0) && (n % 128 == 0);
+  tw->has256 = (k % TC_BK == 0) && (n % 256 == 0);
   if (!tw->usable()) return;
   const size_t bytes = (size_t)k * n * 4;
   if (tw->hi == nullptr) {
@@ -381,6 +382,10 @@ void prepare_one(litnice_b200_session *s, TcWeight *tw, const float *w, int k, i
   if (tw->has128) {
     tc_make_map(&tw->m128.hi, tw->hi, (unsigned long long)n, (unsigned long long)k, 128);
     tc_make_map(&tw->m128.lo, tw->lo, (unsigned long long)n, (unsigned long long)k, 128);
+  }
+  if (tw->has256) {
+    tc_make_map(&tw->m256.hi, tw->hi, (unsigned long long)n, (unsigned long long)k, 256);
+    tc_make_map(&tw->m256.lo, tw->lo, (unsigned long long)n, (unsigned long long)k, 256);
   }
 }
 
@@ -1073,7 +1078,7 @@ static int projection_impl(int32_t engine, const float *a, int32_t m, int32_t k,
       float *w_hi = dev_alloc((size_t)k * n * 4), *w_lo = dev_alloc((size_t)k * n * 4);
       launch_split_tf32(da, a_hi, a_lo, mp * k, st);
       launch_transpose_split(dw, k, n, w_hi, w_lo, st);
-      const TcPlan plan = tc_plan(m, n, k, n % 64 == 0, n % 128 == 0);
+      const TcPlan plan = tc_plan(m, n, k, n % 64 == 0, n % 128 == 0, n % 256 == 0);
       const int bn = plan.bn;
       float *scr = plan.scratch_floats ? dev_alloc(plan.scratch_floats * 4) : nullptr;
       int *cnt = nullptr;

@@ -36,7 +36,9 @@ def project():
 
 
 SHAPES = [(128, 32, 64), (128, 64, 128), (1, 64, 64), (129, 96, 192), (640, 512, 1536), (300, 2048, 512),
-          (1000, 512, 2048), (4096, 256, 1024)]
+          (1000, 512, 2048), (4096, 256, 1024),
+          # enough row tiles for the 256-column configuration
+          (9600, 128, 1024), (19100, 96, 512)]
 
 
 @pytest.mark.parametrize("m,k,n", SHAPES)
