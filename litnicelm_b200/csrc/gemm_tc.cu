@@ -16,6 +16,7 @@
 // sets the error word, lets the pipeline drain and the kernel returns after
 // freeing its tensor memory. No cluster launch and no multicast is used.
 #include "gemm_tc.cuh"
+#include "tc_ptx.cuh"
 
 #include <cstdlib>
 #include <mutex>
@@ -26,104 +27,6 @@ namespace {
 
 // 2 role warps (TMA, MMA) + 4 drain warps per 128 accumulator columns.
 __host__ __device__ constexpr int tc_threads(int bn) { return 64 + 128 * (bn > 128 ? bn / 128 : 1); }
-constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
-
-// ---- PTX helpers ---------------------------------------------------------------
-
-__device__ __forceinline__ unsigned smem_u32(const void *p) {
-  return static_cast<unsigned>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ unsigned long long global_timer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)::"memory");
-  return t;
-}
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ unsigned mbar_try_wait(unsigned bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-// Bounded wait: false (and the error word set) if the phase does not complete
-// within WAIT_LIMIT_NS or another role has already given up.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, DevErr *err,
-                                          int where) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_timer();
-  unsigned spins = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (global_timer() - t0 > WAIT_LIMIT_NS) {
-        *abort_flag = 1;
-        err->code = DEVERR_WAIT_TIMEOUT;
-        err->detail = where;
-        return false;
-      }
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *map, int x, int y, unsigned bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tc_mma_tf32(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
-                                            unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tc_commit(unsigned bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
-// (32 fp32) stored with the 128-byte swizzle: groups of 8 rows are 1024 bytes
-// apart (stride byte offset), the leading byte offset is unused for this layout,
-// descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ unsigned long long umma_desc_k128(unsigned smem_addr) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
-  d |= 1ull << 16;
-  d |= (unsigned long long)(1024 >> 4) << 32;
-  d |= 1ull << 46;
-  d |= 2ull << 61;
-  return d;
-}
-
-// Instruction descriptor: D fp32, A and B TF32, both K-major, M = 128, N = bn.
-__host__ __device__ constexpr unsigned umma_idesc_tf32(int bn) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
-}
-
 template <int BN, int STAGES>
 struct TcSmem {
   static constexpr int A_BYTES = TC_BM * TC_BK * 4;  // 16 KiB
@@ -150,9 +53,6 @@ struct TcSmem {
 #endif
 constexpr int TC_CHUNK = LB_TC_CHUNK;  // k-blocks (of 32) per TMEM accumulation chain
 
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(tc_threads(BN), 1)
@@ -188,7 +88,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
 
   pdl_launch_dependents();
   const bool stamp = ep.timeline != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-  if (stamp && threadIdx.x == 0) ep.timeline[0] = global_timer();
+  if (ep.timeline != nullptr && threadIdx.x == 0) {
+    const unsigned long long t = global_timer();
+    atomicMin(ep.timeline + 8, t);   // earliest CTA start
+    atomicMax(ep.timeline + 10, t);  // latest CTA start
+    if (stamp) ep.timeline[0] = t;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -364,14 +269,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     }
     if (stamp && warp == 2 && lane == 0) ep.timeline[5] = global_timer();
     bool finish = ok && !*abort_flag;
+    const int rl = q * 32 + lane;  // row inside the tile
     if (splits > 1) {
       // Split-k: leave the partial tile in scratch; the CTA that arrives last at
       // the tile's counter adds all partials in split order and stores C.
+      // Partial tiles are laid out [column / 4][row][4] so that the 32 rows of a
+      // warp are contiguous (a row-major tile would cost 32 lines per access).
       const long long tile = (long long)blockIdx.y * gridDim.x + blockIdx.x;
-      float *mine = part + ((tile * splits + blockIdx.z) * TC_BM + (q * 32 + lane)) * BN + col0;
+      float4 *mine = reinterpret_cast<float4 *>(part + (tile * splits + blockIdx.z) * TC_BM * BN) +
+                     (col0 / 4) * TC_BM + rl;
 #pragma unroll
-      for (int j = 0; j < CW; j += 4)
-        *reinterpret_cast<float4 *>(mine + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      for (int j = 0; j < CW; j += 4) mine[(j / 4) * TC_BM] = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
       __threadfence();
       asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
       if (warp == 2 && lane == 0) {
@@ -386,40 +294,102 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
         __threadfence();
 #pragma unroll
         for (int j = 0; j < CW; ++j) acc[j] = 0.f;
-        for (int z = 0; z < splits; ++z) {
-          const float *pz = part + ((tile * splits + z) * TC_BM + (q * 32 + lane)) * BN + col0;
+        // Two partials per step (narrow tiles) with every load issued before the first add (the
+        // reduction is a chain of L2 round trips otherwise); added in split order.
+        constexpr int ZU = BN == 64 ? 2 : 1;  // wider tiles have no registers to spare
+        for (int z = 0; z < splits; z += ZU) {
+          const float4 *p0 = reinterpret_cast<const float4 *>(part + (tile * splits + z) * TC_BM * BN) +
+                             (col0 / 4) * TC_BM + rl;
+          const bool two = ZU == 2 && z + 1 < splits;
+          const float4 *p1 = two ? p0 + TC_BM * BN / 4 : p0;
 #pragma unroll
-          for (int j = 0; j < CW; j += 4) {
-            const float4 t = __ldcg(reinterpret_cast<const float4 *>(pz + j));
-            acc[j] += t.x; acc[j + 1] += t.y; acc[j + 2] += t.z; acc[j + 3] += t.w;
+          for (int j0 = 0; j0 < CW; j0 += 64) {
+            float4 t0[16], t1[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              t0[j] = __ldcg(p0 + (j0 / 4 + j) * TC_BM);
+              if (ZU == 2) t1[j] = __ldcg(p1 + (j0 / 4 + j) * TC_BM);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              acc[j0 + 4 * j] += t0[j].x; acc[j0 + 4 * j + 1] += t0[j].y;
+              acc[j0 + 4 * j + 2] += t0[j].z; acc[j0 + 4 * j + 3] += t0[j].w;
+              if (ZU == 2 && two) {
+                acc[j0 + 4 * j] += t1[j].x; acc[j0 + 4 * j + 1] += t1[j].y;
+                acc[j0 + 4 * j + 2] += t1[j].z; acc[j0 + 4 * j + 3] += t1[j].w;
+              }
+            }
           }
         }
       }
     }
-    if (finish && row < m) {
-      const long long off = (long long)row * n + n0 + col0;
+
+    // Stores. A thread holds CW columns of one row; written directly, every
+    // instruction of a warp would touch 32 different lines. The V^T columns of a
+    // QKV projection are the exception (lanes = consecutive positions of one
+    // column): they go out from the registers. Everything else is transposed
+    // through the pipeline's shared memory (idle by now: every load has landed
+    // and every MMA has completed) and stored row by row, where bias, residual,
+    // ReLU and the TF32 split are applied on coalesced float4s.
+    const bool vt_on = ep.vt_hi != nullptr;
+    if (finish && vt_on && row < m && n0 + col0 + CW > ep.vt_col0) {
+      const int sl = ep.state ? ep.state->s : ep.vt_s;
+      const int v_stream = row / sl, v_tok = row - v_stream * sl;
+      if (v_stream < ep.vt_streams) {
 #pragma unroll
-      for (int j = 0; j < CW; j += 4) {
-        float v[4] = {acc[j], acc[j + 1], acc[j + 2], acc[j + 3]};
+        for (int j = 0; j < CW; ++j) {
+          const int col = n0 + col0 + j;
+          if (col >= ep.vt_col0) {
+            float hh, ll;
+            split_tf32(acc[j] + (ep.bias ? ep.bias[col] : 0.f), hh, ll);
+            const long long at = ((long long)v_stream * ep.vt_rows + (col - ep.vt_col0)) * ep.vt_pitch + v_tok;
+            ep.vt_hi[at] = hh;
+            ep.vt_lo[at] = ll;
+          }
+        }
+      }
+    }
+    constexpr int LDS = BN + 4;  // staging pitch: 16-byte accesses of 8 consecutive rows hit all banks once
+    static_assert(TC_BM * LDS * 4 <= L::TILES_BYTES, "staging tile must fit in the pipeline stages");
+    float *stage = reinterpret_cast<float *>(base_ptr);
+    if (finish) {
+#pragma unroll
+      for (int j = 0; j < CW; j += 4)
+        *reinterpret_cast<float4 *>(stage + rl * LDS + col0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
+    if (finish) {
+      const int t2 = threadIdx.x - 64;
+      constexpr int PER_ROW = BN / 4;
+#pragma unroll 4
+      for (int i = 0; i < TC_BM * PER_ROW / DRAIN_THREADS; ++i) {
+        const int u = t2 + i * DRAIN_THREADS;
+        const int rr = u / PER_ROW, c4 = u % PER_ROW;
+        const int col = n0 + c4 * 4;
+        if (m0 + rr >= m || (vt_on && col >= ep.vt_col0)) continue;
+        float4 v = *reinterpret_cast<const float4 *>(stage + rr * LDS + c4 * 4);
+        const long long off = (long long)(m0 + rr) * n + col;
         if (ep.bias) {
-          const float4 b = *reinterpret_cast<const float4 *>(ep.bias + n0 + col0 + j);
-          v[0] += b.x; v[1] += b.y; v[2] += b.z; v[3] += b.w;
+          const float4 bb = *reinterpret_cast<const float4 *>(ep.bias + col);
+          v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
         }
         if (ep.residual) {
-          const float4 rr = *reinterpret_cast<const float4 *>(ep.residual + off + j);
-          v[0] += rr.x; v[1] += rr.y; v[2] += rr.z; v[3] += rr.w;
+          const float4 rs = *reinterpret_cast<const float4 *>(ep.residual + off);
+          v.x += rs.x; v.y += rs.y; v.z += rs.z; v.w += rs.w;
         }
         if (ep.relu) {
-#pragma unroll
-          for (int t = 0; t < 4; ++t) v[t] = v[t] > 0.f ? v[t] : 0.f;
+          v.x = v.x > 0.f ? v.x : 0.f; v.y = v.y > 0.f ? v.y : 0.f;
+          v.z = v.z > 0.f ? v.z : 0.f; v.w = v.w > 0.f ? v.w : 0.f;
         }
-        if (ep.c) *reinterpret_cast<float4 *>(ep.c + off + j) = make_float4(v[0], v[1], v[2], v[3]);
+        if (ep.c) *reinterpret_cast<float4 *>(ep.c + off) = v;
         if (ep.c_hi) {
-          float h[4], l[4];
-#pragma unroll
-          for (int t = 0; t < 4; ++t) split_tf32(v[t], h[t], l[t]);
-          *reinterpret_cast<float4 *>(ep.c_hi + off + j) = make_float4(h[0], h[1], h[2], h[3]);
-          *reinterpret_cast<float4 *>(ep.c_lo + off + j) = make_float4(l[0], l[1], l[2], l[3]);
+          float4 hh, ll;
+          split_tf32(v.x, hh.x, ll.x);
+          split_tf32(v.y, hh.y, ll.y);
+          split_tf32(v.z, hh.z, ll.z);
+          split_tf32(v.w, hh.w, ll.w);
+          *reinterpret_cast<float4 *>(ep.c_hi + off) = hh;
+          *reinterpret_cast<float4 *>(ep.c_lo + off) = ll;
         }
       }
     }
@@ -427,7 +397,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   if (stamp && warp == 2 && lane == 0) ep.timeline[6] = global_timer();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (stamp && threadIdx.x == 0) ep.timeline[7] = global_timer();
+  if (ep.timeline != nullptr && threadIdx.x == 0) {
+    const unsigned long long t = global_timer();
+    atomicMax(ep.timeline + 9, t);  // latest CTA end
+    if (stamp) ep.timeline[7] = t;
+  }
   if (warp == 1) {
     __syncwarp();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

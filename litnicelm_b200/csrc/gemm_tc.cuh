@@ -28,8 +28,18 @@ struct TcEpilogue {
   float *c = nullptr;               // [M, N] dense fp32 result (may be null)
   float *c_hi = nullptr;            // optional split result for a following GEMM
   float *c_lo = nullptr;
+  // Optional transposed store of the columns from vt_col0 on (the V third of a
+  // QKV projection) for the tensor-core attention, which wants V K-major:
+  // element (row r = stream * s + t, column vt_col0 + c) goes, split, to
+  // vt_hi/vt_lo[(stream * vt_rows + c) * vt_pitch + t] instead of c / c_hi / c_lo.
+  // s is state->s when state is set (graph replay), else vt_s.
+  float *vt_hi = nullptr;
+  float *vt_lo = nullptr;
+  int vt_col0 = 0, vt_rows = 0, vt_pitch = 0, vt_s = 0, vt_streams = 0;
+  const LoopState *state = nullptr;
   // Measurement aid: when set, CTA (0,0,0) stores %globaltimer stamps of its
-  // pipeline milestones here (8 entries).
+  // pipeline milestones here (entries 0-7) and every CTA contributes to the
+  // earliest start [8] (preset to all ones), latest end [9] and latest start [10].
   unsigned long long *timeline = nullptr;
 };
 
@@ -58,6 +68,21 @@ TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256);
 // box rows plan.bn.
 void launch_gemm_tc(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const TcPlan &plan,
                     const TcEpilogue &ep, float *scratch, int *counters, DevErr *err, cudaStream_t st);
+
+// attention_tc.cu: fused causal attention on the tensor cores for head
+// dimension 64. qk: maps (box 128 rows x 32) over the split [rows, 3*d_model]
+// output of the QKV projection; vt: maps (box 64 rows x 32) over the split V^T
+// arrays [n_streams * d_model, pitch] the same projection stores (pitch a
+// multiple of 128 that covers s). Writes the context as a TF32 hi/lo pair.
+// state != nullptr: s is an upper bound with the same number of 128-row tiles
+// as the actual context length state->s. Scratch and zero-resting counters as
+// attention_tc_plan says. timeline (optional, 12 entries: [8] preset to all ones,
+// the rest zero): %globaltimer stamps of CTA (0,0,0) and the kernel's span.
+bool attention_tc_supports(int n_heads, int d_model);
+AttentionPlan attention_tc_plan(int n_streams, int s, int n_heads);
+void launch_attention_tc(const TcMatrix &qk, const TcMatrix &vt, float *ctx_hi, float *ctx_lo, int n_streams, int s,
+                         int n_heads, int d_model, float *scratch, int *counters, const LoopState *state,
+                         DevErr *err, cudaStream_t st, unsigned long long *timeline = nullptr);
 
 // x -> (hi, lo) elementwise.
 void launch_split_tf32(const float *x, float *hi, float *lo, long long count, cudaStream_t st);

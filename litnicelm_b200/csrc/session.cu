@@ -140,6 +140,18 @@ struct litnice_b200_session {
   std::vector<std::array<TcWeight, 4>> tcw;  // per layer: qkv, out, w1, w2
   TcWeight tc_head;
   TcMatrix a_map[4]{};
+  // tensor-core attention (head dimension 64): the QKV projection stores Q and K
+  // split in qkv_hi/qkv_lo [rows, 3D] and V transposed and split in vt_hi/vt_lo
+  // [streams * D, vt_pitch] (row = stream * D + column, one entry per position)
+  bool tc_attn = false;
+  float *qkv_hi = nullptr, *qkv_lo = nullptr, *vt_hi = nullptr, *vt_lo = nullptr;
+  long long vt_rows = 0;
+  int vt_pitch = 0;
+  TcMatrix qk_map{}, vt_map{};
+  // measurement aid (LITNICE_B200_ATTN_TIMELINE, profile_step only): 10 stamps per profiled attention launch
+  unsigned long long *attn_timeline = nullptr;
+  int attn_timeline_used = 0;
+  static constexpr int kTimelineSlots = 64;
   float *tc_scratch = nullptr;   // split-k partial tiles of the tensor-core GEMM
   int *tc_counters = nullptr;
   float *attn_scratch = nullptr;
@@ -180,7 +192,8 @@ const float *P(const litnice_b200_session *s, size_t off) {
 }
 
 void free_activations(litnice_b200_session *s) {
-  for (float **p : {&s->x, &s->y, &s->ln, &s->ctx, &s->qkv, &s->h, &s->ln_lo, &s->ctx_lo, &s->h_lo}) {
+  for (float **p : {&s->x, &s->y, &s->ln, &s->ctx, &s->qkv, &s->h, &s->ln_lo, &s->ctx_lo, &s->h_lo, &s->qkv_hi,
+                    &s->qkv_lo}) {
     if (*p) cudaFree(*p);
     *p = nullptr;
   }
@@ -219,6 +232,13 @@ void ensure_rows(litnice_b200_session *s, long long rows) {
     make_activation_map(&s->a_map[A_CTX], s->ctx, s->ctx_lo, rows, (int)D);
     make_activation_map(&s->a_map[A_H], s->h, s->h_lo, rows, (int)F);
   }
+  if (s->tc_attn) {
+    alloc(&s->qkv_hi, rows * 3 * D);
+    alloc(&s->qkv_lo, rows * 3 * D);
+    LB_CUDA(cudaMemsetAsync(s->qkv_hi, 0, rows * 3 * D * 4, s->st));
+    LB_CUDA(cudaMemsetAsync(s->qkv_lo, 0, rows * 3 * D * 4, s->st));
+    make_activation_map(&s->qk_map, s->qkv_hi, s->qkv_lo, rows, (int)(3 * D));
+  }
   s->cap_rows = rows;
   ++s->generation;
 }
@@ -227,8 +247,37 @@ void ensure_rows(litnice_b200_session *s, long long rows) {
 void ensure_attention_scratch(litnice_b200_session *s, int B, int s_lo, int s_hi) {
   size_t need_f = 0, need_c = 0;
   const int dh = s->dims.d_model / s->dims.n_heads;
+  if (s->tc_attn) {
+    // V^T: one row per (stream, column), one entry per position, whole key tiles
+    const long long rows = (long long)B * s->dims.d_model;
+    const int pitch = (s_hi + 127) / 128 * 128;
+    if (rows > s->vt_rows || pitch > s->vt_pitch) {
+      LB_CUDA(cudaStreamSynchronize(s->st));
+      const long long new_rows = rows > s->vt_rows ? rows : s->vt_rows;
+      const int new_pitch = pitch > s->vt_pitch ? pitch : s->vt_pitch;
+      for (float **p : {&s->vt_hi, &s->vt_lo}) {
+        if (*p) cudaFree(*p);
+        *p = nullptr;
+      }
+      s->vt_rows = 0;
+      s->vt_pitch = 0;
+      const size_t bytes = (size_t)new_rows * new_pitch * 4;
+      if (cudaMalloc(reinterpret_cast<void **>(&s->vt_hi), bytes) != cudaSuccess) throw std::bad_alloc();
+      if (cudaMalloc(reinterpret_cast<void **>(&s->vt_lo), bytes) != cudaSuccess) throw std::bad_alloc();
+      // positions past a stream's length are multiplied by zero probabilities:
+      // they must hold finite values from the start
+      LB_CUDA(cudaMemsetAsync(s->vt_hi, 0, bytes, s->st));
+      LB_CUDA(cudaMemsetAsync(s->vt_lo, 0, bytes, s->st));
+      tc_make_map(&s->vt_map.hi, s->vt_hi, (unsigned long long)new_rows, (unsigned long long)new_pitch, 64);
+      tc_make_map(&s->vt_map.lo, s->vt_lo, (unsigned long long)new_rows, (unsigned long long)new_pitch, 64);
+      s->vt_rows = new_rows;
+      s->vt_pitch = new_pitch;
+      ++s->generation;
+    }
+  }
   for (int sl = s_lo; sl <= s_hi; ++sl) {
-    const AttentionPlan p = attention_plan(B, sl, s->dims.n_heads, dh);
+    const AttentionPlan p = s->tc_attn ? attention_tc_plan(B, sl, s->dims.n_heads)
+                                       : attention_plan(B, sl, s->dims.n_heads, dh);
     if (p.scratch_floats > need_f) need_f = p.scratch_floats;
     if (p.counters > need_c) need_c = p.counters;
   }
@@ -280,12 +329,14 @@ struct ClassTimer {
 // else the fp32 SIMT kernel. split_out: store the result as a TF32 hi/lo pair
 // (c, c_lo) for a tensor-core projection that follows.
 void projection(litnice_b200_session *s, AKind ak, long long rows, int k, const float *w, const TcWeight *tw,
-                int n, const float *bias, const float *residual, int relu, float *c, float *c_lo) {
+                int n, const float *bias, const float *residual, int relu, float *c, float *c_lo,
+                const TcEpilogue *vt_store = nullptr) {
   ClassTimer t(s, &s->gemm_ev);
   if (s->profiling) s->gemm_flops += 2.0 * (double)rows * n * k;
   ++s->launches;
   if (s->tc && tw != nullptr && tw->usable()) {
     TcEpilogue ep;
+    if (vt_store) ep = *vt_store;
     ep.bias = bias;
     ep.residual = residual;
     ep.relu = relu;
@@ -324,9 +375,28 @@ void enqueue_body(litnice_b200_session *s, int B, int sl, const LoopState *dstat
     launch_layernorm_dense(s->x, P(s, o.ln1_g), P(s, o.ln1_b), R, D, s->ln, s->tc ? s->ln_lo : nullptr, dstate, B,
                            s->st);
     ++s->launches;
-    projection(s, A_LN, R, D, P(s, o.qkv_w), tw ? &(*tw)[0] : nullptr, 3 * D, P(s, o.qkv_b), nullptr, 0, s->qkv,
-               nullptr);
-    {
+    if (s->tc_attn) {
+      // Q and K as TF32 pairs, V transposed: what the tensor-core attention reads
+      TcEpilogue vt;
+      vt.vt_hi = s->vt_hi;
+      vt.vt_lo = s->vt_lo;
+      vt.vt_col0 = 2 * D;
+      vt.vt_rows = D;
+      vt.vt_pitch = s->vt_pitch;
+      vt.vt_s = sl;
+      vt.vt_streams = B;
+      vt.state = dstate;
+      projection(s, A_LN, R, D, P(s, o.qkv_w), &(*tw)[0], 3 * D, P(s, o.qkv_b), nullptr, 0, s->qkv_hi, s->qkv_lo,
+                 &vt);
+      ClassTimer t(s, &s->attn_ev);
+      launch_attention_tc(s->qk_map, s->vt_map, s->ctx, s->ctx_lo, B, sl, d.n_heads, D, s->attn_scratch,
+                          s->attn_counters, dstate, s->err_dev, s->st, (s->profiling && s->attn_timeline && s->attn_timeline_used < litnice_b200_session::kTimelineSlots)
+                              ? s->attn_timeline + 16 * s->attn_timeline_used++
+                              : nullptr);
+      ++s->launches;
+    } else {
+      projection(s, A_LN, R, D, P(s, o.qkv_w), tw ? &(*tw)[0] : nullptr, 3 * D, P(s, o.qkv_b), nullptr, 0, s->qkv,
+                 nullptr);
       ClassTimer t(s, &s->attn_ev);
       launch_attention(s->qkv, s->ctx, s->tc ? s->ctx_lo : nullptr, B, sl, d.n_heads, D, s->attn_scratch,
                        s->attn_counters, dstate, s->st);
@@ -502,6 +572,10 @@ int litnice_b200_session_create(const litnice_b200_dims *dims, int32_t max_strea
     s->use_graphs = !(graph_env && graph_env[0] == '0');
     const char *tc_env = std::getenv("LITNICE_B200_TC");
     s->tc = !(tc_env && tc_env[0] == '0') && tc_runtime_available() && d.d_model % 64 == 0 && d.d_ff % 64 == 0;
+    // Attention on the tensor cores needs head dimension 64; LITNICE_B200_TC_ATTN=0
+    // keeps the fp32 SIMT attention kernel.
+    const char *ta_env = std::getenv("LITNICE_B200_TC_ATTN");
+    s->tc_attn = s->tc && !(ta_env && ta_env[0] == '0') && attention_tc_supports(d.n_heads, d.d_model);
     size_t lr = (size_t)(max_streams < 8 ? 8 : max_streams);
     if (s->tc) lr = (lr + TC_BM - 1) / TC_BM * TC_BM;
     s->xl_rows = (long long)lr;
@@ -543,6 +617,9 @@ void litnice_b200_session_destroy(litnice_b200_session *s) {
     if (g.exec) cudaGraphExecDestroy(g.exec);
   if (s->xl_lo) cudaFree(s->xl_lo);
   if (s->tc_scratch) cudaFree(s->tc_scratch);
+  if (s->attn_timeline) cudaFree(s->attn_timeline);
+  if (s->vt_hi) cudaFree(s->vt_hi);
+  if (s->vt_lo) cudaFree(s->vt_lo);
   if (s->tc_counters) cudaFree(s->tc_counters);
   if (s->attn_scratch) cudaFree(s->attn_scratch);
   if (s->attn_counters) cudaFree(s->attn_counters);
@@ -966,6 +1043,16 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
     s->gemm_ev.clear();
     s->attn_ev.clear();
     s->gemm_flops = 0;
+    if (s->tc_attn && s->attn_timeline == nullptr && std::getenv("LITNICE_B200_ATTN_TIMELINE") != nullptr)
+      if (cudaMalloc(reinterpret_cast<void **>(&s->attn_timeline), litnice_b200_session::kTimelineSlots * 128) !=
+          cudaSuccess)
+        throw std::bad_alloc();
+    if (s->attn_timeline) {
+      LB_CUDA(cudaMemsetAsync(s->attn_timeline, 0, litnice_b200_session::kTimelineSlots * 128, s->st));
+      for (int i = 0; i < litnice_b200_session::kTimelineSlots; ++i)
+        LB_CUDA(cudaMemsetAsync(s->attn_timeline + 16 * i + 8, 0xff, 8, s->st));  // earliest start: preset to max
+      s->attn_timeline_used = 0;
+    }
     enqueue_body(s, n_streams, seq_len);  // warm-up, untimed
     s->profiling = true;
     try {
@@ -999,6 +1086,22 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
     s->stats.gemm_flops = s->gemm_flops;
     s->gemm_ev.clear();
     s->attn_ev.clear();
+    if (s->attn_timeline) {
+      // per profiled launch: stamps of CTA (0,0,0) and the span from the first CTA's start to the last CTA's end
+      std::vector<unsigned long long> t(16 * (size_t)s->attn_timeline_used);
+      if (!t.empty()) LB_CUDA(cudaMemcpy(t.data(), s->attn_timeline, t.size() * 8, cudaMemcpyDeviceToHost));
+      for (int i = 0; i < s->attn_timeline_used; ++i) {
+        const unsigned long long *u = t.data() + 16 * i;
+        std::fprintf(stderr,
+                     "attention launch %d (ns from CTA start): setup %lld, Q+K landed %lld, S ready %lld, P stored %lld, "
+                     "O ready %lld, partial merged %lld, end %lld; CTA start after first %lld; last CTA start %lld; whole grid %lld; last to end: blockIdx.x %d merge %d; split path: partial stored %lld, fenced %lld, counted %lld, merge loaded %lld\n",
+                     i, (long long)(u[1] - u[0]), (long long)(u[2] - u[0]), (long long)(u[3] - u[0]),
+                     (long long)(u[4] - u[0]), (long long)(u[5] - u[0]), (long long)(u[6] - u[0]),
+                     (long long)(u[7] - u[0]), (long long)(u[0] - u[8]), (long long)(u[10] - u[8]),
+                     (long long)(u[9] - u[8]), (int)((u[11] >> 1) & 0x3ff), (int)(u[11] & 1), (long long)(u[12] - u[0]),
+                     (long long)(u[13] - u[0]), (long long)(u[14] - u[0]), (long long)(u[15] - u[0]));
+      }
+    }
     return LITNICE_B200_OK;
   });
 }
@@ -1098,15 +1201,20 @@ static int projection_impl(int32_t engine, const float *a, int32_t m, int32_t k,
       ep.c = dc;
       const bool want_timeline = std::getenv("LITNICE_B200_TC_TIMELINE") != nullptr;
       if (want_timeline) {
-        ep.timeline = reinterpret_cast<unsigned long long *>(dev_alloc(8 * 8));
-        LB_CUDA(cudaMemsetAsync(ep.timeline, 0, 64, st));
+        ep.timeline = reinterpret_cast<unsigned long long *>(dev_alloc(12 * 8));
       }
       cudaEvent_t e0, e1;
       LB_CUDA(cudaEventCreate(&e0));
       LB_CUDA(cudaEventCreate(&e1));
       launch_gemm_tc(ma, mb, m, n, k, plan, ep, scr, cnt, err_dev, st);
       LB_CUDA(cudaEventRecord(e0, st));
-      for (int r = 1; r < repeats; ++r) launch_gemm_tc(ma, mb, m, n, k, plan, ep, scr, cnt, err_dev, st);
+      for (int r = 1; r < repeats; ++r) {
+        if (want_timeline) {  // stamps of the last launch only
+          LB_CUDA(cudaMemsetAsync(ep.timeline, 0, 96, st));
+          LB_CUDA(cudaMemsetAsync(ep.timeline + 8, 0xff, 8, st));
+        }
+        launch_gemm_tc(ma, mb, m, n, k, plan, ep, scr, cnt, err_dev, st);
+      }
       LB_CUDA(cudaEventRecord(e1, st));
       LB_CUDA(cudaStreamSynchronize(st));
       float ms = 0.f;
@@ -1115,14 +1223,14 @@ static int projection_impl(int32_t engine, const float *a, int32_t m, int32_t k,
       cudaEventDestroy(e0);
       cudaEventDestroy(e1);
       if (want_timeline) {
-        unsigned long long t[8];
-        LB_CUDA(cudaMemcpy(t, ep.timeline, 64, cudaMemcpyDeviceToHost));
+        unsigned long long t[12];
+        LB_CUDA(cudaMemcpy(t, ep.timeline, 96, cudaMemcpyDeviceToHost));
         std::fprintf(stderr,
                      "tc timeline (ns from start): setup %lld, loads issued %lld, first stage full %lld, mma issued %lld, "
-                     "chunks drained %lld, stored %lld, end %lld\n",
+                     "chunks drained %lld, stored %lld, end %lld; last CTA start %lld, whole grid %lld\n",
                      (long long)(t[1] - t[0]), (long long)(t[2] - t[0]), (long long)(t[3] - t[0]),
                      (long long)(t[4] - t[0]), (long long)(t[5] - t[0]), (long long)(t[6] - t[0]),
-                     (long long)(t[7] - t[0]));
+                     (long long)(t[7] - t[0]), (long long)(t[10] - t[8]), (long long)(t[9] - t[8]));
       }
     }
     LB_CUDA(cudaMemcpyAsync(c, dc, (size_t)m * n * 4, cudaMemcpyDeviceToHost, st));

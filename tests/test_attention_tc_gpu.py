@@ -1,0 +1,119 @@
+"""Tensor-core attention (head dimension 64) against the oracle and against the
+fp32 SIMT attention kernel, through the C ABI's native forward and token loop.
+
+Shapes are chosen around the kernel's 128-row tiles and around its two
+schedules: key ranges cut over several CTAs (few streams x heads) and one CTA
+walking several key tiles (many streams x heads).
+"""
+import os
+
+import numpy as np
+import pytest
+
+from litnicelm_b200 import formats
+from litnicelm_b200.plugin import Session
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_RTOL = 1e-3   # the path's stated tolerance against the oracle
+KERNEL_RTOL = 1e-4  # two fp32-accurate kernels against each other
+NEAR_TIE = 1e-4
+
+DIMS = formats.ModelDims(2, 2, 128, 256, 96, 1024)  # L, H, D, F, V, S: head dimension 64
+
+
+def rel_err(got, want):
+    scale = np.maximum(np.abs(want).max(axis=-1, keepdims=True), 1e-6)
+    return float((np.abs(got - want) / scale).max())
+
+
+@pytest.fixture(scope="module")
+def arena():
+    return formats.make_param_arena(DIMS, 1234, bias_std=0.02)
+
+
+class simt_attention:
+    """Sessions created inside this block keep the SIMT attention kernel."""
+
+    def __enter__(self):
+        self.old = os.environ.get("LITNICE_B200_TC_ATTN")
+        os.environ["LITNICE_B200_TC_ATTN"] = "0"
+
+    def __exit__(self, *exc):
+        if self.old is None:
+            del os.environ["LITNICE_B200_TC_ATTN"]
+        else:
+            os.environ["LITNICE_B200_TC_ATTN"] = self.old
+
+
+@pytest.mark.parametrize("seq", [1, 64, 127, 128, 129, 255, 256, 257, 300, 513, 640])
+def test_split_key_schedule_matches_oracle(oracle, arena, seq):
+    """One and three streams of two heads: every query tile's keys are cut over CTAs."""
+    ids = formats.zipf_prompt(DIMS.vocab, seq, 9000 + seq)
+    want = oracle.forward(DIMS, arena, ids)
+    with Session(DIMS, 3) as s:
+        s.load_params(arena)
+        one = s.forward(ids, all_rows=True)[0]
+        three = s.forward(np.stack([ids, ids[::-1].copy(), ids]), all_rows=True)
+    assert rel_err(one, want) < LOGIT_RTOL
+    assert rel_err(three[0], want) < LOGIT_RTOL
+    assert np.array_equal(three[0], three[2])
+    assert rel_err(three[1], oracle.forward(DIMS, arena, ids[::-1].copy())) < LOGIT_RTOL
+
+
+@pytest.mark.parametrize("streams,seq", [(40, 200), (19, 512), (80, 130)])
+def test_multi_tile_schedule_matches_simt_kernel_and_oracle(oracle, arena, streams, seq):
+    """Enough (stream, head) pairs that one CTA walks all key tiles of its query tile."""
+    ids = np.stack([formats.zipf_prompt(DIMS.vocab, seq, 500 + b) for b in range(streams)])
+    with Session(DIMS, streams) as s:
+        s.load_params(arena)
+        got = s.forward(ids, all_rows=True)
+    with simt_attention():
+        with Session(DIMS, streams) as s:
+            s.load_params(arena)
+            ref = s.forward(ids, all_rows=True)
+    assert rel_err(got, ref) < KERNEL_RTOL
+    for b in (0, streams // 2, streams - 1):
+        assert rel_err(got[b], oracle.forward(DIMS, arena, ids[b])) < LOGIT_RTOL
+
+
+def test_token_loop_across_tile_boundaries(oracle, arena):
+    """Graph replay with the context growing through 128 and 192: tokens and step logits."""
+    prompt = formats.zipf_prompt(DIMS.vocab, 120, 77)
+    ref_t, ref_l = oracle.generate(DIMS, arena, prompt, 80, want_logits=True)
+    with Session(DIMS, 2) as s:
+        s.load_params(arena)
+        s.keep_step_logits(True)
+        toks = s.generate(np.stack([prompt, prompt]), 80)
+        lg = s.read_step_logits(toks.shape[1], 2)
+    assert np.array_equal(toks[0], toks[1])
+    n = len(ref_t)
+    for i in range(n):
+        if toks[0][i] != ref_t[i]:
+            top2 = np.sort(ref_l[i])[-2:]
+            assert top2[1] - top2[0] < NEAR_TIE, f"step {i}"
+            n = i
+            break
+    assert n >= 8
+    assert rel_err(lg[:n, 0, :], ref_l[:n]) < LOGIT_RTOL
+
+
+def test_token_loop_graph_replay_equals_direct_launches(arena):
+    """The replayed graphs (launches sized for a 64-token bucket, the length read on
+    the device) give the same tokens as launching every kernel for the exact length."""
+    prompts = np.stack([formats.zipf_prompt(DIMS.vocab, 100, 31 + b) for b in range(3)])
+    with Session(DIMS, 3) as s:
+        s.load_params(arena)
+        a = s.generate(prompts, 70)
+    old = os.environ.get("LITNICE_B200_GRAPHS")
+    os.environ["LITNICE_B200_GRAPHS"] = "0"
+    try:
+        with Session(DIMS, 3) as s:
+            s.load_params(arena)
+            b = s.generate(prompts, 70)
+    finally:
+        if old is None:
+            del os.environ["LITNICE_B200_GRAPHS"]
+        else:
+            os.environ["LITNICE_B200_GRAPHS"] = old
+    assert np.array_equal(a, b)
