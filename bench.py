@@ -325,6 +325,18 @@ def run_b200_arm(args, rank, local_rank, world):
                      f"{prof.gemm_ms:.3f} ms (CUDA events around each launch on the session stream); "
                      f"attention: {prof.attn_launches} launches, {prof.attn_ms:.3f} ms"),
         }
+        # The same kernel where the path's definition puts it on the tensor roofline (many rows): the
+        # QKV projection of the config-4/5 model on 16 384 rows, warm, back to back.
+        try:
+            from litnicelm_b200.plugin import projection_time
+            m_big, k_big, n_big = 16384, 1024, 3072
+            us = projection_time(m_big, k_big, n_big, repeats=20)
+            big = 2.0 * m_big * k_big * n_big / (us * 1e-6) / 1e12
+            roofline["at_scale"] = {"shape_mkn": [m_big, k_big, n_big], "us_per_launch": us, "achieved": big,
+                                    "frac": big / peaks["bf16_tflops"],
+                                    "frac_of_3xtf32_ceiling": 6.0 * big / peaks["bf16_tflops"]}
+        except Exception as e:
+            roofline["at_scale"] = {"unavailable": str(e)}
         # ---- CPU baseline: the reference itself on a bounded sample ----
         cpu = None
         if not args.no_cpu_baseline:

@@ -17,6 +17,7 @@
 // freeing its tensor memory. No cluster launch and no multicast is used.
 #include "gemm_tc.cuh"
 #include "tc_ptx.cuh"
+#include "gemm_tc_epilogue.cuh"
 
 #include <cstdlib>
 #include <mutex>
@@ -268,131 +269,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
       if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
     }
     if (stamp && warp == 2 && lane == 0) ep.timeline[5] = global_timer();
-    bool finish = ok && !*abort_flag;
-    const int rl = q * 32 + lane;  // row inside the tile
-    if (splits > 1) {
-      // Split-k: leave the partial tile in scratch; the CTA that arrives last at
-      // the tile's counter adds all partials in split order and stores C.
-      // Partial tiles are laid out [column / 4][row][4] so that the 32 rows of a
-      // warp are contiguous (a row-major tile would cost 32 lines per access).
-      const long long tile = (long long)blockIdx.y * gridDim.x + blockIdx.x;
-      float4 *mine = reinterpret_cast<float4 *>(part + (tile * splits + blockIdx.z) * TC_BM * BN) +
-                     (col0 / 4) * TC_BM + rl;
-#pragma unroll
-      for (int j = 0; j < CW; j += 4) mine[(j / 4) * TC_BM] = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-      __threadfence();
-      asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
-      if (warp == 2 && lane == 0) {
-        const int prev = atomicAdd(counters + tile, 1);
-        const int last = (prev == splits - 1) ? 1 : 0;
-        if (last) counters[tile] = 0;  // ready for the next launch
-        *last_flag = last;
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
-      finish = finish && (*last_flag != 0);
-      if (finish) {
-        __threadfence();
-#pragma unroll
-        for (int j = 0; j < CW; ++j) acc[j] = 0.f;
-        // Two partials per step (narrow tiles) with every load issued before the first add (the
-        // reduction is a chain of L2 round trips otherwise); added in split order.
-        constexpr int ZU = BN == 64 ? 2 : 1;  // wider tiles have no registers to spare
-        for (int z = 0; z < splits; z += ZU) {
-          const float4 *p0 = reinterpret_cast<const float4 *>(part + (tile * splits + z) * TC_BM * BN) +
-                             (col0 / 4) * TC_BM + rl;
-          const bool two = ZU == 2 && z + 1 < splits;
-          const float4 *p1 = two ? p0 + TC_BM * BN / 4 : p0;
-#pragma unroll
-          for (int j0 = 0; j0 < CW; j0 += 64) {
-            float4 t0[16], t1[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              t0[j] = __ldcg(p0 + (j0 / 4 + j) * TC_BM);
-              if (ZU == 2) t1[j] = __ldcg(p1 + (j0 / 4 + j) * TC_BM);
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              acc[j0 + 4 * j] += t0[j].x; acc[j0 + 4 * j + 1] += t0[j].y;
-              acc[j0 + 4 * j + 2] += t0[j].z; acc[j0 + 4 * j + 3] += t0[j].w;
-              if (ZU == 2 && two) {
-                acc[j0 + 4 * j] += t1[j].x; acc[j0 + 4 * j + 1] += t1[j].y;
-                acc[j0 + 4 * j + 2] += t1[j].z; acc[j0 + 4 * j + 3] += t1[j].w;
-              }
-            }
-          }
-        }
-      }
-    }
-
-    // Stores. A thread holds CW columns of one row; written directly, every
-    // instruction of a warp would touch 32 different lines. The V^T columns of a
-    // QKV projection are the exception (lanes = consecutive positions of one
-    // column): they go out from the registers. Everything else is transposed
-    // through the pipeline's shared memory (idle by now: every load has landed
-    // and every MMA has completed) and stored row by row, where bias, residual,
-    // ReLU and the TF32 split are applied on coalesced float4s.
-    const bool vt_on = ep.vt_hi != nullptr;
-    if (finish && vt_on && row < m && n0 + col0 + CW > ep.vt_col0) {
-      const int sl = ep.state ? ep.state->s : ep.vt_s;
-      const int v_stream = row / sl, v_tok = row - v_stream * sl;
-      if (v_stream < ep.vt_streams) {
-#pragma unroll
-        for (int j = 0; j < CW; ++j) {
-          const int col = n0 + col0 + j;
-          if (col >= ep.vt_col0) {
-            float hh, ll;
-            split_tf32(acc[j] + (ep.bias ? ep.bias[col] : 0.f), hh, ll);
-            const long long at = ((long long)v_stream * ep.vt_rows + (col - ep.vt_col0)) * ep.vt_pitch + v_tok;
-            ep.vt_hi[at] = hh;
-            ep.vt_lo[at] = ll;
-          }
-        }
-      }
-    }
-    constexpr int LDS = BN + 4;  // staging pitch: 16-byte accesses of 8 consecutive rows hit all banks once
-    static_assert(TC_BM * LDS * 4 <= L::TILES_BYTES, "staging tile must fit in the pipeline stages");
-    float *stage = reinterpret_cast<float *>(base_ptr);
-    if (finish) {
-#pragma unroll
-      for (int j = 0; j < CW; j += 4)
-        *reinterpret_cast<float4 *>(stage + rl * LDS + col0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
-    if (finish) {
-      const int t2 = threadIdx.x - 64;
-      constexpr int PER_ROW = BN / 4;
-#pragma unroll 4
-      for (int i = 0; i < TC_BM * PER_ROW / DRAIN_THREADS; ++i) {
-        const int u = t2 + i * DRAIN_THREADS;
-        const int rr = u / PER_ROW, c4 = u % PER_ROW;
-        const int col = n0 + c4 * 4;
-        if (m0 + rr >= m || (vt_on && col >= ep.vt_col0)) continue;
-        float4 v = *reinterpret_cast<const float4 *>(stage + rr * LDS + c4 * 4);
-        const long long off = (long long)(m0 + rr) * n + col;
-        if (ep.bias) {
-          const float4 bb = *reinterpret_cast<const float4 *>(ep.bias + col);
-          v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
-        }
-        if (ep.residual) {
-          const float4 rs = *reinterpret_cast<const float4 *>(ep.residual + off);
-          v.x += rs.x; v.y += rs.y; v.z += rs.z; v.w += rs.w;
-        }
-        if (ep.relu) {
-          v.x = v.x > 0.f ? v.x : 0.f; v.y = v.y > 0.f ? v.y : 0.f;
-          v.z = v.z > 0.f ? v.z : 0.f; v.w = v.w > 0.f ? v.w : 0.f;
-        }
-        if (ep.c) *reinterpret_cast<float4 *>(ep.c + off) = v;
-        if (ep.c_hi) {
-          float4 hh, ll;
-          split_tf32(v.x, hh.x, ll.x);
-          split_tf32(v.y, hh.y, ll.y);
-          split_tf32(v.z, hh.z, ll.z);
-          split_tf32(v.w, hh.w, ll.w);
-          *reinterpret_cast<float4 *>(ep.c_hi + off) = hh;
-          *reinterpret_cast<float4 *>(ep.c_lo + off) = ll;
-        }
-      }
-    }
+    static_assert(TC_BM * (BN + 4) * 4 <= L::TILES_BYTES, "staging tile must fit in the pipeline stages");
+    tc_finish_tile<BN, CW, DRAIN_THREADS>(acc, ok && !*abort_flag, ep, m, n, m0, n0, col0, q * 32 + lane,
+                                          (int)threadIdx.x - 64, warp == 2 && lane == 0, splits, part, counters,
+                                          last_flag, reinterpret_cast<float *>(base_ptr));
   }
   if (stamp && warp == 2 && lane == 0) ep.timeline[6] = global_timer();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

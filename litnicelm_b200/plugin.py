@@ -142,6 +142,28 @@ def get_api(lib: C.CDLL) -> BackendApiV1:
     return api.contents
 
 
+def projection_time(m: int, k: int, n: int, repeats: int = 20, engine: int = 1,
+                    lib: Optional[C.CDLL] = None) -> float:
+    """Average device time in microseconds of one C[m,n] = A[m,k]·W[k,n] on the
+    tensor-core (engine 1) or SIMT (engine 0) projection kernel, warm, launched
+    back to back (litnice_b200_projection_time)."""
+    lib = lib or load_library()
+    f32p = C.POINTER(C.c_float)
+    fn = lib.litnice_b200_projection_time
+    fn.argtypes = [C.c_int32, f32p, C.c_int32, C.c_int32, f32p, C.c_int32, f32p, C.c_int32, C.POINTER(C.c_double)]
+    fn.restype = C.c_int
+    rng = np.random.default_rng(0)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    w = (rng.standard_normal((k, n), dtype=np.float32) * 0.02).astype(np.float32)
+    c = np.empty((m, n), np.float32)
+    us = C.c_double(0)
+    rc = fn(engine, a.ctypes.data_as(f32p), m, k, w.ctypes.data_as(f32p), n, c.ctypes.data_as(f32p), repeats,
+            C.byref(us))
+    if rc != 0:
+        raise RuntimeError(f"litnice_b200_projection_time failed with status {rc}")
+    return us.value
+
+
 @dataclass
 class DevTensor:
     """A byte-strided view into plugin-allocated memory (TensorView of the
