@@ -15,7 +15,8 @@ namespace {
 __global__ void embed_pos_kernel(const float *__restrict__ tok_emb,
                                  const float *__restrict__ pos_emb, const int *__restrict__ ids,
                                  int ids_ld, const LoopState *state, int n_streams, int s_cap, int d,
-                                 int vocab, float *__restrict__ x, DevErr *err) {
+                                 int vocab, float *__restrict__ x, float *__restrict__ x_hi,
+                                 float *__restrict__ x_lo, double2 *__restrict__ stats, DevErr *err) {
   pdl_launch_dependents();
   pdl_wait();
   const int s = state ? state->s : s_cap;
@@ -34,9 +35,37 @@ __global__ void embed_pos_kernel(const float *__restrict__ tok_emb,
   const float4 *tp = reinterpret_cast<const float4 *>(tok_emb + (long long)id * d);
   const float4 *pp = reinterpret_cast<const float4 *>(pos_emb + (long long)t * d);
   float4 *xp = reinterpret_cast<float4 *>(x + r * d);
-  for (int c = threadIdx.x; c < (d >> 2); c += blockDim.x) {
-    const float4 a = tp[c], p = pp[c];
-    xp[c] = make_float4(a.x + p.x, a.y + p.y, a.z + p.z, a.w + p.w);
+  const int n4 = d >> 2;
+  // Uniform trip count: with `stats` the 16 lanes that share a 64-column slot
+  // reduce their sums by shuffles, so every lane of a warp takes part.
+  for (int c0 = 0; c0 < n4; c0 += blockDim.x) {
+    const int c = c0 + threadIdx.x;
+    const bool valid = c < n4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (valid) {
+      const float4 a = tp[c], p = pp[c];
+      v = make_float4(a.x + p.x, a.y + p.y, a.z + p.z, a.w + p.w);
+      xp[c] = v;
+      if (x_hi != nullptr) {  // TF32 pair for a tensor-core projection that reads x itself
+        float4 hh, ll;
+        split_tf32(v.x, hh.x, ll.x);
+        split_tf32(v.y, hh.y, ll.y);
+        split_tf32(v.z, hh.z, ll.z);
+        split_tf32(v.w, hh.w, ll.w);
+        reinterpret_cast<float4 *>(x_hi + r * d)[c] = hh;
+        reinterpret_cast<float4 *>(x_lo + r * d)[c] = ll;
+      }
+    }
+    if (stats != nullptr) {  // (sum x, sum x^2) per slot of 64 columns, for a LayerNorm folded into that projection
+      double sx = ((double)v.x + (double)v.y) + ((double)v.z + (double)v.w);
+      double sxx = ((double)v.x * v.x + (double)v.y * v.y) + ((double)v.z * v.z + (double)v.w * v.w);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) {
+        sx += __shfl_xor_sync(0xffffffffu, sx, o);
+        sxx += __shfl_xor_sync(0xffffffffu, sxx, o);
+      }
+      if (valid && (c & 15) == 0) stats[r * TC_STAT_SLOTS + (c >> 4)] = make_double2(sx, sxx);
+    }
   }
 }
 
@@ -95,11 +124,11 @@ __global__ void advance_state_kernel(LoopState *state) {
 
 void launch_embed_pos(const float *tok_emb, const float *pos_emb, const int *ids, int ids_ld,
                       const LoopState *state, int n_streams, int s_host, int d, int vocab,
-                      float *x, DevErr *err, cudaStream_t st) {
+                      float *x, DevErr *err, cudaStream_t st, float *x_hi, float *x_lo, double2 *stats) {
   const long long rows = (long long)n_streams * s_host;
   if (rows <= 0) return;
   launch_pdl(embed_pos_kernel, dim3((unsigned)rows), dim3(d >= 512 ? 128 : 32), 0, st, g_pdl_enabled, tok_emb, pos_emb,
-             ids, ids_ld, state, n_streams, s_host, d, vocab, x, err);
+             ids, ids_ld, state, n_streams, s_host, d, vocab, x, x_hi, x_lo, stats, err);
 }
 
 void launch_gather_last_ln(const float *x, const float *gamma, const float *beta,

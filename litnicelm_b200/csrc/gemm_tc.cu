@@ -35,7 +35,8 @@ struct TcSmem {
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   static constexpr int TILES_BYTES = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFFSET = TILES_BYTES;          // full[S], empty[S], tmem_full
-  static constexpr int TOTAL = TILES_BYTES + 256 + 1024;  // + barriers/holders + alignment slack
+  static constexpr int ROWSTATS_OFFSET = BAR_OFFSET + 256;  // float2 (mean, 1/std) per tile row
+  static constexpr int TOTAL = TILES_BYTES + 256 + TC_BM * 8 + 1024;  // + barriers/holders, row statistics, alignment slack
 };
 
 // Tensor-core accumulation rounds toward zero: every tcgen05.mma that adds into
@@ -245,6 +246,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     const int q = warp & 3;
     const int col0 = ((warp - 2) >> 2) * CW;          // first column of this warp inside the tile
     const int row = m0 + q * 32 + lane;
+    // LayerNorm folded into this product: the row's statistics from the partial
+    // sums its producer left (read while the first tiles are still in flight)
+    float2 ln_st = make_float2(0.f, 1.f);
+    if (ep.ln_u != nullptr && row < m)
+      ln_st = ln_row_stats(ep.ln_stats + (long long)row * TC_STAT_SLOTS, ep.ln_slots, k);
     float acc[CW];
 #pragma unroll
     for (int j = 0; j < CW; ++j) acc[j] = 0.f;
@@ -272,7 +278,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     static_assert(TC_BM * (BN + 4) * 4 <= L::TILES_BYTES, "staging tile must fit in the pipeline stages");
     tc_finish_tile<BN, CW, DRAIN_THREADS>(acc, ok && !*abort_flag, ep, m, n, m0, n0, col0, q * 32 + lane,
                                           (int)threadIdx.x - 64, warp == 2 && lane == 0, splits, part, counters,
-                                          last_flag, reinterpret_cast<float *>(base_ptr));
+                                          last_flag, reinterpret_cast<float *>(base_ptr), ln_st,
+                                          reinterpret_cast<float2 *>(base_ptr + L::ROWSTATS_OFFSET));
   }
   if (stamp && warp == 2 && lane == 0) ep.timeline[6] = global_timer();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -304,12 +311,14 @@ __global__ void split_tf32_kernel(const float *__restrict__ x, float *__restrict
 
 // W [k, n] row-major -> wt_hi, wt_lo [n, k] (K-major), 32 x 32 tiles through shared memory.
 __global__ void transpose_split_kernel(const float *__restrict__ w, int k, int n, float *__restrict__ wt_hi,
-                                       float *__restrict__ wt_lo) {
+                                       float *__restrict__ wt_lo, const float *__restrict__ row_scale) {
   __shared__ float tile[32][33];
   const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
     const int kk = k0 + r, nn = n0 + threadIdx.x;
-    tile[r][threadIdx.x] = (kk < k && nn < n) ? w[(long long)kk * n + nn] : 0.f;
+    float v = (kk < k && nn < n) ? w[(long long)kk * n + nn] : 0.f;
+    if (row_scale != nullptr && kk < k) v = __fmul_rn(row_scale[kk], v);
+    tile[r][threadIdx.x] = v;
   }
   __syncthreads();
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
@@ -321,6 +330,26 @@ __global__ void transpose_split_kernel(const float *__restrict__ w, int k, int n
       wt_lo[(long long)nn * k + kk] = l;
     }
   }
+}
+
+// One thread per output column: u[n] = sum_k fl(gamma[k] W[k,n]) (the scaled
+// weights exactly as transpose_split_kernel stores them, hi + lo), v[n] =
+// sum_k beta[k] W[k,n] + bias[n]; sums in double.
+__global__ void ln_fold_vectors_kernel(const float *__restrict__ w, int k, int n, const float *__restrict__ gamma,
+                                       const float *__restrict__ beta, const float *__restrict__ bias,
+                                       float *__restrict__ u, float *__restrict__ v) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= n) return;
+  double su = 0.0, sv = 0.0;
+  for (int kk = 0; kk < k; ++kk) {
+    const float wv = w[(long long)kk * n + col];
+    float hh, ll;
+    split_tf32(__fmul_rn(gamma[kk], wv), hh, ll);
+    su += (double)hh + (double)ll;
+    sv += (double)beta[kk] * (double)wv;
+  }
+  u[col] = (float)su;
+  v[col] = (float)(sv + (bias ? (double)bias[col] : 0.0));
 }
 
 // ---- host side -----------------------------------------------------------------------
@@ -428,9 +457,16 @@ void launch_split_tf32(const float *x, float *hi, float *lo, long long count, cu
   LB_LAUNCH_CHECK();
 }
 
-void launch_transpose_split(const float *w, int k, int n, float *wt_hi, float *wt_lo, cudaStream_t st) {
+void launch_transpose_split(const float *w, int k, int n, float *wt_hi, float *wt_lo, cudaStream_t st,
+                            const float *row_scale) {
   dim3 grid((n + 31) / 32, (k + 31) / 32), block(32, 8);
-  transpose_split_kernel<<<grid, block, 0, st>>>(w, k, n, wt_hi, wt_lo);
+  transpose_split_kernel<<<grid, block, 0, st>>>(w, k, n, wt_hi, wt_lo, row_scale);
+  LB_LAUNCH_CHECK();
+}
+
+void launch_ln_fold_vectors(const float *w, int k, int n, const float *gamma, const float *beta, const float *bias,
+                            float *u, float *v, cudaStream_t st) {
+  ln_fold_vectors_kernel<<<(n + 127) / 128, 128, 0, st>>>(w, k, n, gamma, beta, bias, u, v);
   LB_LAUNCH_CHECK();
 }
 

@@ -16,6 +16,7 @@ namespace lb {
 
 constexpr int TC_BM = 128;  // rows per CTA (one UMMA M=128 tile)
 constexpr int TC_BK = 32;   // fp32 elements per k-block = one 128-byte swizzle row
+constexpr int TC_STAT_SLOTS = 32;  // row-statistics slots of 64 columns per row (rows up to 2048 wide)
 
 struct TcMatrix {  // one split operand: two tensor maps over K-major fp32 arrays
   CUtensorMap hi, lo;
@@ -37,6 +38,20 @@ struct TcEpilogue {
   float *vt_lo = nullptr;
   int vt_col0 = 0, vt_rows = 0, vt_pitch = 0, vt_s = 0, vt_streams = 0;
   const LoopState *state = nullptr;
+  // LayerNorm folded into the product. With W' = diag(gamma) W the reference's
+  // LN(x) W + b (layernorm_forward then gemm_ranked_matrix_rhs + add_bias_rowwise)
+  // equals inv_std * (x W' - mean * u) + v, u[n] = sum_k W'[k,n],
+  // v[n] = sum_k beta[k] W[k,n] + b[n]: the kernel multiplies the raw rows by W'
+  // and the epilogue applies the row statistics. ln_u != nullptr turns this on;
+  // `bias` then holds v. Statistics come as partial sums (sum x, sum x^2) in
+  // double over slots of 64 columns, ln_slots per row, written by the kernel
+  // that produced x (stats_out below) and added here in slot order.
+  const float *ln_u = nullptr;
+  const double2 *ln_stats = nullptr;  // [rows][TC_STAT_SLOTS]
+  int ln_slots = 0;
+  // Producer side: per row and 64-column slot of the stored result (after bias,
+  // residual, ReLU) the sums (x, x^2) in double, at stats_out[row][column / 64].
+  double2 *stats_out = nullptr;
   // Measurement aid: when set, CTA (0,0,0) stores %globaltimer stamps of its
   // pipeline milestones here (entries 0-7) and every CTA contributes to the
   // earliest start [8] (preset to all ones), latest end [9] and latest start [10].
@@ -86,8 +101,27 @@ void launch_attention_tc(const TcMatrix &qk, const TcMatrix &vt, float *ctx_hi, 
 
 // x -> (hi, lo) elementwise.
 void launch_split_tf32(const float *x, float *hi, float *lo, long long count, cudaStream_t st);
-// Row-major W [k, n] -> K-major split copies wt_hi, wt_lo [n, k].
-void launch_transpose_split(const float *w, int k, int n, float *wt_hi, float *wt_lo, cudaStream_t st);
+// Row-major W [k, n] -> K-major split copies wt_hi, wt_lo [n, k]; row_scale
+// (optional, [k]) multiplies row k first (the LayerNorm scale folded into W).
+void launch_transpose_split(const float *w, int k, int n, float *wt_hi, float *wt_lo, cudaStream_t st,
+                            const float *row_scale = nullptr);
+// u[n] = sum_k gamma[k] W[k,n], v[n] = sum_k beta[k] W[k,n] + bias[n] (sums in double).
+void launch_ln_fold_vectors(const float *w, int k, int n, const float *gamma, const float *beta, const float *bias,
+                            float *u, float *v, cudaStream_t st);
+// Mean and 1/std of one row from its partial sums, as layernorm_forward of the
+// reference forms them (biased variance, eps 1e-5 added in float).
+__device__ __forceinline__ float2 ln_row_stats(const double2 *slots, int n_slots, int d) {
+  double sx = 0.0, sxx = 0.0;
+  for (int i = 0; i < n_slots; ++i) {
+    const double2 t = slots[i];
+    sx += t.x;
+    sxx += t.y;
+  }
+  const double mean = sx / (double)d;
+  double var = sxx / (double)d - mean * mean;
+  if (var < 0.0) var = 0.0;
+  return make_float2((float)mean, 1.0f / sqrtf((float)var + 1e-5f));
+}
 
 __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
   unsigned h, l;

@@ -11,11 +11,14 @@ namespace lb {
 // t2: index of the thread among the DRAIN_THREADS epilogue threads, which share
 // named barrier 1; leader: the one thread that counts split-k arrivals. stage:
 // shared memory for a 128 x (BN + 4) float tile that nothing else uses any more.
+// ln_st: (mean, 1/std) of this thread's row when ep.ln_u is set; row_stats: 128
+// float2 of shared memory through which the store phase learns them.
 template <int BN, int CW, int DRAIN_THREADS>
 __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, const TcEpilogue &ep, int m, int n, int m0,
                                                int n0, int col0, int rl, int t2, bool leader, int splits,
                                                float *__restrict__ part, int *__restrict__ counters,
-                                               volatile int *last_flag, float *stage) {
+                                               volatile int *last_flag, float *stage, float2 ln_st,
+                                               float2 *row_stats) {
   const int row = m0 + rl;
   if (splits > 1) {
     // Split-k: leave the partial tile in scratch; the CTA that arrives last at
@@ -87,8 +90,10 @@ __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, co
       for (int j = 0; j < CW; ++j) {
         const int col = n0 + col0 + j;
         if (col >= ep.vt_col0) {
+          float val = acc[j];
+          if (ep.ln_u != nullptr) val = __fmul_rn(ln_st.y, __fmaf_rn(-ln_st.x, ep.ln_u[col], val));
           float hh, ll;
-          split_tf32(acc[j] + (ep.bias ? ep.bias[col] : 0.f), hh, ll);
+          split_tf32(val + (ep.bias ? ep.bias[col] : 0.f), hh, ll);
           const long long at = ((long long)v_stream * ep.vt_rows + (col - ep.vt_col0)) * ep.vt_pitch + v_tok;
           ep.vt_hi[at] = hh;
           ep.vt_lo[at] = ll;
@@ -101,6 +106,7 @@ __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, co
 #pragma unroll
     for (int j = 0; j < CW; j += 4)
       *reinterpret_cast<float4 *>(stage + rl * LDS + col0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+    if (ep.ln_u != nullptr && col0 == 0) row_stats[rl] = ln_st;
   }
   asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
   if (finish) {
@@ -113,6 +119,14 @@ __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, co
       if (m0 + rr >= m || (vt_on && col >= ep.vt_col0)) continue;
       float4 v = *reinterpret_cast<const float4 *>(stage + rr * LDS + c4 * 4);
       const long long off = (long long)(m0 + rr) * n + col;
+      if (ep.ln_u != nullptr) {  // inv_std * (x W' - mean * u); v comes in as the bias
+        const float2 st = row_stats[rr];
+        const float4 uu = *reinterpret_cast<const float4 *>(ep.ln_u + col);
+        v.x = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.x, v.x));
+        v.y = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.y, v.y));
+        v.z = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.z, v.z));
+        v.w = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.w, v.w));
+      }
       if (ep.bias) {
         const float4 bb = *reinterpret_cast<const float4 *>(ep.bias + col);
         v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
@@ -134,6 +148,27 @@ __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, co
         split_tf32(v.w, hh.w, ll.w);
         *reinterpret_cast<float4 *>(ep.c_hi + off) = hh;
         *reinterpret_cast<float4 *>(ep.c_lo + off) = ll;
+      }
+      if (ep.stats_out != nullptr) *reinterpret_cast<float4 *>(stage + rr * LDS + c4 * 4) = v;  // final values
+    }
+  }
+  if (ep.stats_out != nullptr) {
+    // Row statistics for a LayerNorm folded into the next product: thread = row
+    // again, sums of its stored values over slots of 64 columns, in column order.
+    asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
+    if (finish && row < m) {
+#pragma unroll
+      for (int j0 = 0; j0 < CW; j0 += 64) {
+        double sx = 0.0, sxx = 0.0;
+#pragma unroll 4
+        for (int j = 0; j < 64; j += 4) {
+          const float4 t = *reinterpret_cast<const float4 *>(stage + rl * LDS + col0 + j0 + j);
+          sx += (double)t.x; sxx += (double)t.x * (double)t.x;
+          sx += (double)t.y; sxx += (double)t.y * (double)t.y;
+          sx += (double)t.z; sxx += (double)t.z * (double)t.z;
+          sx += (double)t.w; sxx += (double)t.w * (double)t.w;
+        }
+        ep.stats_out[(long long)row * TC_STAT_SLOTS + (n0 + col0 + j0) / 64] = make_double2(sx, sxx);
       }
     }
   }

@@ -100,6 +100,8 @@ struct TcWeight {
   int k = 0, n = 0;
   bool has64 = false, has128 = false, has256 = false;
   TcMatrix m64{}, m128{}, m256{};
+  // LayerNorm folded into this product (the copies above then hold diag(gamma) W): u[n], v[n] of TcEpilogue
+  float *ln_u = nullptr, *ln_v = nullptr;
   bool usable() const { return has64 || has128; }
 };
 
@@ -152,6 +154,11 @@ struct litnice_b200_session {
   unsigned long long *attn_timeline = nullptr;
   int attn_timeline_used = 0;
   static constexpr int kTimelineSlots = 64;
+  // LayerNorm folded into the QKV and W1 products: the kernels that produce x and y
+  // (embedding, out-projection, W2) also store them as TF32 pairs in (ln, ln_lo) and
+  // leave per-row partial sums here, [rows][TC_STAT_SLOTS] (LITNICE_B200_LN_FOLD=0 disables)
+  bool ln_fold = false;
+  double2 *row_stats = nullptr;
   float *tc_scratch = nullptr;   // split-k partial tiles of the tensor-core GEMM
   int *tc_counters = nullptr;
   float *attn_scratch = nullptr;
@@ -197,6 +204,8 @@ void free_activations(litnice_b200_session *s) {
     if (*p) cudaFree(*p);
     *p = nullptr;
   }
+  if (s->row_stats) cudaFree(s->row_stats);
+  s->row_stats = nullptr;
   s->cap_rows = 0;
 }
 
@@ -231,6 +240,14 @@ void ensure_rows(litnice_b200_session *s, long long rows) {
     make_activation_map(&s->a_map[A_LN], s->ln, s->ln_lo, rows, (int)D);
     make_activation_map(&s->a_map[A_CTX], s->ctx, s->ctx_lo, rows, (int)D);
     make_activation_map(&s->a_map[A_H], s->h, s->h_lo, rows, (int)F);
+  }
+  if (s->ln_fold) {
+    if (cudaMalloc(reinterpret_cast<void **>(&s->row_stats), (size_t)rows * TC_STAT_SLOTS * sizeof(double2)) !=
+        cudaSuccess) {
+      free_activations(s);
+      throw std::bad_alloc();
+    }
+    LB_CUDA(cudaMemsetAsync(s->row_stats, 0, (size_t)rows * TC_STAT_SLOTS * sizeof(double2), s->st));
   }
   if (s->tc_attn) {
     alloc(&s->qkv_hi, rows * 3 * D);
@@ -330,19 +347,20 @@ struct ClassTimer {
 // (c, c_lo) for a tensor-core projection that follows.
 void projection(litnice_b200_session *s, AKind ak, long long rows, int k, const float *w, const TcWeight *tw,
                 int n, const float *bias, const float *residual, int relu, float *c, float *c_lo,
-                const TcEpilogue *vt_store = nullptr) {
+                const TcEpilogue *extra = nullptr, float *c_plain = nullptr) {
   ClassTimer t(s, &s->gemm_ev);
   if (s->profiling) s->gemm_flops += 2.0 * (double)rows * n * k;
   ++s->launches;
   if (s->tc && tw != nullptr && tw->usable()) {
     TcEpilogue ep;
-    if (vt_store) ep = *vt_store;
+    if (extra) ep = *extra;  // transposed V store, folded LayerNorm, row statistics
     ep.bias = bias;
     ep.residual = residual;
     ep.relu = relu;
     if (c_lo) {
       ep.c_hi = c;
       ep.c_lo = c_lo;
+      ep.c = c_plain;  // optionally the plain fp32 result as well
     } else {
       ep.c = c;
     }
@@ -366,41 +384,63 @@ void enqueue_body(litnice_b200_session *s, int B, int sl, const LoopState *dstat
   const litnice_b200_dims &d = s->dims;
   const long long R = (long long)B * sl;
   const int D = d.d_model, F = d.d_ff;
+  // With the LayerNorms folded into the QKV and W1 products, the kernels that
+  // produce x and y also store them as TF32 pairs in (ln, ln_lo) with per-row
+  // partial sums in row_stats, and no LayerNorm kernel runs in the layers.
+  const bool fold = s->ln_fold;
   launch_embed_pos(P(s, s->lay.tok_emb), P(s, s->lay.pos_emb), s->ids, d.max_seq_len, dstate, B, sl, D,
-                   d.vocab_size, s->x, s->err_dev, s->st);
+                   d.vocab_size, s->x, s->err_dev, s->st, fold ? s->ln : nullptr, fold ? s->ln_lo : nullptr,
+                   fold ? s->row_stats : nullptr);
   ++s->launches;
   for (int l = 0; l < d.n_layers; ++l) {
     const LayerOff &o = s->lay.layer[l];
     const std::array<TcWeight, 4> *tw = s->tc ? &s->tcw[l] : nullptr;
-    launch_layernorm_dense(s->x, P(s, o.ln1_g), P(s, o.ln1_b), R, D, s->ln, s->tc ? s->ln_lo : nullptr, dstate, B,
-                           s->st);
-    ++s->launches;
+    TcEpilogue consume1, consume2, produce;  // extra epilogue terms of the folded form
+    if (fold) {
+      consume1.ln_u = (*tw)[0].ln_u;
+      consume2.ln_u = (*tw)[2].ln_u;
+      consume1.ln_stats = consume2.ln_stats = s->row_stats;
+      consume1.ln_slots = consume2.ln_slots = D / 64;
+      produce.stats_out = s->row_stats;
+    } else {
+      launch_layernorm_dense(s->x, P(s, o.ln1_g), P(s, o.ln1_b), R, D, s->ln, s->tc ? s->ln_lo : nullptr, dstate, B,
+                             s->st);
+      ++s->launches;
+    }
+    const float *qkv_bias = fold ? (*tw)[0].ln_v : P(s, o.qkv_b);
     if (s->tc_attn) {
       // Q and K as TF32 pairs, V transposed: what the tensor-core attention reads
-      TcEpilogue vt;
-      vt.vt_hi = s->vt_hi;
-      vt.vt_lo = s->vt_lo;
-      vt.vt_col0 = 2 * D;
-      vt.vt_rows = D;
-      vt.vt_pitch = s->vt_pitch;
-      vt.vt_s = sl;
-      vt.vt_streams = B;
-      vt.state = dstate;
-      projection(s, A_LN, R, D, P(s, o.qkv_w), &(*tw)[0], 3 * D, P(s, o.qkv_b), nullptr, 0, s->qkv_hi, s->qkv_lo,
-                 &vt);
+      consume1.vt_hi = s->vt_hi;
+      consume1.vt_lo = s->vt_lo;
+      consume1.vt_col0 = 2 * D;
+      consume1.vt_rows = D;
+      consume1.vt_pitch = s->vt_pitch;
+      consume1.vt_s = sl;
+      consume1.vt_streams = B;
+      consume1.state = dstate;
+      projection(s, A_LN, R, D, P(s, o.qkv_w), &(*tw)[0], 3 * D, qkv_bias, nullptr, 0, s->qkv_hi, s->qkv_lo,
+                 &consume1);
       ClassTimer t(s, &s->attn_ev);
       launch_attention_tc(s->qk_map, s->vt_map, s->ctx, s->ctx_lo, B, sl, d.n_heads, D, s->attn_scratch,
-                          s->attn_counters, dstate, s->err_dev, s->st, (s->profiling && s->attn_timeline && s->attn_timeline_used < litnice_b200_session::kTimelineSlots)
+                          s->attn_counters, dstate, s->err_dev, s->st,
+                          (s->profiling && s->attn_timeline &&
+                           s->attn_timeline_used < litnice_b200_session::kTimelineSlots)
                               ? s->attn_timeline + 16 * s->attn_timeline_used++
                               : nullptr);
       ++s->launches;
     } else {
-      projection(s, A_LN, R, D, P(s, o.qkv_w), tw ? &(*tw)[0] : nullptr, 3 * D, P(s, o.qkv_b), nullptr, 0, s->qkv,
-                 nullptr);
+      projection(s, A_LN, R, D, P(s, o.qkv_w), tw ? &(*tw)[0] : nullptr, 3 * D, qkv_bias, nullptr, 0, s->qkv,
+                 nullptr, fold ? &consume1 : nullptr);
       ClassTimer t(s, &s->attn_ev);
       launch_attention(s->qkv, s->ctx, s->tc ? s->ctx_lo : nullptr, B, sl, d.n_heads, D, s->attn_scratch,
                        s->attn_counters, dstate, s->st);
       ++s->launches;
+    }
+    if (fold) {
+      projection(s, A_CTX, R, D, P(s, o.out_w), &(*tw)[1], D, P(s, o.out_b), s->x, 0, s->ln, s->ln_lo, &produce, s->y);
+      projection(s, A_LN, R, D, P(s, o.w1), &(*tw)[2], F, (*tw)[2].ln_v, nullptr, 1, s->h, s->h_lo, &consume2);
+      projection(s, A_H, R, F, P(s, o.w2), &(*tw)[3], D, P(s, o.b2), s->y, 0, s->ln, s->ln_lo, &produce, s->x);
+      continue;
     }
     projection(s, A_CTX, R, D, P(s, o.out_w), tw ? &(*tw)[1] : nullptr, D, P(s, o.out_b), s->x, 0, s->y, nullptr);
     launch_layernorm_dense(s->y, P(s, o.ln2_g), P(s, o.ln2_b), R, D, s->ln, s->tc ? s->ln_lo : nullptr, dstate, B,
@@ -432,7 +472,8 @@ void enqueue_head_last(litnice_b200_session *s, int B, int sl, const LoopState *
 
 // Weights are immutable during inference: build, once per load, the K-major
 // TF32 hi/lo copies [n, k] the tensor-core GEMM reads, and their tensor maps.
-void prepare_one(litnice_b200_session *s, TcWeight *tw, const float *w, int k, int n) {
+void prepare_one(litnice_b200_session *s, TcWeight *tw, const float *w, int k, int n, const float *ln_gamma = nullptr,
+                 const float *ln_beta = nullptr, const float *bias = nullptr) {
   tw->k = k;
   tw->n = n;
   tw->has64 = (k % TC_BK == 0) && (n % 64 == 0);
@@ -444,7 +485,14 @@ void prepare_one(litnice_b200_session *s, TcWeight *tw, const float *w, int k, i
     if (cudaMalloc(reinterpret_cast<void **>(&tw->hi), bytes) != cudaSuccess) throw std::bad_alloc();
     if (cudaMalloc(reinterpret_cast<void **>(&tw->lo), bytes) != cudaSuccess) throw std::bad_alloc();
   }
-  launch_transpose_split(w, k, n, tw->hi, tw->lo, s->st);
+  launch_transpose_split(w, k, n, tw->hi, tw->lo, s->st, ln_gamma);
+  if (ln_gamma != nullptr) {  // the LayerNorm in front of this product is folded into it
+    if (tw->ln_u == nullptr) {
+      if (cudaMalloc(reinterpret_cast<void **>(&tw->ln_u), (size_t)n * 4) != cudaSuccess) throw std::bad_alloc();
+      if (cudaMalloc(reinterpret_cast<void **>(&tw->ln_v), (size_t)n * 4) != cudaSuccess) throw std::bad_alloc();
+    }
+    launch_ln_fold_vectors(w, k, n, ln_gamma, ln_beta, bias, tw->ln_u, tw->ln_v, s->st);
+  }
   if (tw->has64) {
     tc_make_map(&tw->m64.hi, tw->hi, (unsigned long long)n, (unsigned long long)k, 64);
     tc_make_map(&tw->m64.lo, tw->lo, (unsigned long long)n, (unsigned long long)k, 64);
@@ -465,9 +513,14 @@ void prepare_tc_weights(litnice_b200_session *s) {
   s->tcw.resize(d.n_layers);
   for (int l = 0; l < d.n_layers; ++l) {
     const LayerOff &o = s->lay.layer[l];
-    prepare_one(s, &s->tcw[l][0], P(s, o.qkv_w), D, 3 * D);
+    if (s->ln_fold) {
+      prepare_one(s, &s->tcw[l][0], P(s, o.qkv_w), D, 3 * D, P(s, o.ln1_g), P(s, o.ln1_b), P(s, o.qkv_b));
+      prepare_one(s, &s->tcw[l][2], P(s, o.w1), D, F, P(s, o.ln2_g), P(s, o.ln2_b), P(s, o.b1));
+    } else {
+      prepare_one(s, &s->tcw[l][0], P(s, o.qkv_w), D, 3 * D);
+      prepare_one(s, &s->tcw[l][2], P(s, o.w1), D, F);
+    }
     prepare_one(s, &s->tcw[l][1], P(s, o.out_w), D, D);
-    prepare_one(s, &s->tcw[l][2], P(s, o.w1), D, F);
     prepare_one(s, &s->tcw[l][3], P(s, o.w2), F, D);
   }
   prepare_one(s, &s->tc_head, P(s, s->lay.lm_head), D, d.vocab_size);
@@ -576,6 +629,10 @@ int litnice_b200_session_create(const litnice_b200_dims *dims, int32_t max_strea
     // keeps the fp32 SIMT attention kernel.
     const char *ta_env = std::getenv("LITNICE_B200_TC_ATTN");
     s->tc_attn = s->tc && !(ta_env && ta_env[0] == '0') && attention_tc_supports(d.n_heads, d.d_model);
+    // LayerNorm folded into the projections that follow it: needs the tensor-core
+    // path and at most TC_STAT_SLOTS slots of 64 columns per row.
+    const char *lf_env = std::getenv("LITNICE_B200_LN_FOLD");
+    s->ln_fold = s->tc && !(lf_env && lf_env[0] == '0') && d.d_model / 64 <= TC_STAT_SLOTS;
     size_t lr = (size_t)(max_streams < 8 ? 8 : max_streams);
     if (s->tc) lr = (lr + TC_BM - 1) / TC_BM * TC_BM;
     s->xl_rows = (long long)lr;
@@ -627,6 +684,8 @@ void litnice_b200_session_destroy(litnice_b200_session *s) {
     for (auto &w : layer) {
       if (w.hi) cudaFree(w.hi);
       if (w.lo) cudaFree(w.lo);
+      if (w.ln_u) cudaFree(w.ln_u);
+      if (w.ln_v) cudaFree(w.ln_v);
     }
   if (s->tc_head.hi) cudaFree(s->tc_head.hi);
   if (s->tc_head.lo) cudaFree(s->tc_head.lo);
