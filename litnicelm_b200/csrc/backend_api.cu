@@ -13,6 +13,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <fstream>
+#include <map>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -27,11 +28,44 @@ struct Backend {
   DevErr *err_host = nullptr;  // host-mapped; kernels write, host reads after a sync
   DevErr *err_dev = nullptr;
   std::unordered_map<void *, void *> over_aligned;  // user pointer -> cudaMalloc base
+  std::map<uintptr_t, uint64_t> allocs;             // user pointer -> bytes, for every live allocation
   int ctx_iteration = 0, ctx_group = 0;
   long long launches = 0;
+
+  // Read-ahead for row-by-row read-back. The host reads logits one row per
+  // copy_device2host call (host_tensor_stage.hpp:101-125: s calls of V floats per
+  // token). When two small copies in a row walk forward through one allocation
+  // with nothing written to the device in between, the rest of that walk is
+  // fetched in one transfer into pinned memory and later calls are answered
+  // from there. `epoch` counts the table calls that may write device memory;
+  // the mirror is valid only for the epoch it was filled in.
+  unsigned long long epoch = 0;
+  bool read_ahead = true;        // LITNICE_B200_READ_AHEAD=0 turns it off
+  char *shadow = nullptr;        // pinned
+  uint64_t shadow_cap = 0;
+  uintptr_t shadow_src = 0;      // device range mirrored: [shadow_src, shadow_src + shadow_len)
+  uint64_t shadow_len = 0;
+  unsigned long long shadow_epoch = ~0ull;
+  uintptr_t last_src = 0;        // previous small copy
+  uint64_t last_bytes = 0;
+  unsigned long long last_epoch = ~0ull;
+  uint64_t next_window = 0;
+  long long d2h_calls = 0, d2h_served_from_shadow = 0;
 };
 
+constexpr uint64_t SHADOW_SMALL = 1ull << 20;    // copies up to this size are candidates
+constexpr uint64_t SHADOW_FIRST = 1ull << 20;    // first read-ahead window
+constexpr uint64_t SHADOW_MAX = 64ull << 20;     // largest window (pinned buffer size)
+
+// Every table entry except the read-only ones comes through here: whatever it
+// does may write device memory, which invalidates the read-back mirror.
 Backend *self(void *h) {
+  if (h == nullptr) throw std::invalid_argument("litnice_b200: null backend handle");
+  Backend *b = static_cast<Backend *>(h);
+  ++b->epoch;
+  return b;
+}
+Backend *self_reader(void *h) {  // entries that only read
   if (h == nullptr) throw std::invalid_argument("litnice_b200: null backend handle");
   return static_cast<Backend *>(h);
 }
@@ -89,6 +123,7 @@ void *api_create(uint32_t device_kind) {
   auto *b = new Backend();
   try {
     b->device = dev;
+    if (const char *env = std::getenv("LITNICE_B200_READ_AHEAD")) b->read_ahead = env[0] != '0';
     bind(b);
     cudaDeviceProp prop{};
     LB_CUDA(cudaGetDeviceProperties(&prop, dev));
@@ -116,11 +151,12 @@ void api_destroy(void *h) {
     cudaStreamDestroy(b->st);
   }
   if (b->err_host) cudaFreeHost(b->err_host);
+  if (b->shadow) cudaFreeHost(b->shadow);
   delete b;
 }
 
 uint32_t api_device(void *h) {
-  self(h);
+  self_reader(h);
   return 1u;
 }
 
@@ -135,6 +171,7 @@ void *api_alloc(void *h, uint64_t bytes, uint32_t alignment) {
     cudaError_t e = cudaMalloc(&p, bytes);
     if (e != cudaSuccess)
       throw std::runtime_error(std::string("litnice_b200::alloc failed: ") + cudaGetErrorString(e));
+    b->allocs[reinterpret_cast<uintptr_t>(p)] = bytes;
     return p;
   }
   cudaError_t e = cudaMalloc(&p, bytes + alignment);
@@ -142,6 +179,7 @@ void *api_alloc(void *h, uint64_t bytes, uint32_t alignment) {
     throw std::runtime_error(std::string("litnice_b200::alloc failed: ") + cudaGetErrorString(e));
   const uintptr_t a = (reinterpret_cast<uintptr_t>(p) + alignment - 1) & ~(uintptr_t)(alignment - 1);
   b->over_aligned[reinterpret_cast<void *>(a)] = p;
+  b->allocs[a] = bytes;
   return reinterpret_cast<void *>(a);
 }
 
@@ -150,6 +188,7 @@ void api_free(void *h, void *ptr) {
   if (ptr == nullptr) return;
   bind(b);
   LB_CUDA(cudaStreamSynchronize(b->st));
+  b->allocs.erase(reinterpret_cast<uintptr_t>(ptr));
   auto it = b->over_aligned.find(ptr);
   if (it != b->over_aligned.end()) {
     LB_CUDA(cudaFree(it->second));
@@ -170,17 +209,72 @@ void api_h2d(void *h, void *dst, const void *src, uint64_t bytes) {
 }
 
 void api_d2h(void *h, void *dst, const void *src, uint64_t bytes) {
-  Backend *b = self(h);
+  Backend *b = self_reader(h);
   if (bytes == 0) return;
   if (dst == nullptr || src == nullptr)
     throw std::invalid_argument("litnice_b200::copy_device2host: null pointer");
+  ++b->d2h_calls;
+  const uintptr_t a = reinterpret_cast<uintptr_t>(src);
+  if (b->shadow_epoch == b->epoch && a >= b->shadow_src && a + bytes <= b->shadow_src + b->shadow_len) {
+    std::memcpy(dst, b->shadow + (a - b->shadow_src), bytes);  // mirrored since the last device write
+    ++b->d2h_served_from_shadow;
+    b->last_src = a;
+    b->last_bytes = bytes;
+    b->last_epoch = b->epoch;
+    return;
+  }
   bind(b);
+  // Second small copy of a forward walk with no device write in between: fetch
+  // ahead, up to the end of the allocation the walk is in.
+  const bool walking = b->read_ahead && bytes <= SHADOW_SMALL && b->last_epoch == b->epoch &&
+                       b->last_bytes == bytes && a > b->last_src;
+  if (walking) {
+    auto it = b->allocs.upper_bound(a);
+    if (it != b->allocs.begin()) {
+      --it;
+      const uintptr_t end = it->first + it->second;
+      if (a + bytes <= end && b->last_src >= it->first) {
+        // a walk that outruns its window doubles the next one
+        uint64_t want = b->shadow_epoch == b->epoch ? b->next_window : SHADOW_FIRST;
+        if (want > SHADOW_MAX) want = SHADOW_MAX;
+        uint64_t len = end - a < want ? end - a : want;
+        if (len >= 2 * bytes) {
+          if (b->shadow_cap < len) {
+            if (b->shadow) cudaFreeHost(b->shadow);
+            b->shadow = nullptr;
+            b->shadow_cap = 0;
+            const uint64_t cap = len > SHADOW_FIRST ? SHADOW_MAX : SHADOW_FIRST;
+            if (cudaHostAlloc(reinterpret_cast<void **>(&b->shadow), cap, cudaHostAllocDefault) == cudaSuccess)
+              b->shadow_cap = cap;
+            else
+              (void)cudaGetLastError();
+          }
+          if (b->shadow_cap >= len) {
+            LB_CUDA(cudaMemcpyAsync(b->shadow, src, len, cudaMemcpyDeviceToHost, b->st));
+            sync_and_check(b);
+            b->shadow_src = a;
+            b->shadow_len = len;
+            b->shadow_epoch = b->epoch;
+            b->next_window = 2 * want;
+            std::memcpy(dst, b->shadow, bytes);
+            b->last_src = a;
+            b->last_bytes = bytes;
+            b->last_epoch = b->epoch;
+            return;
+          }
+        }
+      }
+    }
+  }
   LB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, b->st));
   sync_and_check(b);
+  b->last_src = a;
+  b->last_bytes = bytes;
+  b->last_epoch = b->epoch;
 }
 
 BackendMemoryInfo api_memory_info(void *h) {
-  Backend *b = self(h);
+  Backend *b = self_reader(h);
   bind(b);
   size_t fr = 0, tot = 0;
   LB_CUDA(cudaMemGetInfo(&fr, &tot));
@@ -543,7 +637,7 @@ void api_adamw_step(void *, LitniceView, LitniceView, LitniceView, LitniceView, 
 
 // device_backend.cpp:1426-1428: synchronous scalar read.
 float api_read_scalar(void *h, LitniceView x) {
-  Backend *b = self(h);
+  Backend *b = self_reader(h);
   require_gpu_f32(x, "litnice_b200::read_scalar_f32");
   bind(b);
   float v = 0.f;

@@ -113,24 +113,31 @@ class ParamLayout:
         return arena[off:off + 4 * n].view(np.float32).reshape(shape)
 
 
-def make_param_arena(d: ModelDims, seed: int, bias_std: float = 0.0) -> np.ndarray:
+def make_param_arena(d: ModelDims, seed: int, bias_std: float = 0.0, ln_std: float = 0.0) -> np.ndarray:
     """Seeded synthetic weights as a parameter-arena image (uint8).
 
     Matrices and embeddings are N(0, 0.02); LayerNorm gamma 1, beta 0; biases 0
-    (or N(0, bias_std) for the harder variant). The reference has no seeded
+    (or N(0, bias_std) for the harder variant; ln_std > 0 also draws gamma from
+    1 + N(0, ln_std) and beta from N(0, ln_std), from a generator of their own
+    so that the other values do not change). The reference has no seeded
     initialiser of its own for inference (it loads a checkpoint,
     inference.cpp:73-91), so both sides read the same image.
     """
     lay = ParamLayout.build(d)
     arena = np.zeros(lay.total_bytes, dtype=np.uint8)
     rng = np.random.default_rng(seed)
+    ln_rng = np.random.default_rng(seed + 7919)
     for name, (off, shape) in lay.slices.items():
         v = lay.view(arena, name)
         base = name.split(".")[-1]
         if base.endswith("gamma"):
             v[...] = 1.0
+            if ln_std > 0:
+                v[...] += ln_rng.normal(0.0, ln_std, size=shape).astype(np.float32)
         elif base.endswith("beta"):
             v[...] = 0.0
+            if ln_std > 0:
+                v[...] = ln_rng.normal(0.0, ln_std, size=shape).astype(np.float32)
         elif shape[0] == 1:  # biases
             if bias_std > 0:
                 v[...] = rng.normal(0.0, bias_std, size=shape).astype(np.float32)

@@ -267,3 +267,43 @@ def test_memory_info_and_alloc(be):
     p = be.alloc(1000, 1024)
     assert p % 1024 == 0
     assert be.api.supports_exec_context_iteration(be.h) == 1
+
+
+def test_row_by_row_read_back_sees_every_device_write(be):
+    """The reference reads logits one row per copy_device2host call
+    (host_tensor_stage.hpp:101-125); the plugin answers such a walk from one
+    read-ahead transfer. Every row must still be what the device holds at that
+    moment: after a host upload, after a kernel wrote, walking to the very end
+    of an allocation, and reading backwards."""
+    rows, cols = 1024, 96
+    rng = np.random.default_rng(11)
+    buf = Buffer(be, rows * cols * 4, rng=rng)
+    want = buf.host.view(np.float32).reshape(rows, cols).copy()
+
+    def row(r):
+        return be.download(buf.ptr, cols * 4, offset=r * cols * 4).view(np.float32)
+
+    for r in range(300):  # forward walk: served from the read-ahead after the second call
+        assert np.array_equal(row(r), want[r]), r
+    # a host upload invalidates what was fetched ahead
+    want[310:320] = rng.standard_normal((10, cols)).astype(np.float32)
+    be.upload(buf.ptr, want[310:320], offset=310 * cols * 4)
+    for r in range(300, 330):
+        assert np.array_equal(row(r), want[r]), r
+    # so does a kernel: fill rows 400..499 with a constant between two reads of the walk
+    for r in range(330, 350):
+        assert np.array_equal(row(r), want[r]), r
+    t = buf.view((100, cols), offset=400 * cols * 4)
+    be.call("fill", t, 2.5)
+    want[400:500] = 2.5
+    for r in range(350, 520):
+        assert np.array_equal(row(r), want[r]), r
+    # to the last row of the allocation, then backwards and at random
+    for r in range(900, rows):
+        assert np.array_equal(row(r), want[r]), r
+    for r in [1023, 1000, 5, 700, 699, 698, 0]:
+        assert np.array_equal(row(r), want[r]), r
+    # a walk with a stride larger than the row (column slice of a wider tensor)
+    for r in range(0, 1000, 7):
+        got = be.download(buf.ptr, 16, offset=r * cols * 4 + 32).view(np.float32)
+        assert np.array_equal(got, want[r, 8:12]), r

@@ -77,3 +77,22 @@ def test_unmodified_litnicelm_cli_infer_on_plugin(ref, tmp_path):
         assert len(outs[tag]) == 24
     assert "Loaded backend library" in p.stdout
     assert outs["cpu"] == outs["b200"]
+
+
+def test_reference_token_loop_on_plugin_config2_shape(ref):
+    """The reference's own loop (whole-context forward, one copy_device2host per
+    logits row, host-side argmax) at the config-2 shape on the plugin: same
+    tokens with and without the plugin's read-ahead for row-by-row read-back,
+    and the per-token times of both, for the record."""
+    d = formats.CONFIG_DIMS["c2"]
+    arena = formats.make_param_arena(d, 1002)
+    prompt = formats.zipf_prompt(d.vocab, 200, 4002)
+    runs = {}
+    for tag, env in (("read-ahead", {}), ("row copies", {"LITNICE_B200_READ_AHEAD": "0"})):
+        toks, _, secs, _ = ref.ref_run(d, arena, prompt, mode="generate", max_new=24, backend_library=LIB_PATH,
+                                       attention="fused_inplace", ffn="inplace_fused_bias_relu", threads_env=env)
+        runs[tag] = (toks, float(np.median(secs[2:])))
+    assert np.array_equal(runs["read-ahead"][0], runs["row copies"][0])
+    assert len(runs["read-ahead"][0]) == 24
+    for tag, (_, t) in runs.items():
+        print(f"reference host loop on the plugin, context ~212, {tag}: {1e3 * t:.2f} ms per token")
