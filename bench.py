@@ -375,23 +375,113 @@ def run_b200_arm(args, rank, local_rank, world):
         print(json.dumps(line), flush=True)
 
 
+def run_prefill_arm(args, rank, local_rank, world):
+    """Config 4: 32 sequences of 2048 tokens per GPU, one whole-context forward
+    each, output = the full next-token distribution per sequence
+    (inspect_distribution of the reference, inference.cpp:298-359). A step is one
+    such batch; the value is sequences per second."""
+    import torch
+    from litnicelm_b200.plugin import Session
+
+    os.environ["LITNICE_B200_DEVICE"] = str(local_rank)
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    d = formats.CONFIG_DIMS["c5"]
+    streams, s_len = 32, d.max_seq
+    arena = formats.make_param_arena(d, 1004)
+    ids = np.stack([formats.zipf_prompt(d.vocab, s_len, 2000 * 4 + rank * streams + i) for i in range(streams)])
+    peaks = load_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sess = Session(d, streams)
+    sess.load_params(arena)
+    for _ in range(args.warmup):
+        sess.inspect(ids)
+    clocks = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        clocks.start()
+    dev_ms, launches, e2e_s = 0.0, 0, 0.0
+    for _ in range(args.steps):
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        probs = sess.inspect(ids)               # host ids in, host probabilities out
+        e2e_s += time.perf_counter() - t0
+        st = sess.stats()
+        dev_ms += st.device_ms                  # CUDA events around the forward, ids already on the device
+        launches += st.kernel_launches
+    barrier()
+    clock_info = clocks.stop() if rank == 0 else None
+    dev_ms = max_over_ranks(dev_ms)
+    e2e_s = max_over_ranks(e2e_s)
+    if rank == 0:
+        flops = algorithmic_flops(d, streams, s_len) * args.steps
+        tflops = flops / (dev_ms * 1e-3) / 1e12
+        line = {
+            "metric": "prefill sequences/s (whole-context forward, full next-token distribution)",
+            "value": world * streams * args.steps / (dev_ms * 1e-3), "unit": "sequences/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": (f"c4: L{d.n_layers} H{d.n_heads} D{d.d_model} F{d.d_ff} V{d.vocab} S{d.max_seq}, "
+                                    f"{streams} sequences of {s_len} tokens per GPU"),
+                       "l2": "256 MB buffer written between timed steps (L2 flush)"},
+            "e2e": {"value": world * streams * args.steps / e2e_s, "unit": "sequences/s",
+                    "h2d_bytes_per_step": int(ids.nbytes), "d2h_bytes_per_step": int(probs.nbytes)},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "kernel": "whole forward (projections + attention)", "achieved": tflops,
+                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tflops / peaks["bf16_tflops"],
+                         "peak_source": f"bf16 burst, {peaks['source']}", "ceiling_frac_3xtf32": 1.0 / 6.0,
+                         "traffic": None,
+                         "note": "algorithmic flops of the step (projections on all rows, causal-useful attention, "
+                                 "head on the last rows) / device time of the step"},
+            "cpu_baseline": None, "clocks": clock_info,
+            "probability_row_sums": [float(probs[0].sum()), float(probs[-1].sum())],
+        }
+        print(json.dumps(line), flush=True)
+    sess.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
+        if args.workload == "c4":
+            ap.error("the prefill workload c4 has no reference arm; use c1, c2, c3 or c5")
         run_reference_arm(args, rank, world)
         return
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "c4":
+        run_prefill_arm(args, rank, local_rank, world)
+        return
     run_b200_arm(args, rank, local_rank, world)
 
 
