@@ -157,15 +157,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
       }
     }
     __syncwarp();
+    // K(t) may be overwritten once S(t-1) has completed, V^T(t) once P V(t-1) has. The MMA warp issues
+    // S(t+1) ahead of P V(t), so in time order: S(0), S(1), PV(0), S(2), PV(1), ... and the loads follow
+    // that order: K runs one tile further ahead than V^T.
     int k_issued = 0, v_issued = 0;
-    for (int it = 0; it < ntiles; ++it) {
-      const int k0 = (kt_begin + it) * TA_BK;
-      if (it > 0) {  // the S MMAs of the previous tile have read K
-        const bool ok = mbar_wait_warp(s_full, (unsigned)(it - 1) & 1u, abort_flag, err, 11);
-        __syncwarp();
-        if (!ok) break;
-      }
+    auto load_k = [&](int it) {
       if (lane == 0) {
+        const int k0 = (kt_begin + it) * TA_BK;
         mbar_expect_tx(k_full, (unsigned)TA_K_BYTES);
         for (int kb = 0; kb < TA_DH / 32; ++kb) {
           tma_load_2d(base + TA_K_OFF + kb * TA_SLAB, &map_qk_hi, d_model + h * TA_DH + kb * 32, row0 + k0, k_full);
@@ -175,12 +173,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
       }
       __syncwarp();
       ++k_issued;
-      if (it > 0) {  // the PV MMAs of the previous tile have read V^T
-        const bool ok = mbar_wait_warp(o_full, (unsigned)(it - 1) & 1u, abort_flag, err, 12);
-        __syncwarp();
-        if (!ok) break;
-      }
+    };
+    auto load_v = [&](int it) {
       if (lane == 0) {
+        const int k0 = (kt_begin + it) * TA_BK;
         mbar_expect_tx(v_full, (unsigned)TA_V_BYTES);
         for (int kb = 0; kb < TA_BK / 32; ++kb) {
           tma_load_2d(base + TA_V_OFF + kb * TA_VSLAB, &map_vt_hi, k0 + kb * 32, b * d_model + h * TA_DH, v_full);
@@ -190,6 +186,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
       }
       __syncwarp();
       ++v_issued;
+    };
+    load_k(0);
+    load_v(0);
+    bool ok = true;
+    if (ntiles > 1) {
+      ok = mbar_wait_warp(s_full, 0u, abort_flag, err, 11);
+      if (ok) load_k(1);
+    }
+    for (int it = 0; it + 1 < ntiles && ok; ++it) {
+      if (it + 2 < ntiles) {  // S(it+1) has read K
+        ok = mbar_wait_warp(s_full, (unsigned)(it + 1) & 1u, abort_flag, err, 11);
+        if (!ok) break;
+        load_k(it + 2);
+      }
+      ok = mbar_wait_warp(o_full, (unsigned)it & 1u, abort_flag, err, 12);  // P V(it) has read V^T
+      if (!ok) break;
+      load_v(it + 1);
     }
     if (*abort_flag) {
       // let copies already in flight land before the CTA's shared memory goes away
@@ -329,6 +342,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
       ok = mbar_wait_warp(s_full, ph, abort_flag, err, 18);
       if (!ok) break;
       if (stamp && it == 0 && warp == 2 && lane == 0) timeline[3] = global_timer();
+      if (stamp && nchunks == 1 && it >= 1 && it <= 4 && warp == 2 && lane == 0) timeline[11 + it] = global_timer();
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float p[64];
       {
