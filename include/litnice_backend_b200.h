@@ -247,7 +247,9 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
  * (ReLU when relu != 0), i.e. gemm_ranked_matrix_rhs followed by add_bias_rowwise
  * / add_bias_relu_rowwise / add (device_backend.cpp:1112-1131, 840-908, 752-813).
  * engine 0: fp32 SIMT kernel; engine 1: tcgen05 tensor-core kernel with the
- * three-product TF32 split (needs k % 32 == 0 and n % 64 == 0). Allocates and
+ * three-product TF32 split (needs k % 32 == 0 and n % 64 == 0); engine 2: the
+ * same kernel on fp16 pairs with one power-of-two scale per 64 consecutive k of
+ * a row (k % 64 == 0), the operand format of the native loop. Allocates and
  * frees its own device buffers; meant for checking the two engines against
  * each other and against the CPU. */
 int litnice_b200_projection_host(int32_t engine, const float *a, int32_t m, int32_t k, const float *w, int32_t n,

@@ -80,7 +80,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
                     const __grid_constant__ CUtensorMap map_vt_hi, const __grid_constant__ CUtensorMap map_vt_lo,
                     float *__restrict__ ctx_hi, float *__restrict__ ctx_lo, int s_cap, int d_model, float scale_log2e,
                     int kc, float *__restrict__ part, int *__restrict__ counters, const LoopState *state,
-                    DevErr *err, unsigned long long *timeline) {
+                    DevErr *err, unsigned long long *timeline, TcPairF16 ctx_f16) {
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char *base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -500,13 +500,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
             make_float4(o[j] * inv, o[j + 1] * inv, o[j + 2] * inv, o[j + 3] * inv);
     }
     asm volatile("bar.sync 1, %0;" ::"n"(TA_SOFTMAX_THREADS) : "memory");
+    finish = __all_sync(0xffffffffu, finish);  // whole warps store or skip together (the fp16 store shuffles)
     if (finish) {
       const int t2 = threadIdx.x - 64;
 #pragma unroll
       for (int i = 0; i < TA_BQ * TA_DH / 4 / TA_SOFTMAX_THREADS; ++i) {
         const int u = t2 + i * TA_SOFTMAX_THREADS;
         const int row = u >> 4, c4 = u & 15;
-        if (q0 + row < s) {
+        if (ctx_f16.hi != nullptr) {
+          // fp16 pair with one scale per row of this head's 64 columns (16 lanes = one block)
+          const bool active = q0 + row < s;
+          const float4 v = active ? *reinterpret_cast<const float4 *>(stage + row * TA_STAGE_LD + c4 * 4)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+          const long long grow = (long long)row0 + q0 + row;
+          const long long off = grow * d_model + h * TA_DH + c4 * 4;
+          f16_store_block(v, active, ctx_f16.hi + off, ctx_f16.lo + off,
+                          ctx_f16.inv_scale + grow * (d_model / TC_F16_SLOT) + h);
+        } else if (q0 + row < s) {
           const float4 v = *reinterpret_cast<const float4 *>(stage + row * TA_STAGE_LD + c4 * 4);
           float4 hh, ll;
           split_tf32(v.x, hh.x, ll.x);
@@ -571,7 +581,7 @@ AttentionPlan attention_tc_plan(int n_streams, int s, int n_heads) {
 
 void launch_attention_tc(const TcMatrix &qk, const TcMatrix &vt, float *ctx_hi, float *ctx_lo, int n_streams, int s,
                          int n_heads, int d_model, float *scratch, int *counters, const LoopState *state,
-                         DevErr *err, cudaStream_t st, unsigned long long *timeline) {
+                         DevErr *err, cudaStream_t st, unsigned long long *timeline, const TcPairF16 *ctx_f16) {
   if (!attention_tc_supports(n_heads, d_model))
     throw std::invalid_argument("litnice_b200: tensor-core attention needs head_dim 64");
   const AttentionPlan plan = attention_tc_plan(n_streams, s, n_heads);
@@ -587,7 +597,7 @@ void launch_attention_tc(const TcMatrix &qk, const TcMatrix &vt, float *ctx_hi, 
   dim3 grid(plan.ctas_per_head, n_heads, n_streams);
   launch_pdl(attention_tc_kernel, grid, dim3(TA_THREADS), (size_t)TA_SMEM, st, g_pdl_enabled, qk.hi, qk.lo, vt.hi,
              vt.lo, ctx_hi, ctx_lo, s, d_model, (float)(1.4426950408889634 / sqrt((double)TA_DH)), plan.kc, scratch, counters, state, err,
-             timeline);
+             timeline, ctx_f16 ? *ctx_f16 : TcPairF16{});
 }
 
 }  // namespace lb

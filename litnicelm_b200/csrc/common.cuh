@@ -181,7 +181,7 @@ struct LoopState {
 void launch_embed_pos(const float *tok_emb, const float *pos_emb, const int *ids, int ids_ld,
                       const LoopState *state, int n_streams, int s_host, int d, int vocab,
                       float *x, DevErr *err, cudaStream_t st, float *x_hi = nullptr, float *x_lo = nullptr,
-                      double2 *stats = nullptr);
+                      double2 *stats = nullptr, const struct TcPairF16 *x_f16 = nullptr);
 void launch_gather_last_ln(const float *x, const float *gamma, const float *beta,
                            const LoopState *state, int n_streams, int s_host, int d, float *out,
                            float *out_lo, cudaStream_t st);

@@ -16,7 +16,8 @@ __global__ void embed_pos_kernel(const float *__restrict__ tok_emb,
                                  const float *__restrict__ pos_emb, const int *__restrict__ ids,
                                  int ids_ld, const LoopState *state, int n_streams, int s_cap, int d,
                                  int vocab, float *__restrict__ x, float *__restrict__ x_hi,
-                                 float *__restrict__ x_lo, double2 *__restrict__ stats, DevErr *err) {
+                                 float *__restrict__ x_lo, double2 *__restrict__ stats, TcPairF16 x_f16,
+                                 DevErr *err) {
   pdl_launch_dependents();
   pdl_wait();
   const int s = state ? state->s : s_cap;
@@ -56,6 +57,9 @@ __global__ void embed_pos_kernel(const float *__restrict__ tok_emb,
         reinterpret_cast<float4 *>(x_lo + r * d)[c] = ll;
       }
     }
+    if (x_f16.hi != nullptr)  // or the fp16 pair, one scale per block of 64 columns
+      f16_store_block(v, valid, x_f16.hi + r * d + c * 4, x_f16.lo + r * d + c * 4,
+                      x_f16.inv_scale + r * (d / TC_F16_SLOT) + (c >> 4));
     if (stats != nullptr) {  // (sum x, sum x^2) per slot of 64 columns, for a LayerNorm folded into that projection
       double sx = ((double)v.x + (double)v.y) + ((double)v.z + (double)v.w);
       double sxx = ((double)v.x * v.x + (double)v.y * v.y) + ((double)v.z * v.z + (double)v.w * v.w);
@@ -124,11 +128,12 @@ __global__ void advance_state_kernel(LoopState *state) {
 
 void launch_embed_pos(const float *tok_emb, const float *pos_emb, const int *ids, int ids_ld,
                       const LoopState *state, int n_streams, int s_host, int d, int vocab,
-                      float *x, DevErr *err, cudaStream_t st, float *x_hi, float *x_lo, double2 *stats) {
+                      float *x, DevErr *err, cudaStream_t st, float *x_hi, float *x_lo, double2 *stats,
+                      const TcPairF16 *x_f16) {
   const long long rows = (long long)n_streams * s_host;
   if (rows <= 0) return;
   launch_pdl(embed_pos_kernel, dim3((unsigned)rows), dim3(d >= 512 ? 128 : 32), 0, st, g_pdl_enabled, tok_emb, pos_emb,
-             ids, ids_ld, state, n_streams, s_host, d, vocab, x, x_hi, x_lo, stats, err);
+             ids, ids_ld, state, n_streams, s_host, d, vocab, x, x_hi, x_lo, stats, x_f16 ? *x_f16 : TcPairF16{}, err);
 }
 
 void launch_gather_last_ln(const float *x, const float *gamma, const float *beta,

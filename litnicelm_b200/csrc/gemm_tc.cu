@@ -56,12 +56,18 @@ struct TcSmem {
 constexpr int TC_CHUNK = LB_TC_CHUNK;  // k-blocks (of 32) per TMEM accumulation chain
 
 
-template <int BN, int STAGES>
+// F16: operands are fp16 pairs with block scales (see TcPairF16) instead of TF32
+// pairs: a k-block is 64 elements (still one 128-byte row per tile row), the
+// instructions are kind::f16 with K = 16, and the drain multiplies each chain by
+// a_inv_scale[row][k-block] * b_inv_scale.
+template <int BN, int STAGES, bool F16>
 __global__ void __launch_bounds__(tc_threads(BN), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                TcEpilogue ep, int m, int n, int k, int splits, float *__restrict__ part,
-               int *__restrict__ counters, DevErr *err) {
+               int *__restrict__ counters, DevErr *err, const float *__restrict__ a_inv_scale,
+               const float *__restrict__ b_inv_scale) {
+  constexpr int KBE = F16 ? TC_F16_SLOT : TC_BK;  // k elements per k-block
   using L = TcSmem<BN, STAGES>;
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
@@ -82,7 +88,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * TC_BM;
   // With split-k (gridDim.z CTAs per tile) this CTA owns k-blocks [kb0, kb0 + kblocks).
-  const int kb_total = k / TC_BK;
+  const int kb_total = k / KBE;
   const int kb_per = (kb_total + splits - 1) / splits;
   const int kb0 = blockIdx.z * kb_per;
   const int kblocks = min(kb_per, kb_total - kb0);
@@ -131,7 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     if (lane == 0) {
       for (int kb = 0; kb < pre; ++kb) {
         const unsigned stage = base + (unsigned)kb * L::STAGE_BYTES;
-        const int kx = (kb0 + kb) * TC_BK;
+        const int kx = (kb0 + kb) * KBE;
         mbar_expect_tx(full_bar(kb), (unsigned)L::STAGE_BYTES);
         tma_load_2d(stage + 2 * L::A_BYTES, &map_b_hi, kx, n0, full_bar(kb));
         tma_load_2d(stage + 2 * L::A_BYTES + L::B_BYTES, &map_b_lo, kx, n0, full_bar(kb));
@@ -141,7 +147,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     if (lane == 0) {
       for (int kb = 0; kb < pre; ++kb) {
         const unsigned stage = base + (unsigned)kb * L::STAGE_BYTES;
-        const int kx = (kb0 + kb) * TC_BK;
+        const int kx = (kb0 + kb) * KBE;
         tma_load_2d(stage, &map_a_hi, kx, m0, full_bar(kb));
         tma_load_2d(stage + L::A_BYTES, &map_a_lo, kx, m0, full_bar(kb));
       }
@@ -158,7 +164,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
       if (lane == 0) {
         const unsigned stage = base + (unsigned)s * L::STAGE_BYTES;
         mbar_expect_tx(full_bar(s), (unsigned)L::STAGE_BYTES);
-        const int kx = (kb0 + kb) * TC_BK;
+        const int kx = (kb0 + kb) * KBE;
         tma_load_2d(stage, &map_a_hi, kx, m0, full_bar(s));
         tma_load_2d(stage + L::A_BYTES, &map_a_lo, kx, m0, full_bar(s));
         tma_load_2d(stage + 2 * L::A_BYTES, &map_b_hi, kx, n0, full_bar(s));
@@ -178,7 +184,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----
-    const unsigned idesc = umma_idesc_tf32(BN);
+    const unsigned idesc = F16 ? umma_idesc_f16(BN) : umma_idesc_tf32(BN);
+    auto mma = [&](unsigned d, unsigned long long a, unsigned long long b, unsigned acc) {
+      if (F16) tc_mma_f16(d, a, b, idesc, acc);
+      else tc_mma_tf32(d, a, b, idesc, acc);
+    };
     bool ok = true;
     int committed = -1;  // last chunk whose completion was committed to a tmem_full barrier
     for (int c = 0; c < nchunks && ok; ++c) {
@@ -208,13 +218,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
           for (int ks = 0; ks < TC_BK / 8; ++ks) {
             const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);  // 8 fp32 = 32 bytes along k
             const unsigned first = (kb == c * TC_CHUNK && ks == 0) ? 0u : 1u;   // a chunk starts from zero
-            tc_mma_tf32(tmem_d, a_lo + adv, b_hi + adv, idesc, first);
-            tc_mma_tf32(tmem_d, a_hi + adv, b_lo + adv, idesc, 1u);
+            mma(tmem_d, a_lo + adv, b_hi + adv, first);
+            mma(tmem_d, a_hi + adv, b_lo + adv, 1u);
           }
 #pragma unroll
           for (int ks = 0; ks < TC_BK / 8; ++ks) {
             const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);
-            tc_mma_tf32(tmem_d, a_hi + adv, b_hi + adv, idesc, 1u);
+            mma(tmem_d, a_hi + adv, b_hi + adv, 1u);
           }
           tc_commit(empty_bar(s));  // the stage is free once these MMAs have read it
         }
@@ -254,12 +264,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     float acc[CW];
 #pragma unroll
     for (int j = 0; j < CW; ++j) acc[j] = 0.f;
+    // fp16 pairs: every chain (one 64-wide k-block) carries the product of its operands' block scales
+    static_assert(!F16 || TC_CHUNK == 1, "one scale per accumulation chain");
+    const float *a_inv_row = F16 ? a_inv_scale + (long long)min(row, m - 1) * kb_total + kb0 : nullptr;
+    const float b_inv = F16 ? *b_inv_scale : 1.f;
+    float chain_scale = F16 ? a_inv_row[0] * b_inv : 1.f;
     bool ok = true;
     for (int c = 0; c < nchunks && ok; ++c) {
       const int buf = c % NBUF;
       ok = mbar_wait(tmem_full_bar(buf), (unsigned)(c / NBUF) & 1u, abort_flag, err, 3);
       __syncwarp();
       if (!ok) break;
+      const float sc = chain_scale;
+      if (F16 && c + 1 < nchunks) chain_scale = a_inv_row[c + 1] * b_inv;  // in flight during this chain's adds
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
       for (int c0 = 0; c0 < CW; c0 += 32) {
@@ -268,7 +285,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
         tc_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN + col0 + c0), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[c0 + j] = __fadd_rn(acc[c0 + j], __uint_as_float(r[j]));
+        for (int j = 0; j < 32; ++j)
+          acc[c0 + j] = F16 ? __fmaf_rn(__uint_as_float(r[j]), sc, acc[c0 + j])
+                            : __fadd_rn(acc[c0 + j], __uint_as_float(r[j]));
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -337,15 +356,25 @@ __global__ void transpose_split_kernel(const float *__restrict__ w, int k, int n
 // sum_k beta[k] W[k,n] + bias[n]; sums in double.
 __global__ void ln_fold_vectors_kernel(const float *__restrict__ w, int k, int n, const float *__restrict__ gamma,
                                        const float *__restrict__ beta, const float *__restrict__ bias,
-                                       float *__restrict__ u, float *__restrict__ v) {
+                                       float *__restrict__ u, float *__restrict__ v,
+                                       const int *__restrict__ f16_amax_bits) {
   const int col = blockIdx.x * blockDim.x + threadIdx.x;
   if (col >= n) return;
+  float inv = 1.f;
+  const float scale = f16_amax_bits ? f16_block_scale(__int_as_float(*f16_amax_bits), &inv) : 1.f;
   double su = 0.0, sv = 0.0;
   for (int kk = 0; kk < k; ++kk) {
     const float wv = w[(long long)kk * n + col];
-    float hh, ll;
-    split_tf32(__fmul_rn(gamma[kk], wv), hh, ll);
-    su += (double)hh + (double)ll;
+    const float sw = __fmul_rn(gamma[kk], wv);
+    if (f16_amax_bits) {  // the fp16 pair transpose_split_f16_kernel stores
+      const float a = sw * scale;
+      const __half h = __float2half_rn(a);
+      su += ((double)__half2float(h) + (double)__half2float(__float2half_rn(a - __half2float(h)))) * (double)inv;
+    } else {
+      float hh, ll;
+      split_tf32(sw, hh, ll);
+      su += (double)hh + (double)ll;
+    }
     sv += (double)beta[kk] * (double)wv;
   }
   u[col] = (float)su;
@@ -373,20 +402,22 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool F16>
 void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const TcEpilogue &ep, int splits,
-                float *part, int *counters, DevErr *err, cudaStream_t st) {
+                float *part, int *counters, DevErr *err, cudaStream_t st, const float *a_inv_scale = nullptr,
+                const float *b_inv_scale = nullptr) {
   using L = TcSmem<BN, STAGES>;
   static bool configured[64] = {};
   int dev = 0;
   LB_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    LB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    LB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 L::TOTAL));
     configured[dev] = true;
   }
   dim3 grid(n / BN, (m + TC_BM - 1) / TC_BM, splits);
-  launch_pdl(gemm_tc_kernel<BN, STAGES>, grid, dim3(tc_threads(BN)), (size_t)L::TOTAL, st, g_pdl_enabled, a.hi, a.lo, b.hi,
-             b.lo, ep, m, n, k, splits, part, counters, err);
+  launch_pdl(gemm_tc_kernel<BN, STAGES, F16>, grid, dim3(tc_threads(BN)), (size_t)L::TOTAL, st, g_pdl_enabled, a.hi,
+             a.lo, b.hi, b.lo, ep, m, n, k, splits, part, counters, err, a_inv_scale, b_inv_scale);
 }
 
 }  // namespace
@@ -410,7 +441,24 @@ void tc_make_map(CUtensorMap *map, const float *base, unsigned long long rows, u
     throw std::runtime_error("litnice_b200: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
 }
 
-TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256) {
+void tc_make_map_f16(CUtensorMap *map, const __half *base, unsigned long long rows, unsigned long long k,
+                     unsigned box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) throw std::runtime_error("litnice_b200: cuTensorMapEncodeTiled is not available");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || k % TC_F16_SLOT != 0 || box_rows == 0 || box_rows > 256)
+    throw std::invalid_argument("litnice_b200: fp16 tensor map operand must be 16-byte aligned with k % 64 == 0");
+  const cuuint64_t dims[2] = {k, rows};
+  const cuuint64_t strides[1] = {k * 2};  // bytes between rows
+  const cuuint32_t box[2] = {(cuuint32_t)TC_F16_SLOT, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw std::runtime_error("litnice_b200: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+}
+
+TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256, int k_block) {
   TcPlan p{};
   const long long mt = (m + TC_BM - 1) / TC_BM;
   // One thread issues every tcgen05.mma of a CTA, at most one per ~40 ns, and a
@@ -420,7 +468,7 @@ TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256) {
   p.bn = (has128 && (!has64 || mt * (n / 128) >= 74)) ? 128 : 64;
   if (has256 && mt * (n / 256) >= 2 * 148) p.bn = 256;
   const long long ctas = mt * (n / p.bn);
-  const int kb = k / TC_BK;
+  const int kb = k / k_block;
   // Few tiles (a short single stream): cut k over several CTAs per tile so the
   // serial k loop shortens, keeping one wave and at least 4 k-blocks per CTA.
   int splits = 1;
@@ -445,9 +493,106 @@ void launch_gemm_tc(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, c
     throw std::invalid_argument("litnice_b200: tensor-core GEMM needs k % 32 == 0 and n % bn == 0");
   if (plan.splits > 1 && (scratch == nullptr || counters == nullptr))
     throw std::invalid_argument("litnice_b200: split-k tensor-core GEMM needs scratch");
-  if (bn == 256) launch_cfg<256, 2>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st);
-  else if (bn == 128) launch_cfg<128, 3>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st);
-  else launch_cfg<64, 4>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st);
+  if (bn == 256) launch_cfg<256, 2, false>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st);
+  else if (bn == 128) launch_cfg<128, 3, false>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st);
+  else launch_cfg<64, 4, false>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st);
+}
+
+void launch_gemm_tc_f16(const TcMatrix &a, const float *a_inv_scale, const TcMatrix &b, const float *b_inv_scale,
+                        int m, int n, int k, const TcPlan &plan, const TcEpilogue &ep, float *scratch, int *counters,
+                        DevErr *err, cudaStream_t st) {
+  if (m <= 0) return;
+  const int bn = plan.bn;
+  if (k < TC_F16_SLOT || k % TC_F16_SLOT != 0 || (bn != 64 && bn != 128 && bn != 256) || n % bn != 0)
+    throw std::invalid_argument("litnice_b200: fp16-pair tensor-core GEMM needs k % 64 == 0 and n % bn == 0");
+  if (a_inv_scale == nullptr || b_inv_scale == nullptr)
+    throw std::invalid_argument("litnice_b200: fp16-pair tensor-core GEMM needs the operands' scales");
+  if (plan.splits > 1 && (scratch == nullptr || counters == nullptr))
+    throw std::invalid_argument("litnice_b200: split-k tensor-core GEMM needs scratch");
+  if (bn == 256)
+    launch_cfg<256, 2, true>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st, a_inv_scale, b_inv_scale);
+  else if (bn == 128)
+    launch_cfg<128, 3, true>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st, a_inv_scale, b_inv_scale);
+  else
+    launch_cfg<64, 4, true>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st, a_inv_scale, b_inv_scale);
+}
+
+// ---- fp16-pair operand preparation --------------------------------------------------
+
+namespace {
+
+// One warp per row: per block of 64 columns the scale and the pair.
+__global__ void split_f16_kernel(const float *__restrict__ x, long long rows, int k, __half *__restrict__ hi,
+                                 __half *__restrict__ lo, float *__restrict__ inv_scale) {
+  const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int n4 = k >> 2;  // k % 64 == 0: whole warps of float4s, two blocks per pass
+  for (int c = lane; c < n4; c += 32) {
+    const float4 v = reinterpret_cast<const float4 *>(x + row * k)[c];
+    f16_store_block(v, true, hi + row * k + c * 4, lo + row * k + c * 4, inv_scale + row * (k / 64) + (c >> 4));
+  }
+}
+
+// Largest magnitude of W (rows optionally scaled) -> *amax_bits (float bits; non-negative floats order as ints).
+__global__ void amax_kernel(const float *__restrict__ w, int k, int n, const float *__restrict__ row_scale,
+                            int *__restrict__ amax_bits) {
+  float am = 0.f;
+  const long long total = (long long)k * n;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    float v = w[i];
+    if (row_scale != nullptr) v = __fmul_rn(row_scale[i / n], v);
+    am = fmaxf(am, fabsf(v));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+  if ((threadIdx.x & 31) == 0) atomicMax(amax_bits, __float_as_int(am));
+}
+
+// W [k, n] row-major -> K-major fp16 pair [n, k] under the matrix's one scale; 32 x 32 tiles through shared memory.
+__global__ void transpose_split_f16_kernel(const float *__restrict__ w, int k, int n, __half *__restrict__ wt_hi,
+                                           __half *__restrict__ wt_lo, const float *__restrict__ row_scale,
+                                           const int *__restrict__ amax_bits, float *__restrict__ inv_scale_out) {
+  __shared__ float tile[32][33];
+  float inv;
+  const float scale = f16_block_scale(__int_as_float(*amax_bits), &inv);
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && threadIdx.y == 0) *inv_scale_out = inv;
+  const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int kk = k0 + r, nn = n0 + threadIdx.x;
+    float v = (kk < k && nn < n) ? w[(long long)kk * n + nn] : 0.f;
+    if (row_scale != nullptr && kk < k) v = __fmul_rn(row_scale[kk], v);
+    tile[r][threadIdx.x] = v;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int nn = n0 + r, kk = k0 + threadIdx.x;
+    if (nn < n && kk < k) {
+      const float a = tile[threadIdx.x][r] * scale;
+      const __half h = __float2half_rn(a);
+      wt_hi[(long long)nn * k + kk] = h;
+      wt_lo[(long long)nn * k + kk] = __float2half_rn(a - __half2float(h));
+    }
+  }
+}
+
+}  // namespace
+
+void launch_split_f16(const float *x, long long rows, int k, const TcPairF16 &out, cudaStream_t st) {
+  if (rows <= 0) return;
+  if (k % TC_F16_SLOT != 0) throw std::invalid_argument("litnice_b200: fp16 pairs need k % 64 == 0");
+  split_f16_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(x, rows, k, out.hi, out.lo, out.inv_scale);
+  LB_LAUNCH_CHECK();
+}
+
+void launch_transpose_split_f16(const float *w, int k, int n, __half *wt_hi, __half *wt_lo, float *inv_scale_dev,
+                                cudaStream_t st, const float *row_scale, int *amax_scratch) {
+  LB_CUDA(cudaMemsetAsync(amax_scratch, 0, sizeof(int), st));
+  amax_kernel<<<296, 256, 0, st>>>(w, k, n, row_scale, amax_scratch);
+  LB_LAUNCH_CHECK();
+  dim3 grid((n + 31) / 32, (k + 31) / 32), block(32, 8);
+  transpose_split_f16_kernel<<<grid, block, 0, st>>>(w, k, n, wt_hi, wt_lo, row_scale, amax_scratch, inv_scale_dev);
+  LB_LAUNCH_CHECK();
 }
 
 void launch_split_tf32(const float *x, float *hi, float *lo, long long count, cudaStream_t st) {
@@ -465,8 +610,8 @@ void launch_transpose_split(const float *w, int k, int n, float *wt_hi, float *w
 }
 
 void launch_ln_fold_vectors(const float *w, int k, int n, const float *gamma, const float *beta, const float *bias,
-                            float *u, float *v, cudaStream_t st) {
-  ln_fold_vectors_kernel<<<(n + 127) / 128, 128, 0, st>>>(w, k, n, gamma, beta, bias, u, v);
+                            float *u, float *v, cudaStream_t st, const int *f16_amax_bits) {
+  ln_fold_vectors_kernel<<<(n + 127) / 128, 128, 0, st>>>(w, k, n, gamma, beta, bias, u, v, f16_amax_bits);
   LB_LAUNCH_CHECK();
 }
 

@@ -9,6 +9,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 #include "common.cuh"
 
@@ -18,8 +19,21 @@ constexpr int TC_BM = 128;  // rows per CTA (one UMMA M=128 tile)
 constexpr int TC_BK = 32;   // fp32 elements per k-block = one 128-byte swizzle row
 constexpr int TC_STAT_SLOTS = 32;  // row-statistics slots of 64 columns per row (rows up to 2048 wide)
 
-struct TcMatrix {  // one split operand: two tensor maps over K-major fp32 arrays
+struct TcMatrix {  // one split operand: two tensor maps over K-major arrays (fp32 TF32 pairs or fp16 pairs)
   CUtensorMap hi, lo;
+};
+
+// Second operand format: x = (hi + lo) / scale with hi, lo fp16 and scale a power
+// of two chosen per block of 64 consecutive k (per row for activations, one for a
+// whole weight matrix) so that the block's largest magnitude lands in [2^12, 2^13).
+// hi = fp16(x * scale), lo = fp16(x * scale - hi): 22 significant bits like a TF32
+// pair, but an fp16 instruction covers 16 of k at twice the TF32 rate and the
+// operands take half the bytes. Products are formed on scaled operands; the drain
+// multiplies every 64-wide accumulation chain by the two inverse scales.
+constexpr int TC_F16_SLOT = 64;  // k elements per scale block = one 128-byte swizzle row of fp16
+struct TcPairF16 {  // activations in that format
+  __half *hi = nullptr, *lo = nullptr;  // [rows, k]
+  float *inv_scale = nullptr;           // [rows, k / 64]
 };
 
 struct TcEpilogue {
@@ -29,6 +43,7 @@ struct TcEpilogue {
   float *c = nullptr;               // [M, N] dense fp32 result (may be null)
   float *c_hi = nullptr;            // optional split result for a following GEMM
   float *c_lo = nullptr;
+  TcPairF16 c_f16;                  // optional fp16-pair result (n % 64 == 0) for a following GEMM
   // Optional transposed store of the columns from vt_col0 on (the V third of a
   // QKV projection) for the tensor-core attention, which wants V K-major:
   // element (row r = stream * s + t, column vt_col0 + c) goes, split, to
@@ -66,6 +81,9 @@ bool tc_runtime_available();
 // box_rows x 32 elements and the 128-byte swizzle the UMMA descriptors expect.
 void tc_make_map(CUtensorMap *map, const float *base, unsigned long long rows, unsigned long long k,
                  unsigned box_rows);
+// The same over an fp16 array, boxes of box_rows x 64 elements (k % 64 == 0).
+void tc_make_map_f16(CUtensorMap *map, const __half *base, unsigned long long rows, unsigned long long k,
+                     unsigned box_rows);
 
 // How one product is tiled: tile width (64, 128 or 256 columns), how many CTAs share
 // the k range of a tile, and the scratch that sharing needs (floats of partial
@@ -77,18 +95,73 @@ struct TcPlan {
   size_t scratch_floats;
   size_t counters;
 };
-TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256);
+// k_block: k elements per pipeline stage (32 for TF32 pairs, 64 for fp16 pairs).
+TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256, int k_block = TC_BK);
 
 // Requires n % plan.bn == 0, k % 32 == 0; a maps must use box rows 128, b maps
 // box rows plan.bn.
 void launch_gemm_tc(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const TcPlan &plan,
                     const TcEpilogue &ep, float *scratch, int *counters, DevErr *err, cudaStream_t st);
+// The same product on fp16 pairs: maps over the fp16 arrays (k % 64 == 0), the
+// activations' inverse scales [rows, k / 64] and the weight matrix's inverse scale
+// (one float in device memory, written when the weights were converted).
+void launch_gemm_tc_f16(const TcMatrix &a, const float *a_inv_scale, const TcMatrix &b, const float *b_inv_scale,
+                        int m, int n, int k, const TcPlan &plan, const TcEpilogue &ep, float *scratch, int *counters,
+                        DevErr *err, cudaStream_t st);
+// Row-major W [k, n] (rows optionally scaled) -> K-major fp16 pair [n, k] with one
+// scale for the matrix; *inv_scale_dev (device float) receives its inverse.
+// amax_scratch: one int of device memory.
+void launch_transpose_split_f16(const float *w, int k, int n, __half *wt_hi, __half *wt_lo, float *inv_scale_dev,
+                                cudaStream_t st, const float *row_scale, int *amax_scratch);
+// Dense rows x [rows, k] -> fp16 pair with per-row scales per 64 columns.
+void launch_split_f16(const float *x, long long rows, int k, const TcPairF16 &out, cudaStream_t st);
+
+// Scale of one block from its largest magnitude: a power of two with
+// amax * scale in [2^12, 2^13) (1 for a block of zeros or denormals).
+__device__ __forceinline__ float f16_block_scale(float amax, float *inv) {
+  int eb = (__float_as_int(amax) >> 23) & 0xff;  // amax = 1.m * 2^(eb - 127)
+  eb = eb < 20 ? 139 : eb;                        // nothing to scale: 2^0
+  eb = eb > 250 ? 250 : eb;
+  *inv = __int_as_float((eb - 12) << 23);         // 2^(eb - 139)
+  return __int_as_float((266 - eb) << 23);        // 2^(139 - eb)
+}
+// Four consecutive elements of a block whose scale is known -> the pair, packed for 8-byte stores.
+__device__ __forceinline__ void f16_pair4(float4 v, float scale, uint2 &hi, uint2 &lo) {
+  const float a = v.x * scale, b = v.y * scale, c = v.z * scale, d = v.w * scale;
+  const __half ha = __float2half_rn(a), hb = __float2half_rn(b), hc = __float2half_rn(c), hd = __float2half_rn(d);
+  const __half la = __float2half_rn(a - __half2float(ha)), lb = __float2half_rn(b - __half2float(hb));
+  const __half lc = __float2half_rn(c - __half2float(hc)), ld = __float2half_rn(d - __half2float(hd));
+  hi.x = (unsigned)__half_as_ushort(ha) | ((unsigned)__half_as_ushort(hb) << 16);
+  hi.y = (unsigned)__half_as_ushort(hc) | ((unsigned)__half_as_ushort(hd) << 16);
+  lo.x = (unsigned)__half_as_ushort(la) | ((unsigned)__half_as_ushort(lb) << 16);
+  lo.y = (unsigned)__half_as_ushort(lc) | ((unsigned)__half_as_ushort(ld) << 16);
+}
+// 16 consecutive lanes hold the 64 columns of one block of one row, a float4
+// each (all 32 lanes of the warp call this together): scale from the block's
+// largest magnitude, the lane's four elements stored, the inverse scale by the
+// block's first lane. `active` false: the lane's values are ignored and nothing
+// is stored for it.
+__device__ __forceinline__ void f16_store_block(float4 v, bool active, __half *hi4, __half *lo4, float *inv_slot) {
+  float am = active ? fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))) : 0.f;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+  float inv;
+  const float scale = f16_block_scale(am, &inv);
+  if (active) {
+    uint2 hi, lo;
+    f16_pair4(v, scale, hi, lo);
+    *reinterpret_cast<uint2 *>(hi4) = hi;
+    *reinterpret_cast<uint2 *>(lo4) = lo;
+    if ((threadIdx.x & 15) == 0) *inv_slot = inv;
+  }
+}
 
 // attention_tc.cu: fused causal attention on the tensor cores for head
 // dimension 64. qk: maps (box 128 rows x 32) over the split [rows, 3*d_model]
 // output of the QKV projection; vt: maps (box 64 rows x 32) over the split V^T
 // arrays [n_streams * d_model, pitch] the same projection stores (pitch a
-// multiple of 128 that covers s). Writes the context as a TF32 hi/lo pair.
+// multiple of 128 that covers s). Writes the context as a TF32 hi/lo pair, or as
+// the fp16 pair ctx_f16 (one scale per row and head) when that is given.
 // state != nullptr: s is an upper bound with the same number of 128-row tiles
 // as the actual context length state->s. Scratch and zero-resting counters as
 // attention_tc_plan says. timeline (optional, 12 entries: [8] preset to all ones,
@@ -97,7 +170,8 @@ bool attention_tc_supports(int n_heads, int d_model);
 AttentionPlan attention_tc_plan(int n_streams, int s, int n_heads);
 void launch_attention_tc(const TcMatrix &qk, const TcMatrix &vt, float *ctx_hi, float *ctx_lo, int n_streams, int s,
                          int n_heads, int d_model, float *scratch, int *counters, const LoopState *state,
-                         DevErr *err, cudaStream_t st, unsigned long long *timeline = nullptr);
+                         DevErr *err, cudaStream_t st, unsigned long long *timeline = nullptr,
+                         const TcPairF16 *ctx_f16 = nullptr);
 
 // x -> (hi, lo) elementwise.
 void launch_split_tf32(const float *x, float *hi, float *lo, long long count, cudaStream_t st);
@@ -106,8 +180,10 @@ void launch_split_tf32(const float *x, float *hi, float *lo, long long count, cu
 void launch_transpose_split(const float *w, int k, int n, float *wt_hi, float *wt_lo, cudaStream_t st,
                             const float *row_scale = nullptr);
 // u[n] = sum_k gamma[k] W[k,n], v[n] = sum_k beta[k] W[k,n] + bias[n] (sums in double).
+// f16_amax_bits (optional): the matrix is stored as an fp16 pair under the scale that
+// launch_transpose_split_f16 derived from this maximum; u sums those stored values.
 void launch_ln_fold_vectors(const float *w, int k, int n, const float *gamma, const float *beta, const float *bias,
-                            float *u, float *v, cudaStream_t st);
+                            float *u, float *v, cudaStream_t st, const int *f16_amax_bits = nullptr);
 // Mean and 1/std of one row from its partial sums, as layernorm_forward of the
 // reference forms them (biased variance, eps 1e-5 added in float).
 __device__ __forceinline__ float2 ln_row_stats(const double2 *slots, int n_slots, int d) {

@@ -20,6 +20,7 @@ __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, co
                                                volatile int *last_flag, float *stage, float2 ln_st,
                                                float2 *row_stats) {
   const int row = m0 + rl;
+  finish = __all_sync(0xffffffffu, finish);  // whole warps store or skip together (the stores shuffle)
   if (splits > 1) {
     // Split-k: leave the partial tile in scratch; the CTA that arrives last at
     // the tile's counter adds all partials in split order and stores C.
@@ -102,7 +103,7 @@ __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, co
     }
   }
   constexpr int LDS = BN + 4;  // staging pitch: 16-byte accesses of 8 consecutive rows hit all banks once
-      if (finish) {
+  if (finish) {
 #pragma unroll
     for (int j = 0; j < CW; j += 4)
       *reinterpret_cast<float4 *>(stage + rl * LDS + col0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
@@ -110,15 +111,18 @@ __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, co
   }
   asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
   if (finish) {
-        constexpr int PER_ROW = BN / 4;
+    constexpr int PER_ROW = BN / 4;
 #pragma unroll 4
     for (int i = 0; i < TC_BM * PER_ROW / DRAIN_THREADS; ++i) {
       const int u = t2 + i * DRAIN_THREADS;
       const int rr = u / PER_ROW, c4 = u % PER_ROW;
       const int col = n0 + c4 * 4;
-      if (m0 + rr >= m || (vt_on && col >= ep.vt_col0)) continue;
-      float4 v = *reinterpret_cast<const float4 *>(stage + rr * LDS + c4 * 4);
+      // (no early exit: with an fp16-pair result the 16 lanes of a 64-column block shuffle together)
+      const bool active = m0 + rr < m && !(vt_on && col >= ep.vt_col0);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       const long long off = (long long)(m0 + rr) * n + col;
+      if (active) {
+      v = *reinterpret_cast<const float4 *>(stage + rr * LDS + c4 * 4);
       if (ep.ln_u != nullptr) {  // inv_std * (x W' - mean * u); v comes in as the bias
         const float2 st = row_stats[rr];
         const float4 uu = *reinterpret_cast<const float4 *>(ep.ln_u + col);
@@ -150,6 +154,10 @@ __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, co
         *reinterpret_cast<float4 *>(ep.c_lo + off) = ll;
       }
       if (ep.stats_out != nullptr) *reinterpret_cast<float4 *>(stage + rr * LDS + c4 * 4) = v;  // final values
+      }
+      if (ep.c_f16.hi != nullptr)
+        f16_store_block(v, active, ep.c_f16.hi + off, ep.c_f16.lo + off,
+                        ep.c_f16.inv_scale + (long long)(m0 + rr) * (n / TC_F16_SLOT) + col / TC_F16_SLOT);
     }
   }
   if (ep.stats_out != nullptr) {

@@ -79,6 +79,16 @@ __device__ __forceinline__ void tc_mma_tf32(unsigned tmem_d, unsigned long long 
       ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// fp16 operands (K = 16 per instruction), fp32 accumulation.
+__device__ __forceinline__ void tc_mma_f16(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
+                                           unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void tc_commit(unsigned bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -109,6 +119,10 @@ __device__ __forceinline__ unsigned long long umma_desc_k128(unsigned smem_addr)
 }
 
 // Instruction descriptor: D fp32, A and B TF32, both K-major, M = 128, N = bn.
+// The same with fp16 operands (format code 0).
+__host__ __device__ constexpr unsigned umma_idesc_f16(int bn) {
+  return (1u << 4) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
+}
 __host__ __device__ constexpr unsigned umma_idesc_tf32(int bn) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
 }

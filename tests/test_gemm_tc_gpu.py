@@ -54,7 +54,12 @@ def test_tensor_core_projection_matches_simt_and_oracle(project, oracle, m, k, n
     np.testing.assert_allclose(tc, want, rtol=2e-5, atol=atol)
     err_tc = float(np.abs(tc - want).max())
     err_simt = float(np.abs(simt - want).max())
-    print(f"{m}x{k}x{n}: max abs err tensor-core {err_tc:.2e}, simt {err_simt:.2e}")
+    msg = f"{m}x{k}x{n}: max abs err TF32 pairs {err_tc:.2e}, simt {err_simt:.2e}"
+    if k % 64 == 0:  # fp16 pairs with block scales
+        f16 = project(2, a, w)
+        np.testing.assert_allclose(f16, want, rtol=2e-5, atol=atol)
+        msg += f", fp16 pairs {float(np.abs(f16 - want).max()):.2e}"
+    print(msg)
 
 
 @pytest.mark.parametrize("relu", [False, True])
@@ -68,7 +73,7 @@ def test_tensor_core_epilogue(project, relu):
     want = a.astype(np.float64) @ w.astype(np.float64) + bias + res
     if relu:
         want = np.maximum(want, 0)
-    for engine in (0, 1):
+    for engine in (0, 1, 2):
         got = project(engine, a, w, bias, res, relu)
         np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-4)
 
@@ -82,3 +87,22 @@ def test_tensor_core_engine_rejects_unsupported_shapes(project):
     rc = lib.litnice_b200_projection_host(1, a.ctypes.data_as(f32p), 4, 48, w.ctypes.data_as(f32p), 64, None, None,
                                           0, out.ctypes.data_as(f32p))
     assert rc == -1  # k % 32 != 0
+
+
+def test_fp16_pairs_follow_the_dynamic_range_of_each_block(project):
+    """Rows and k-blocks of very different magnitude (2^-30 .. 2^20), a matrix far from
+    unit scale, exact zeros: the per-block scales keep every block at full precision."""
+    rng = np.random.default_rng(9)
+    m, k, n = 300, 512, 256
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    a *= np.exp2(rng.integers(-30, 21, size=(m, k // 64))).repeat(64, axis=1).astype(np.float32)
+    a[5] = 0.0
+    a[:, 64:128] = 0.0
+    w = (rng.standard_normal((k, n)) * 3e-4).astype(np.float32)
+    want = a.astype(np.float64) @ w.astype(np.float64)
+    got = project(2, a, w)
+    ref = project(1, a, w)
+    scale = np.abs(a).astype(np.float64) @ np.abs(w).astype(np.float64) + 1e-30
+    assert float((np.abs(got - want) / scale).max()) < 2e-6
+    assert float((np.abs(ref - want) / scale).max()) < 2e-6
+    assert np.all(got[5] == 0.0)
