@@ -109,11 +109,32 @@ __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, co
       *reinterpret_cast<float4 *>(stage + rl * LDS + col0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
     if (ep.ln_u != nullptr && col0 == 0) row_stats[rl] = ln_st;
   }
+  const bool tstamp = ep.timeline != nullptr && leader && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  if (tstamp) ep.timeline[12] = clock64();
   asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
+  if (tstamp) ep.timeline[13] = clock64();
   if (finish) {
     constexpr int PER_ROW = BN / 4;
-#pragma unroll 4
-    for (int i = 0; i < TC_BM * PER_ROW / DRAIN_THREADS; ++i) {
+    constexpr int UNITS = TC_BM * PER_ROW / DRAIN_THREADS;  // float4s per thread: 16 or 32
+    constexpr int BATCH = 16;
+    static_assert(UNITS % BATCH == 0, "whole batches");
+    for (int i0 = 0; i0 < UNITS; i0 += BATCH) {
+    // The residual rows come from L2 / HBM: all loads of a batch are issued before
+    // the first is used (a few in flight per thread would leave the SM at a
+    // fraction of its bandwidth, and the epilogue is a quarter of a short k loop).
+    float4 res[BATCH];
+    if (ep.residual) {
+#pragma unroll
+      for (int b = 0; b < BATCH; ++b) {
+        const int u = t2 + (i0 + b) * DRAIN_THREADS;
+        const int rr = u / PER_ROW, c4 = u % PER_ROW;
+        res[b] = (m0 + rr < m) ? __ldg(reinterpret_cast<const float4 *>(ep.residual + (long long)(m0 + rr) * n + n0 + c4 * 4))
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < BATCH; ++b) {
+      const int i = i0 + b;
       const int u = t2 + i * DRAIN_THREADS;
       const int rr = u / PER_ROW, c4 = u % PER_ROW;
       const int col = n0 + c4 * 4;
@@ -136,7 +157,7 @@ __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, co
         v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
       }
       if (ep.residual) {
-        const float4 rs = *reinterpret_cast<const float4 *>(ep.residual + off);
+        const float4 rs = res[b];
         v.x += rs.x; v.y += rs.y; v.z += rs.z; v.w += rs.w;
       }
       if (ep.relu) {
@@ -159,7 +180,9 @@ __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, co
         f16_store_block(v, active, ep.c_f16.hi + off, ep.c_f16.lo + off,
                         ep.c_f16.inv_scale + (long long)(m0 + rr) * (n / TC_F16_SLOT) + col / TC_F16_SLOT);
     }
+    }
   }
+  if (tstamp) ep.timeline[14] = clock64();
   if (ep.stats_out != nullptr) {
     // Row statistics for a LayerNorm folded into the next product: thread = row
     // again, sums of its stored values over slots of 64 columns, in column order.

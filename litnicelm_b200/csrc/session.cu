@@ -247,16 +247,23 @@ void ensure_rows(litnice_b200_session *s, long long rows) {
   alloc(&s->x, rows * D);
   alloc(&s->y, rows * D);
   alloc(&s->ln, rows * D);
-  alloc(&s->ctx, rows * D);
-  alloc(&s->qkv, rows * 3 * D);
-  alloc(&s->h, rows * F);
+  // With fp16-pair operands the attention context, the FFN hidden rows and the QKV
+  // output exist only in the formats their consumers read (pair_ctx, pair_h,
+  // qkv_hi/qkv_lo + vt), not as fp32 arrays.
+  if (!s->f16) {
+    alloc(&s->ctx, rows * D);
+    alloc(&s->qkv, rows * 3 * D);
+    alloc(&s->h, rows * F);
+  }
   if (s->tc) {
     alloc(&s->ln_lo, rows * D);
-    alloc(&s->ctx_lo, rows * D);
-    alloc(&s->h_lo, rows * F);
-    make_activation_map(&s->a_map[A_LN], s->ln, s->ln_lo, rows, (int)D);
-    make_activation_map(&s->a_map[A_CTX], s->ctx, s->ctx_lo, rows, (int)D);
-    make_activation_map(&s->a_map[A_H], s->h, s->h_lo, rows, (int)F);
+    make_activation_map(&s->a_map[A_LN], s->ln, s->ln_lo, rows, (int)D);  // also the final norm before an all-rows head
+    if (!s->f16) {
+      alloc(&s->ctx_lo, rows * D);
+      alloc(&s->h_lo, rows * F);
+      make_activation_map(&s->a_map[A_CTX], s->ctx, s->ctx_lo, rows, (int)D);
+      make_activation_map(&s->a_map[A_H], s->h, s->h_lo, rows, (int)F);
+    }
   }
   if (s->f16) {
     auto alloc_pair = [&](TcPairF16 *p, PairKind kind, size_t cols) {
@@ -1408,7 +1415,7 @@ static int projection_impl(int32_t engine, const float *a, int32_t m, int32_t k,
       ep.c = dc;
       const bool want_timeline = std::getenv("LITNICE_B200_TC_TIMELINE") != nullptr;
       if (want_timeline) {
-        ep.timeline = reinterpret_cast<unsigned long long *>(dev_alloc(12 * 8));
+        ep.timeline = reinterpret_cast<unsigned long long *>(dev_alloc(16 * 8));
       }
       auto launch = [&]() {
         if (f16) launch_gemm_tc_f16(ma, pa.inv_scale, mb, w_inv, m, n, k, plan, ep, scr, cnt, err_dev, st);
@@ -1434,8 +1441,10 @@ static int projection_impl(int32_t engine, const float *a, int32_t m, int32_t k,
       cudaEventDestroy(e0);
       cudaEventDestroy(e1);
       if (want_timeline) {
-        unsigned long long t[12];
-        LB_CUDA(cudaMemcpy(t, ep.timeline, 96, cudaMemcpyDeviceToHost));
+        unsigned long long t[16];
+        LB_CUDA(cudaMemcpy(t, ep.timeline, 128, cudaMemcpyDeviceToHost));
+        std::fprintf(stderr, "epilogue clocks: staged..barrier %lld, store phase %lld\n", (long long)(t[13] - t[12]),
+                     (long long)(t[14] - t[13]));
         std::fprintf(stderr,
                      "tc timeline (ns from start): setup %lld, loads issued %lld, first stage full %lld, mma issued %lld, "
                      "chunks drained %lld, stored %lld, end %lld; last CTA start %lld, whole grid %lld\n",
