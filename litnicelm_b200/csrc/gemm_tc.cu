@@ -84,9 +84,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   volatile unsigned *tmem_holder = reinterpret_cast<volatile unsigned *>(base_ptr + HOLDER_OFFSET);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + HOLDER_OFFSET + 4);
   volatile int *last_flag = reinterpret_cast<volatile int *>(base_ptr + HOLDER_OFFSET + 8);
+  volatile int *store_flag = reinterpret_cast<volatile int *>(base_ptr + HOLDER_OFFSET + 12);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * TC_BM;
+  // Drain warps (2 and up): warp w may touch TMEM lanes 32*(w%4) .. +31. Tiles wider than 128 columns
+  // use two warps per lane quarter, each taking 128 columns, so the accumulators stay in registers.
+  constexpr int CW = BN > 128 ? 128 : BN;          // columns per drain warp
+  constexpr int DRAIN_THREADS = tc_threads(BN) - 64;
+  const int q = warp & 3;
+  const int col0 = warp >= 2 ? ((warp - 2) >> 2) * CW : 0;  // first column of this warp inside the tile
+  const int rl = q * 32 + lane;                             // its row inside the tile
+  const int row = m0 + rl;
+  float2 ln_st = make_float2(0.f, 1.f);
+  float *stage = reinterpret_cast<float *>(base_ptr);       // the tile, once the pipeline stages are idle
+  float2 *row_stats = reinterpret_cast<float2 *>(base_ptr + L::ROWSTATS_OFFSET);
   // With split-k (gridDim.z CTAs per tile) this CTA owns k-blocks [kb0, kb0 + kblocks).
   const int kb_total = k / KBE;
   const int kb_per = (kb_total + splits - 1) / splits;
@@ -112,6 +124,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
       mbar_init(tmem_empty_bar(b), (tc_threads(BN) - 64) / 32);  // one arrival per drain warp
     }
     *abort_flag = 0;
+    *store_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -249,16 +262,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   } else if (warp >= 2) {
     // ---- epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 ----
     pdl_wait();  // residual reads, C and scratch writes must follow the predecessor
-    // Tiles wider than 128 columns use two warps per lane quarter, each taking
-    // 128 columns, so the per-thread accumulators stay in registers.
-    constexpr int CW = BN > 128 ? 128 : BN;          // columns per drain warp
-    constexpr int DRAIN_THREADS = tc_threads(BN) - 64;
-    const int q = warp & 3;
-    const int col0 = ((warp - 2) >> 2) * CW;          // first column of this warp inside the tile
-    const int row = m0 + q * 32 + lane;
     // LayerNorm folded into this product: the row's statistics from the partial
     // sums its producer left (read while the first tiles are still in flight)
-    float2 ln_st = make_float2(0.f, 1.f);
     if (ep.ln_u != nullptr && row < m)
       ln_st = ln_row_stats(ep.ln_stats + (long long)row * TC_STAT_SLOTS, ep.ln_slots, k);
     float acc[CW];
@@ -295,10 +300,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     }
     if (stamp && warp == 2 && lane == 0) ep.timeline[5] = global_timer();
     static_assert(TC_BM * (BN + 4) * 4 <= L::TILES_BYTES, "staging tile must fit in the pipeline stages");
-    tc_finish_tile<BN, CW, DRAIN_THREADS>(acc, ok && !*abort_flag, ep, m, n, m0, n0, col0, q * 32 + lane,
-                                          (int)threadIdx.x - 64, warp == 2 && lane == 0, splits, part, counters,
-                                          last_flag, reinterpret_cast<float *>(base_ptr), ln_st,
-                                          reinterpret_cast<float2 *>(base_ptr + L::ROWSTATS_OFFSET));
+    tc_stage_tile<BN, CW, DRAIN_THREADS>(acc, ok && !*abort_flag, ep, col0, rl, warp == 2 && lane == 0, splits, part,
+                                         counters, last_flag, store_flag, stage, ln_st, row_stats);
+  }
+  // Store phase, by every warp of the CTA (the TMA and MMA warps are idle by now, and this
+  // phase is bound by instruction latency, not bandwidth: six warps go 1.5 times as fast as four).
+  asm volatile("bar.sync 2, %0;" ::"n"(tc_threads(BN)) : "memory");
+  const bool go = *store_flag != 0;
+  if (go && warp >= 2 && ep.vt_hi != nullptr) tc_store_vt<BN, CW>(ep, m, m0, n0, col0, rl, stage, ln_st);
+  if (go) tc_store_rows<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats);
+  if (ep.stats_out != nullptr) {
+    asm volatile("bar.sync 2, %0;" ::"n"(tc_threads(BN)) : "memory");
+    if (go && warp >= 2) tc_store_row_stats<BN, CW>(ep, m, m0, n0, col0, rl, stage);
   }
   if (stamp && warp == 2 && lane == 0) ep.timeline[6] = global_timer();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

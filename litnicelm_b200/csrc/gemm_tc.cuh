@@ -128,13 +128,13 @@ __device__ __forceinline__ float f16_block_scale(float amax, float *inv) {
 // Four consecutive elements of a block whose scale is known -> the pair, packed for 8-byte stores.
 __device__ __forceinline__ void f16_pair4(float4 v, float scale, uint2 &hi, uint2 &lo) {
   const float a = v.x * scale, b = v.y * scale, c = v.z * scale, d = v.w * scale;
-  const __half ha = __float2half_rn(a), hb = __float2half_rn(b), hc = __float2half_rn(c), hd = __float2half_rn(d);
-  const __half la = __float2half_rn(a - __half2float(ha)), lb = __float2half_rn(b - __half2float(hb));
-  const __half lc = __float2half_rn(c - __half2float(hc)), ld = __float2half_rn(d - __half2float(hd));
-  hi.x = (unsigned)__half_as_ushort(ha) | ((unsigned)__half_as_ushort(hb) << 16);
-  hi.y = (unsigned)__half_as_ushort(hc) | ((unsigned)__half_as_ushort(hd) << 16);
-  lo.x = (unsigned)__half_as_ushort(la) | ((unsigned)__half_as_ushort(lb) << 16);
-  lo.y = (unsigned)__half_as_ushort(lc) | ((unsigned)__half_as_ushort(ld) << 16);
+  const __half2 h01 = __floats2half2_rn(a, b), h23 = __floats2half2_rn(c, d);  // packed conversions
+  const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+  const __half2 l01 = __floats2half2_rn(a - f01.x, b - f01.y), l23 = __floats2half2_rn(c - f23.x, d - f23.y);
+  hi.x = *reinterpret_cast<const unsigned *>(&h01);
+  hi.y = *reinterpret_cast<const unsigned *>(&h23);
+  lo.x = *reinterpret_cast<const unsigned *>(&l01);
+  lo.y = *reinterpret_cast<const unsigned *>(&l23);
 }
 // 16 consecutive lanes hold the 64 columns of one block of one row, a float4
 // each (all 32 lanes of the warp call this together): scale from the block's

@@ -6,24 +6,127 @@
 
 namespace lb {
 
-// acc: this thread's columns [col0, col0 + CW) of tile row rl. finish: false when
-// the pipeline gave up (nothing is stored then, barriers are still joined).
-// t2: index of the thread among the DRAIN_THREADS epilogue threads, which share
-// named barrier 1; leader: the one thread that counts split-k arrivals. stage:
-// shared memory for a 128 x (BN + 4) float tile that nothing else uses any more.
-// ln_st: (mean, 1/std) of this thread's row when ep.ln_u is set; row_stats: 128
-// float2 of shared memory through which the store phase learns them.
+// The store phase: NT threads (whole warps, thread index tid) walk the staged
+// 128 x BN fp32 tile row by row, a float4 each, apply the epilogue terms and
+// write the results in every requested format. A thread keeps its column for the
+// whole walk (NT is a multiple of the float4s per row), so the per-column terms
+// (bias, folded-LayerNorm u) are loaded once; two rows per trip of a loop that is
+// deliberately not unrolled (this code runs once per CTA: as straight-line code
+// it ran at the speed of instruction fetch), with the residual rows of the next
+// trip requested before this trip's arithmetic.
+template <int BN, int NT>
+__device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n, int m0, int n0, int tid,
+                                              float *stage, const float2 *row_stats) {
+  constexpr int LDS = BN + 4;
+  constexpr int PER_ROW = BN / 4;
+  static_assert(NT % PER_ROW == 0 && NT % 32 == 0, "a thread keeps its column; whole warps");
+  constexpr int RPT = NT / PER_ROW;  // rows covered by the threads at once
+  constexpr int G = 2;
+  const int c4 = tid % PER_ROW, r0 = tid / PER_ROW;
+  const int col = n0 + c4 * 4;
+  const bool col_active = !(ep.vt_hi != nullptr && col >= ep.vt_col0);  // V columns leave transposed, elsewhere
+  const bool fold = ep.ln_u != nullptr;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 uu = fold ? __ldg(reinterpret_cast<const float4 *>(ep.ln_u + col)) : zero4;
+  const float4 bb = ep.bias ? __ldg(reinterpret_cast<const float4 *>(ep.bias + col)) : zero4;
+  const float *res_col = ep.residual ? ep.residual + (long long)m0 * n + col : nullptr;
+  auto residual_row = [&](int rg) {
+    return (res_col != nullptr && rg < TC_BM && m0 + rg < m) ? __ldg(reinterpret_cast<const float4 *>(res_col + (long long)rg * n))
+                                                             : zero4;
+  };
+  float4 res_next[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) res_next[g] = residual_row(r0 + g * RPT);
+#pragma unroll 1
+  for (int rr = r0; rr < TC_BM; rr += G * RPT) {
+    float4 v[G], res[G];
+    bool act[G], valid[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      res[g] = res_next[g];
+      res_next[g] = residual_row(rr + (G + g) * RPT);
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int rg = rr + g * RPT;
+      valid[g] = rg < TC_BM;  // the same for all lanes of a warp (a warp covers whole rows or a part of one)
+      act[g] = valid[g] && m0 + rg < m && col_active;
+      const int rc = valid[g] ? rg : 0;
+      v[g] = *reinterpret_cast<const float4 *>(stage + rc * LDS + c4 * 4);
+      if (fold) {  // inv_std * (x W' - mean * u); v comes in as the bias
+        const float2 st = row_stats[rc];
+        v[g].x = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.x, v[g].x));
+        v[g].y = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.y, v[g].y));
+        v[g].z = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.z, v[g].z));
+        v[g].w = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.w, v[g].w));
+      }
+      v[g].x += bb.x + res[g].x;
+      v[g].y += bb.y + res[g].y;
+      v[g].z += bb.z + res[g].z;
+      v[g].w += bb.w + res[g].w;
+      if (ep.relu) {
+        v[g].x = fmaxf(v[g].x, 0.f); v[g].y = fmaxf(v[g].y, 0.f);
+        v[g].z = fmaxf(v[g].z, 0.f); v[g].w = fmaxf(v[g].w, 0.f);
+      }
+      if (!act[g]) v[g] = zero4;
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      if (!act[g]) continue;
+      const int rg = rr + g * RPT;
+      const long long off = (long long)(m0 + rg) * n + col;
+      if (ep.c) *reinterpret_cast<float4 *>(ep.c + off) = v[g];
+      if (ep.c_hi) {
+        float4 hh, ll;
+        split_tf32(v[g].x, hh.x, ll.x);
+        split_tf32(v[g].y, hh.y, ll.y);
+        split_tf32(v[g].z, hh.z, ll.z);
+        split_tf32(v[g].w, hh.w, ll.w);
+        *reinterpret_cast<float4 *>(ep.c_hi + off) = hh;
+        *reinterpret_cast<float4 *>(ep.c_lo + off) = ll;
+      }
+      if (ep.stats_out != nullptr) *reinterpret_cast<float4 *>(stage + rg * LDS + c4 * 4) = v[g];  // final values
+    }
+    if (ep.c_f16.hi != nullptr) {
+      // fp16 pair: the 16 lanes of a 64-column block of a row agree on its scale
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        if (!valid[g]) continue;  // whole warps
+        float am = fmaxf(fmaxf(fabsf(v[g].x), fabsf(v[g].y)), fmaxf(fabsf(v[g].z), fabsf(v[g].w)));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        float inv;
+        const float scale = f16_block_scale(am, &inv);
+        if (act[g]) {
+          const int rg = rr + g * RPT;
+          const long long off = (long long)(m0 + rg) * n + col;
+          uint2 hi, lo;
+          f16_pair4(v[g], scale, hi, lo);
+          *reinterpret_cast<uint2 *>(ep.c_f16.hi + off) = hi;
+          *reinterpret_cast<uint2 *>(ep.c_f16.lo + off) = lo;
+          if ((c4 & 15) == 0) ep.c_f16.inv_scale[(long long)(m0 + rg) * (n / TC_F16_SLOT) + col / TC_F16_SLOT] = inv;
+        }
+      }
+    }
+  }
+}
+
+// What the drain warps do once a thread holds CW accumulated columns of tile
+// row rl: with split-k, leave the partial tile in scratch and let the CTA that
+// arrives last add all partials in split order; then stage the tile in shared
+// memory (row pitch BN + 4: 16-byte accesses of 8 consecutive rows hit all banks
+// once) for the store phase. finish: false when the pipeline gave up. t2 / leader:
+// index among the DRAIN_THREADS threads (named barrier 1) and the one that counts
+// arrivals. Returns whether this CTA stores the tile; the leader also leaves that
+// in *store_flag for the warps that were not draining.
 template <int BN, int CW, int DRAIN_THREADS>
-__device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, const TcEpilogue &ep, int m, int n, int m0,
-                                               int n0, int col0, int rl, int t2, bool leader, int splits,
-                                               float *__restrict__ part, int *__restrict__ counters,
-                                               volatile int *last_flag, float *stage, float2 ln_st,
-                                               float2 *row_stats) {
-  const int row = m0 + rl;
-  finish = __all_sync(0xffffffffu, finish);  // whole warps store or skip together (the stores shuffle)
+__device__ __forceinline__ bool tc_stage_tile(float (&acc)[CW], bool finish, const TcEpilogue &ep, int col0, int rl,
+                                              bool leader, int splits, float *__restrict__ part,
+                                              int *__restrict__ counters, volatile int *last_flag,
+                                              volatile int *store_flag, float *stage, float2 ln_st,
+                                              float2 *row_stats) {
+  finish = __all_sync(0xffffffffu, finish);
   if (splits > 1) {
-    // Split-k: leave the partial tile in scratch; the CTA that arrives last at
-    // the tile's counter adds all partials in split order and stores C.
     // Partial tiles are laid out [column / 4][row][4] so that the 32 rows of a
     // warp are contiguous (a row-major tile would cost 32 lines per access).
     const long long tile = (long long)blockIdx.y * gridDim.x + blockIdx.x;
@@ -74,134 +177,70 @@ __device__ __forceinline__ void tc_finish_tile(float (&acc)[CW], bool finish, co
       }
     }
   }
-
-  // Stores. A thread holds CW columns of one row; written directly, every
-  // instruction of a warp would touch 32 different lines. The V^T columns of a
-  // QKV projection are the exception (lanes = consecutive positions of one
-  // column): they go out from the registers. Everything else is transposed
-  // through the pipeline's shared memory (idle by now: every load has landed
-  // and every MMA has completed) and stored row by row, where bias, residual,
-  // ReLU and the TF32 split are applied on coalesced float4s.
-  const bool vt_on = ep.vt_hi != nullptr;
-  if (finish && vt_on && row < m && n0 + col0 + CW > ep.vt_col0) {
-    const int sl = ep.state ? ep.state->s : ep.vt_s;
-    const int v_stream = row / sl, v_tok = row - v_stream * sl;
-    if (v_stream < ep.vt_streams) {
-#pragma unroll
-      for (int j = 0; j < CW; ++j) {
-        const int col = n0 + col0 + j;
-        if (col >= ep.vt_col0) {
-          float val = acc[j];
-          if (ep.ln_u != nullptr) val = __fmul_rn(ln_st.y, __fmaf_rn(-ln_st.x, ep.ln_u[col], val));
-          float hh, ll;
-          split_tf32(val + (ep.bias ? ep.bias[col] : 0.f), hh, ll);
-          const long long at = ((long long)v_stream * ep.vt_rows + (col - ep.vt_col0)) * ep.vt_pitch + v_tok;
-          ep.vt_hi[at] = hh;
-          ep.vt_lo[at] = ll;
-        }
-      }
-    }
-  }
-  constexpr int LDS = BN + 4;  // staging pitch: 16-byte accesses of 8 consecutive rows hit all banks once
+  constexpr int LDS = BN + 4;
   if (finish) {
 #pragma unroll
     for (int j = 0; j < CW; j += 4)
       *reinterpret_cast<float4 *>(stage + rl * LDS + col0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
     if (ep.ln_u != nullptr && col0 == 0) row_stats[rl] = ln_st;
   }
-  const bool tstamp = ep.timeline != nullptr && leader && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-  if (tstamp) ep.timeline[12] = clock64();
-  asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
-  if (tstamp) ep.timeline[13] = clock64();
-  if (finish) {
-    constexpr int PER_ROW = BN / 4;
-    constexpr int UNITS = TC_BM * PER_ROW / DRAIN_THREADS;  // float4s per thread: 16 or 32
-    constexpr int BATCH = 16;
-    static_assert(UNITS % BATCH == 0, "whole batches");
-    for (int i0 = 0; i0 < UNITS; i0 += BATCH) {
-    // The residual rows come from L2 / HBM: all loads of a batch are issued before
-    // the first is used (a few in flight per thread would leave the SM at a
-    // fraction of its bandwidth, and the epilogue is a quarter of a short k loop).
-    float4 res[BATCH];
-    if (ep.residual) {
+  if (leader) *store_flag = finish ? 1 : 0;
+  return finish;
+}
+
+// After the staged tile is visible to the drain warps (a barrier): the V^T
+// columns of a QKV projection leave transposed, thread = row (lanes = consecutive
+// positions of one column), element (row r = stream * s + t, column vt_col0 + c)
+// to vt[(stream * vt_rows + c) * vt_pitch + t]. A short loop, like the store phase.
+template <int BN, int CW>
+__device__ __forceinline__ void tc_store_vt(const TcEpilogue &ep, int m, int m0, int n0, int col0, int rl,
+                                            const float *stage, float2 ln_st) {
+  constexpr int LDS = BN + 4;
+  const int row = m0 + rl;
+  if (row >= m || n0 + col0 + CW <= ep.vt_col0) return;
+  const int sl = ep.state ? ep.state->s : ep.vt_s;
+  const int v_stream = row / sl, v_tok = row - v_stream * sl;
+  if (v_stream >= ep.vt_streams) return;
+#pragma unroll 1
+  for (int j = 0; j < CW; j += 4) {
+    const int col = n0 + col0 + j;
+    if (col < ep.vt_col0) continue;
+    const float4 t = *reinterpret_cast<const float4 *>(stage + rl * LDS + col0 + j);
+    const float vals[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
-      for (int b = 0; b < BATCH; ++b) {
-        const int u = t2 + (i0 + b) * DRAIN_THREADS;
-        const int rr = u / PER_ROW, c4 = u % PER_ROW;
-        res[b] = (m0 + rr < m) ? __ldg(reinterpret_cast<const float4 *>(ep.residual + (long long)(m0 + rr) * n + n0 + c4 * 4))
-                               : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-    }
-#pragma unroll
-    for (int b = 0; b < BATCH; ++b) {
-      const int i = i0 + b;
-      const int u = t2 + i * DRAIN_THREADS;
-      const int rr = u / PER_ROW, c4 = u % PER_ROW;
-      const int col = n0 + c4 * 4;
-      // (no early exit: with an fp16-pair result the 16 lanes of a 64-column block shuffle together)
-      const bool active = m0 + rr < m && !(vt_on && col >= ep.vt_col0);
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      const long long off = (long long)(m0 + rr) * n + col;
-      if (active) {
-      v = *reinterpret_cast<const float4 *>(stage + rr * LDS + c4 * 4);
-      if (ep.ln_u != nullptr) {  // inv_std * (x W' - mean * u); v comes in as the bias
-        const float2 st = row_stats[rr];
-        const float4 uu = *reinterpret_cast<const float4 *>(ep.ln_u + col);
-        v.x = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.x, v.x));
-        v.y = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.y, v.y));
-        v.z = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.z, v.z));
-        v.w = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.w, v.w));
-      }
-      if (ep.bias) {
-        const float4 bb = *reinterpret_cast<const float4 *>(ep.bias + col);
-        v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
-      }
-      if (ep.residual) {
-        const float4 rs = res[b];
-        v.x += rs.x; v.y += rs.y; v.z += rs.z; v.w += rs.w;
-      }
-      if (ep.relu) {
-        v.x = v.x > 0.f ? v.x : 0.f; v.y = v.y > 0.f ? v.y : 0.f;
-        v.z = v.z > 0.f ? v.z : 0.f; v.w = v.w > 0.f ? v.w : 0.f;
-      }
-      if (ep.c) *reinterpret_cast<float4 *>(ep.c + off) = v;
-      if (ep.c_hi) {
-        float4 hh, ll;
-        split_tf32(v.x, hh.x, ll.x);
-        split_tf32(v.y, hh.y, ll.y);
-        split_tf32(v.z, hh.z, ll.z);
-        split_tf32(v.w, hh.w, ll.w);
-        *reinterpret_cast<float4 *>(ep.c_hi + off) = hh;
-        *reinterpret_cast<float4 *>(ep.c_lo + off) = ll;
-      }
-      if (ep.stats_out != nullptr) *reinterpret_cast<float4 *>(stage + rr * LDS + c4 * 4) = v;  // final values
-      }
-      if (ep.c_f16.hi != nullptr)
-        f16_store_block(v, active, ep.c_f16.hi + off, ep.c_f16.lo + off,
-                        ep.c_f16.inv_scale + (long long)(m0 + rr) * (n / TC_F16_SLOT) + col / TC_F16_SLOT);
-    }
+    for (int e = 0; e < 4; ++e) {
+      float val = vals[e];
+      if (ep.ln_u != nullptr) val = __fmul_rn(ln_st.y, __fmaf_rn(-ln_st.x, ep.ln_u[col + e], val));
+      float hh, ll;
+      split_tf32(val + (ep.bias ? ep.bias[col + e] : 0.f), hh, ll);
+      const long long at = ((long long)v_stream * ep.vt_rows + (col + e - ep.vt_col0)) * ep.vt_pitch + v_tok;
+      ep.vt_hi[at] = hh;
+      ep.vt_lo[at] = ll;
     }
   }
-  if (tstamp) ep.timeline[14] = clock64();
-  if (ep.stats_out != nullptr) {
-    // Row statistics for a LayerNorm folded into the next product: thread = row
-    // again, sums of its stored values over slots of 64 columns, in column order.
-    asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_THREADS) : "memory");
-    if (finish && row < m) {
-#pragma unroll
-      for (int j0 = 0; j0 < CW; j0 += 64) {
-        double sx = 0.0, sxx = 0.0;
-#pragma unroll 4
-        for (int j = 0; j < 64; j += 4) {
-          const float4 t = *reinterpret_cast<const float4 *>(stage + rl * LDS + col0 + j0 + j);
-          sx += (double)t.x; sxx += (double)t.x * (double)t.x;
-          sx += (double)t.y; sxx += (double)t.y * (double)t.y;
-          sx += (double)t.z; sxx += (double)t.z * (double)t.z;
-          sx += (double)t.w; sxx += (double)t.w * (double)t.w;
-        }
-        ep.stats_out[(long long)row * TC_STAT_SLOTS + (n0 + col0 + j0) / 64] = make_double2(sx, sxx);
-      }
+}
+
+// After the store phase has put the final values back into the staged tile (a
+// barrier): row statistics for a LayerNorm folded into the next product, thread =
+// row, sums over slots of 64 columns in column order.
+template <int BN, int CW>
+__device__ __forceinline__ void tc_store_row_stats(const TcEpilogue &ep, int m, int m0, int n0, int col0, int rl,
+                                                   const float *stage) {
+  constexpr int LDS = BN + 4;
+  const int row = m0 + rl;
+  if (row >= m) return;
+#pragma unroll 1
+  for (int j0 = 0; j0 < CW; j0 += 64) {
+    double sx = 0.0, sxx = 0.0;
+#pragma unroll 2
+    for (int j = 0; j < 64; j += 4) {
+      const float4 t = *reinterpret_cast<const float4 *>(stage + rl * LDS + col0 + j0 + j);
+      sx += (double)t.x; sxx += (double)t.x * (double)t.x;
+      sx += (double)t.y; sxx += (double)t.y * (double)t.y;
+      sx += (double)t.z; sxx += (double)t.z * (double)t.z;
+      sx += (double)t.w; sxx += (double)t.w * (double)t.w;
     }
+    ep.stats_out[(long long)row * TC_STAT_SLOTS + (n0 + col0 + j0) / 64] = make_double2(sx, sxx);
   }
 }
 

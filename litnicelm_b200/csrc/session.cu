@@ -158,6 +158,8 @@ struct litnice_b200_session {
   // measurement aid (LITNICE_B200_ATTN_TIMELINE, profile_step only): 10 stamps per profiled attention launch
   unsigned long long *attn_timeline = nullptr;
   int attn_timeline_used = 0;
+  unsigned long long *gemm_timeline = nullptr;  // the same for the projections (LITNICE_B200_TC_TIMELINE)
+  int gemm_timeline_used = 0;
   static constexpr int kTimelineSlots = 64;
   // LayerNorm folded into the QKV and W1 products: the kernels that produce x and y
   // (embedding, out-projection, W2) also store them as TF32 pairs in (ln, ln_lo) and
@@ -428,8 +430,11 @@ void projection_f16(litnice_b200_session *s, PairKind pk, long long rows, int k,
   ++s->launches;
   const TcPairF16 &a = pk == PAIR_LN ? s->pair_ln : pk == PAIR_CTX ? s->pair_ctx : s->pair_h;
   const TcPlan plan = tc_plan((int)rows, n, k, tw->has64, tw->has128, tw->has256, TC_F16_SLOT);
+  TcEpilogue e = ep;
+  if (s->profiling && s->gemm_timeline && s->gemm_timeline_used < litnice_b200_session::kTimelineSlots)
+    e.timeline = s->gemm_timeline + 32 * s->gemm_timeline_used++;
   launch_gemm_tc_f16(s->pair_map[pk], a.inv_scale, plan.bn == 256 ? tw->f256 : plan.bn == 128 ? tw->f128 : tw->f64,
-                     tw->h_inv_scale, (int)rows, n, k, plan, ep, s->tc_scratch, s->tc_counters, s->err_dev, s->st);
+                     tw->h_inv_scale, (int)rows, n, k, plan, e, s->tc_scratch, s->tc_counters, s->err_dev, s->st);
 }
 
 // Transformer::forward over all rows up to the last layer's output
@@ -800,6 +805,7 @@ void litnice_b200_session_destroy(litnice_b200_session *s) {
   if (s->xl_lo) cudaFree(s->xl_lo);
   if (s->tc_scratch) cudaFree(s->tc_scratch);
   if (s->attn_timeline) cudaFree(s->attn_timeline);
+  if (s->gemm_timeline) cudaFree(s->gemm_timeline);
   if (s->amax_scratch) cudaFree(s->amax_scratch);
   if (s->vt_hi) cudaFree(s->vt_hi);
   if (s->vt_lo) cudaFree(s->vt_lo);
@@ -1232,11 +1238,21 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
     s->attn_ev.clear();
     s->gemm_flops = 0;
     if (s->tc_attn && s->attn_timeline == nullptr && std::getenv("LITNICE_B200_ATTN_TIMELINE") != nullptr)
-      if (cudaMalloc(reinterpret_cast<void **>(&s->attn_timeline), litnice_b200_session::kTimelineSlots * 128) !=
+      if (cudaMalloc(reinterpret_cast<void **>(&s->attn_timeline), litnice_b200_session::kTimelineSlots * 256) !=
           cudaSuccess)
         throw std::bad_alloc();
+    if (s->gemm_timeline == nullptr && std::getenv("LITNICE_B200_TC_TIMELINE") != nullptr)
+      if (cudaMalloc(reinterpret_cast<void **>(&s->gemm_timeline), litnice_b200_session::kTimelineSlots * 256) !=
+          cudaSuccess)
+        throw std::bad_alloc();
+    if (s->gemm_timeline) {
+      LB_CUDA(cudaMemsetAsync(s->gemm_timeline, 0, litnice_b200_session::kTimelineSlots * 256, s->st));
+      for (int i = 0; i < litnice_b200_session::kTimelineSlots; ++i)
+        LB_CUDA(cudaMemsetAsync(s->gemm_timeline + 32 * i + 8, 0xff, 8, s->st));
+      s->gemm_timeline_used = 0;
+    }
     if (s->attn_timeline) {
-      LB_CUDA(cudaMemsetAsync(s->attn_timeline, 0, litnice_b200_session::kTimelineSlots * 128, s->st));
+      LB_CUDA(cudaMemsetAsync(s->attn_timeline, 0, litnice_b200_session::kTimelineSlots * 256, s->st));
       for (int i = 0; i < litnice_b200_session::kTimelineSlots; ++i)
         LB_CUDA(cudaMemsetAsync(s->attn_timeline + 16 * i + 8, 0xff, 8, s->st));  // earliest start: preset to max
       s->attn_timeline_used = 0;
@@ -1274,6 +1290,19 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
     s->stats.gemm_flops = s->gemm_flops;
     s->gemm_ev.clear();
     s->attn_ev.clear();
+    if (s->gemm_timeline) {
+      std::vector<unsigned long long> t(32 * (size_t)s->gemm_timeline_used);
+      if (!t.empty()) LB_CUDA(cudaMemcpy(t.data(), s->gemm_timeline, t.size() * 8, cudaMemcpyDeviceToHost));
+      for (int i = 0; i < s->gemm_timeline_used; ++i) {
+        const unsigned long long *u = t.data() + 32 * i;
+        std::fprintf(stderr,
+                     "projection launch %d (ns from CTA start): setup %lld, loads issued %lld, first stage %lld, mma "
+                     "issued %lld, drained %lld, stored %lld, end %lld; whole grid %lld\n",
+                     i, (long long)(u[1] - u[0]), (long long)(u[2] - u[0]), (long long)(u[3] - u[0]),
+                     (long long)(u[4] - u[0]), (long long)(u[5] - u[0]), (long long)(u[6] - u[0]),
+                     (long long)(u[7] - u[0]), (long long)(u[9] - u[8]));
+      }
+    }
     if (s->attn_timeline) {
       // per profiled launch: stamps of CTA (0,0,0) and the span from the first CTA's start to the last CTA's end
       std::vector<unsigned long long> t(16 * (size_t)s->attn_timeline_used);
@@ -1443,8 +1472,7 @@ static int projection_impl(int32_t engine, const float *a, int32_t m, int32_t k,
       if (want_timeline) {
         unsigned long long t[16];
         LB_CUDA(cudaMemcpy(t, ep.timeline, 128, cudaMemcpyDeviceToHost));
-        std::fprintf(stderr, "epilogue clocks: staged..barrier %lld, store phase %lld\n", (long long)(t[13] - t[12]),
-                     (long long)(t[14] - t[13]));
+
         std::fprintf(stderr,
                      "tc timeline (ns from start): setup %lld, loads issued %lld, first stage full %lld, mma issued %lld, "
                      "chunks drained %lld, stored %lld, end %lld; last CTA start %lld, whole grid %lld\n",
