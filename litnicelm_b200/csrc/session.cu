@@ -131,7 +131,7 @@ struct litnice_b200_session {
   float *xl = nullptr, *logits = nullptr, *gemv_scratch = nullptr;
   // tensor-core path: low parts of the split activations (ln/ctx/h/xl hold the high parts)
   bool tc = false;
-  bool pdl = false;        // early launch of dependent kernels (LITNICE_B200_PDL=1 enables)
+  bool pdl = true;         // early launch of dependent kernels (LITNICE_B200_PDL=0 disables)
   bool use_graphs = true;  // replay one captured step per 64-token context bucket (LITNICE_B200_GRAPHS=0 disables)
   struct StepGraph {
     cudaGraphExec_t exec = nullptr;
@@ -745,7 +745,7 @@ int litnice_b200_session_create(const litnice_b200_dims *dims, int32_t max_strea
     // Tensor-core projections need k % 32 == 0 and n % 64 == 0 for all four
     // layer matrices; LITNICE_B200_TC=0 forces the fp32 SIMT kernels.
     const char *pdl_env = std::getenv("LITNICE_B200_PDL");
-    s->pdl = pdl_env && pdl_env[0] == '1';
+    s->pdl = !(pdl_env && pdl_env[0] == '0');
     const char *graph_env = std::getenv("LITNICE_B200_GRAPHS");
     s->use_graphs = !(graph_env && graph_env[0] == '0');
     const char *tc_env = std::getenv("LITNICE_B200_TC");
