@@ -201,22 +201,32 @@ __device__ __forceinline__ void tc_store_vt(const TcEpilogue &ep, int m, int m0,
   const int sl = ep.state ? ep.state->s : ep.vt_s;
   const int v_stream = row / sl, v_tok = row - v_stream * sl;
   if (v_stream >= ep.vt_streams) return;
+  const int first = n0 + col0 < ep.vt_col0 ? ep.vt_col0 - (n0 + col0) : 0;  // first V column of this thread's range
+  const long long at0 = ((long long)v_stream * ep.vt_rows + (n0 + col0 + first - ep.vt_col0)) * ep.vt_pitch + v_tok;
+  float *out_hi = ep.vt_hi + at0, *out_lo = ep.vt_lo + at0;
+  const float *up = ep.ln_u ? ep.ln_u + n0 + col0 + first : nullptr;
+  const float *bp = ep.bias ? ep.bias + n0 + col0 + first : nullptr;
+  const float *sp = stage + rl * LDS + col0 + first;
+  const float fold_scale = ep.ln_u ? ln_st.y : 1.f, fold_mean = ep.ln_u ? ln_st.x : 0.f;
 #pragma unroll 1
-  for (int j = 0; j < CW; j += 4) {
-    const int col = n0 + col0 + j;
-    if (col < ep.vt_col0) continue;
-    const float4 t = *reinterpret_cast<const float4 *>(stage + rl * LDS + col0 + j);
-    const float vals[4] = {t.x, t.y, t.z, t.w};
+  for (int j = first; j < CW; j += 4) {
+    const float4 t = *reinterpret_cast<const float4 *>(sp);
+    const float4 u4 = up ? __ldg(reinterpret_cast<const float4 *>(up)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 b4 = bp ? __ldg(reinterpret_cast<const float4 *>(bp)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float vals[4] = {t.x, t.y, t.z, t.w}, us[4] = {u4.x, u4.y, u4.z, u4.w}, bs[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      float val = vals[e];
-      if (ep.ln_u != nullptr) val = __fmul_rn(ln_st.y, __fmaf_rn(-ln_st.x, ep.ln_u[col + e], val));
+      const float val = up ? __fmul_rn(fold_scale, __fmaf_rn(-fold_mean, us[e], vals[e])) : vals[e];
       float hh, ll;
-      split_tf32(val + (ep.bias ? ep.bias[col + e] : 0.f), hh, ll);
-      const long long at = ((long long)v_stream * ep.vt_rows + (col + e - ep.vt_col0)) * ep.vt_pitch + v_tok;
-      ep.vt_hi[at] = hh;
-      ep.vt_lo[at] = ll;
+      split_tf32(val + bs[e], hh, ll);
+      out_hi[(long long)e * ep.vt_pitch] = hh;
+      out_lo[(long long)e * ep.vt_pitch] = ll;
     }
+    sp += 4;
+    if (up) up += 4;
+    if (bp) bp += 4;
+    out_hi += 4LL * ep.vt_pitch;
+    out_lo += 4LL * ep.vt_pitch;
   }
 }
 
