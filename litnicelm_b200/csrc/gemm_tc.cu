@@ -26,8 +26,12 @@ namespace lb {
 
 namespace {
 
-// 2 role warps (TMA, MMA) + 4 drain warps per 128 accumulator columns.
-__host__ __device__ constexpr int tc_threads(int bn) { return 64 + 128 * (bn > 128 ? bn / 128 : 1); }
+// Warps of a CTA: 2 role warps (TMA, MMA), then the drain warps (four per lane quarter set: 64
+// accumulator columns per thread for tiles up to 128 columns, 128 for the 256-column tile), then
+// helper warps that only take part in the store phase, which is bound by instruction latency and
+// wants as many warps as the register file allows.
+__host__ __device__ constexpr int tc_drain_warps(int bn) { return bn == 64 ? 4 : 8; }
+__host__ __device__ constexpr int tc_threads(int bn) { return bn > 128 ? 320 : 384; }
 template <int BN, int STAGES>
 struct TcSmem {
   static constexpr int A_BYTES = TC_BM * TC_BK * 4;  // 16 KiB
@@ -90,10 +94,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * TC_BM;
   // Drain warps (2 and up): warp w may touch TMEM lanes 32*(w%4) .. +31. Tiles wider than 128 columns
   // use two warps per lane quarter, each taking 128 columns, so the accumulators stay in registers.
-  constexpr int CW = BN > 128 ? 128 : BN;          // columns per drain warp
-  constexpr int DRAIN_THREADS = tc_threads(BN) - 64;
+  constexpr int CW = BN > 128 ? 128 : 64;          // columns per drain warp
+  constexpr int DRAIN_WARPS = tc_drain_warps(BN);
+  constexpr int DRAIN_THREADS = DRAIN_WARPS * 32;
+  static_assert(CW * (DRAIN_WARPS / 4) == BN, "the drain warps cover the tile");
   const int q = warp & 3;
-  const int col0 = warp >= 2 ? ((warp - 2) >> 2) * CW : 0;  // first column of this warp inside the tile
+  const bool drains = warp >= 2 && warp < 2 + DRAIN_WARPS;
+  const int col0 = drains ? ((warp - 2) >> 2) * CW : 0;     // first column of this warp inside the tile
   const int rl = q * 32 + lane;                             // its row inside the tile
   const int row = m0 + rl;
   float2 ln_st = make_float2(0.f, 1.f);
@@ -121,7 +128,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     }
     for (int b = 0; b < NBUF; ++b) {
       mbar_init(tmem_full_bar(b), 1);
-      mbar_init(tmem_empty_bar(b), (tc_threads(BN) - 64) / 32);  // one arrival per drain warp
+      mbar_init(tmem_empty_bar(b), DRAIN_WARPS);  // one arrival per drain warp
     }
     *abort_flag = 0;
     *store_flag = 0;
@@ -259,7 +266,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
         if (global_timer() - t0 > WAIT_LIMIT_NS) break;
     }
     __syncwarp();
-  } else if (warp >= 2) {
+  } else if (drains) {
     // ---- epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 ----
     pdl_wait();  // residual reads, C and scratch writes must follow the predecessor
     // LayerNorm folded into this product: the row's statistics from the partial
@@ -303,15 +310,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     tc_stage_tile<BN, CW, DRAIN_THREADS>(acc, ok && !*abort_flag, ep, col0, rl, warp == 2 && lane == 0, splits, part,
                                          counters, last_flag, store_flag, stage, ln_st, row_stats);
   }
-  // Store phase, by every warp of the CTA (the TMA and MMA warps are idle by now, and this
-  // phase is bound by instruction latency, not bandwidth: six warps go 1.5 times as fast as four).
+  // Store phase, by every warp of the CTA (role and helper warps included: this phase is bound
+  // by instruction latency, not bandwidth, and speeds up with the number of warps).
   asm volatile("bar.sync 2, %0;" ::"n"(tc_threads(BN)) : "memory");
   const bool go = *store_flag != 0;
-  if (go && warp >= 2 && ep.vt_hi != nullptr) tc_store_vt<BN, CW>(ep, m, m0, n0, col0, rl, stage, ln_st);
+  if (go && drains && ep.vt_hi != nullptr) tc_store_vt<BN, CW>(ep, m, m0, n0, col0, rl, stage, ln_st);
   if (go) tc_store_rows<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats);
   if (ep.stats_out != nullptr) {
     asm volatile("bar.sync 2, %0;" ::"n"(tc_threads(BN)) : "memory");
-    if (go && warp >= 2) tc_store_row_stats<BN, CW>(ep, m, m0, n0, col0, rl, stage);
+    if (go && drains) tc_store_row_stats<BN, CW>(ep, m, m0, n0, col0, rl, stage);
   }
   if (stamp && warp == 2 && lane == 0) ep.timeline[6] = global_timer();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
