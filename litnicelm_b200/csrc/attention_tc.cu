@@ -355,19 +355,33 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
         if (lane == 0) mbar_arrive(s_read);  // S may be overwritten by the next tile's product
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          p[j] = __fmul_rn(__uint_as_float(t0[j]), scale_log2e);
-          p[32 + j] = __fmul_rn(__uint_as_float(t1[j]), scale_log2e);
+          p[j] = __uint_as_float(t0[j]);
+          p[32 + j] = __uint_as_float(t1[j]);
         }
       }
-      float mx = TA_NEG;
+      // Raw scores: the maximum commutes with the positive scale, and the scale joins the
+      // subtraction in one fused multiply-add: p = 2^(s * c - max(s) * c). Only the tile on the
+      // diagonal has keys past a query; the others skip the mask.
+      float mx = TA_NEG, psum = 0.f;
+      if (kt_begin + it == qt) {
 #pragma unroll
-      for (int j = 0; j < 64; ++j)
-        if (kbase + j <= qi) mx = fmaxf(mx, p[j]);
-      float psum = 0.f;
+        for (int j = 0; j < 64; ++j)
+          if (kbase + j <= qi) mx = fmaxf(mx, p[j]);
+        mx = __fmul_rn(mx, scale_log2e);
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
-        p[j] = (kbase + j <= qi) ? fast_exp2(p[j] - mx) : 0.f;
-        psum += p[j];
+        for (int j = 0; j < 64; ++j) {
+          p[j] = (kbase + j <= qi) ? fast_exp2(__fmaf_rn(p[j], scale_log2e, -mx)) : 0.f;
+          psum += p[j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) mx = fmaxf(mx, p[j]);
+        mx = __fmul_rn(mx, scale_log2e);
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          p[j] = fast_exp2(__fmaf_rn(p[j], scale_log2e, -mx));
+          psum += p[j];
+        }
       }
       if (it > 0) {  // PV(it-1) complete: P may be overwritten, O(it-1) can be read
         ok = mbar_wait_warp(o_full, ph ^ 1u, abort_flag, err, 19);
@@ -461,7 +475,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
         if (stamp && warp == 2 && lane == 0) timeline[15] = global_timer();
 #pragma unroll
         for (int c = 0; c < 32; ++c) o[c] = 0.f;
-#pragma unroll
+#pragma unroll 1
         for (int j = 0; j < TA_MAX_CHUNKS; j += 2) {
           if (j < nchunks) {  // uniform over the CTA
             const float4 *p0 = reinterpret_cast<const float4 *>(part + (first_item + j) * TA_PART) + g * 8 * TA_BQ + r;

@@ -38,10 +38,12 @@ __device__ __forceinline__ unsigned mbar_try_wait(unsigned bar, unsigned parity)
   return ok;
 }
 // Bounded wait: false (and the error word set) if the phase does not complete
-// within WAIT_LIMIT_NS or another role has already given up.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, DevErr *err,
-                                          int where) {
-  if (mbar_try_wait(bar, parity)) return true;
+// within WAIT_LIMIT_NS or another role has already given up. The spinning part
+// is a real function, not inlined at the several dozen wait sites of a kernel:
+// these kernels run a few warps per SM and every kilobyte of code they do not
+// execute still costs instruction-cache space.
+static __device__ __noinline__ bool mbar_wait_slow(unsigned bar, unsigned parity, volatile int *abort_flag, DevErr *err,
+                                            int where) {
   const unsigned long long t0 = global_timer();
   unsigned spins = 0;
   while (true) {
@@ -56,6 +58,11 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, DevErr *err,
+                                          int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, err, where);
 }
 // The same for a whole converged warp: every lane learns the common outcome,
 // so the warp cannot split on a wait that runs out for some lanes only.
