@@ -70,7 +70,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
                const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                TcEpilogue ep, int m, int n, int k, int splits, float *__restrict__ part,
                int *__restrict__ counters, DevErr *err, const float *__restrict__ a_inv_scale,
-               const float *__restrict__ b_inv_scale) {
+               const float *__restrict__ b_inv_scale, int cluster_splits) {
   constexpr int KBE = F16 ? TC_F16_SLOT : TC_BK;  // k elements per k-block
   using L = TcSmem<BN, STAGES>;
   extern __shared__ unsigned char smem_raw[];
@@ -307,19 +307,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     }
     if (stamp && warp == 2 && lane == 0) ep.timeline[5] = global_timer();
     static_assert(TC_BM * (BN + 4) * 4 <= L::TILES_BYTES, "staging tile must fit in the pipeline stages");
-    tc_stage_tile<BN, CW, DRAIN_THREADS>(acc, ok && !*abort_flag, ep, col0, rl, warp == 2 && lane == 0, splits, part,
-                                         counters, last_flag, store_flag, stage, ln_st, row_stats);
+    // (with a cluster per tile every CTA stages its partial tile and the sum happens in the store phase)
+    tc_stage_tile<BN, CW, DRAIN_THREADS>(acc, ok && !*abort_flag, ep, col0, rl, warp == 2 && lane == 0,
+                                         cluster_splits > 1 ? 1 : splits, part, counters, last_flag, store_flag, stage,
+                                         ln_st, row_stats);
   }
   // Store phase, by every warp of the CTA (role and helper warps included: this phase is bound
   // by instruction latency, not bandwidth, and speeds up with the number of warps).
   asm volatile("bar.sync 2, %0;" ::"n"(tc_threads(BN)) : "memory");
+  // Split-k over a cluster: the CTAs of a tile (ranks = blockIdx.z) wait for each other's staged
+  // partial tiles, then each stores its share of the rows, summing the partials in rank order from
+  // its peers' shared memory. No scratch, no counters, and the store work is divided as well.
+  int row_begin = 0, row_end = TC_BM;
+  if (cluster_splits > 1) {
+    cluster_sync_all();
+    const int rows_each = ((TC_BM + cluster_splits - 1) / cluster_splits + 1) & ~1;
+    row_begin = min(TC_BM, (int)blockIdx.z * rows_each);
+    row_end = min(TC_BM, row_begin + rows_each);
+  }
   const bool go = *store_flag != 0;
   if (go && drains && ep.vt_hi != nullptr) tc_store_vt<BN, CW>(ep, m, m0, n0, col0, rl, stage, ln_st);
-  if (go) tc_store_rows<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats);
+  if (go)
+    tc_store_rows<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits, row_begin,
+                                      row_end);
   if (ep.stats_out != nullptr) {
     asm volatile("bar.sync 2, %0;" ::"n"(tc_threads(BN)) : "memory");
-    if (go && drains) tc_store_row_stats<BN, CW>(ep, m, m0, n0, col0, rl, stage);
+    if (go && drains) tc_store_row_stats<BN, CW>(ep, m, m0, n0, col0, rl, stage, row_begin, row_end);
   }
+  if (cluster_splits > 1) cluster_sync_all();  // peers have finished reading this CTA's tile
   if (stamp && warp == 2 && lane == 0) ep.timeline[6] = global_timer();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -436,8 +451,17 @@ void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const
     configured[dev] = true;
   }
   dim3 grid(n / BN, (m + TC_BM - 1) / TC_BM, splits);
-  launch_pdl(gemm_tc_kernel<BN, STAGES, F16>, grid, dim3(tc_threads(BN)), (size_t)L::TOTAL, st, g_pdl_enabled, a.hi,
-             a.lo, b.hi, b.lo, ep, m, n, k, splits, part, counters, err, a_inv_scale, b_inv_scale);
+  // The CTAs that share a tile form a cluster and reduce through distributed shared memory when
+  // they can (at most 8 per cluster; the transposed-V store reads the summed tile locally, so it
+  // keeps the reduction through global scratch).
+  static const bool use_clusters = [] {
+    const char *e = std::getenv("LITNICE_B200_CLUSTER");  // 0: split-k through global scratch instead
+    return !(e && e[0] == '0');
+  }();
+  const int cluster_splits = (use_clusters && splits > 1 && splits <= 8 && ep.vt_hi == nullptr) ? splits : 1;
+  launch_pdl_cluster(gemm_tc_kernel<BN, STAGES, F16>, grid, dim3(tc_threads(BN)), (size_t)L::TOTAL, st, g_pdl_enabled,
+                     (unsigned)cluster_splits, a.hi, a.lo, b.hi, b.lo, ep, m, n, k, splits, part, counters, err,
+                     a_inv_scale, b_inv_scale, cluster_splits);
 }
 
 }  // namespace

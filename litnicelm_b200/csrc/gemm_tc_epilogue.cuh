@@ -3,6 +3,7 @@
 #pragma once
 
 #include "gemm_tc.cuh"
+#include "tc_ptx.cuh"
 
 namespace lb {
 
@@ -14,9 +15,13 @@ namespace lb {
 // deliberately not unrolled (this code runs once per CTA: as straight-line code
 // it ran at the speed of instruction fetch), with the residual rows of the next
 // trip requested before this trip's arithmetic.
+// csplits > 1: the CTAs of a cluster each staged the partial tile of one k range at the
+// same shared-memory offset; this CTA stores rows [row_begin, row_end) (even bounds) and
+// adds the partials of all ranks in rank order, read through distributed shared memory.
 template <int BN, int NT>
 __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n, int m0, int n0, int tid,
-                                              float *stage, const float2 *row_stats) {
+                                              float *stage, const float2 *row_stats, int csplits, int row_begin,
+                                              int row_end) {
   constexpr int LDS = BN + 4;
   constexpr int PER_ROW = BN / 4;
   static_assert(NT % PER_ROW == 0 && NT % 32 == 0, "a thread keeps its column; whole warps");
@@ -31,14 +36,15 @@ __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n
   const float4 bb = ep.bias ? __ldg(reinterpret_cast<const float4 *>(ep.bias + col)) : zero4;
   const float *res_col = ep.residual ? ep.residual + (long long)m0 * n + col : nullptr;
   auto residual_row = [&](int rg) {
-    return (res_col != nullptr && rg < TC_BM && m0 + rg < m) ? __ldg(reinterpret_cast<const float4 *>(res_col + (long long)rg * n))
-                                                             : zero4;
+    return (res_col != nullptr && rg < row_end && m0 + rg < m) ? __ldg(reinterpret_cast<const float4 *>(res_col + (long long)rg * n))
+                                                               : zero4;
   };
+  const unsigned stage_addr = smem_u32(stage);
   float4 res_next[G];
 #pragma unroll
-  for (int g = 0; g < G; ++g) res_next[g] = residual_row(r0 + g * RPT);
+  for (int g = 0; g < G; ++g) res_next[g] = residual_row(row_begin + r0 + g * RPT);
 #pragma unroll 1
-  for (int rr = r0; rr < TC_BM; rr += G * RPT) {
+  for (int rr = row_begin + r0; rr < row_end; rr += G * RPT) {
     float4 v[G], res[G];
     bool act[G], valid[G];
 #pragma unroll
@@ -49,10 +55,18 @@ __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       const int rg = rr + g * RPT;
-      valid[g] = rg < TC_BM;  // the same for all lanes of a warp (a warp covers whole rows or a part of one)
+      valid[g] = rg < row_end;  // the same for all lanes of a warp (a warp covers whole rows or a part of one)
       act[g] = valid[g] && m0 + rg < m && col_active;
       const int rc = valid[g] ? rg : 0;
-      v[g] = *reinterpret_cast<const float4 *>(stage + rc * LDS + c4 * 4);
+      if (csplits > 1) {
+        v[g] = zero4;
+        for (int z = 0; z < csplits; ++z) {
+          const float4 t = ld_cluster_f4(stage_addr + (unsigned)(rc * LDS + c4 * 4) * 4u, (unsigned)z);
+          v[g].x += t.x; v[g].y += t.y; v[g].z += t.z; v[g].w += t.w;
+        }
+      } else {
+        v[g] = *reinterpret_cast<const float4 *>(stage + rc * LDS + c4 * 4);
+      }
       if (fold) {  // inv_std * (x W' - mean * u); v comes in as the bias
         const float2 st = row_stats[rc];
         v[g].x = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.x, v[g].x));
@@ -235,10 +249,10 @@ __device__ __forceinline__ void tc_store_vt(const TcEpilogue &ep, int m, int m0,
 // row, sums over slots of 64 columns in column order.
 template <int BN, int CW>
 __device__ __forceinline__ void tc_store_row_stats(const TcEpilogue &ep, int m, int m0, int n0, int col0, int rl,
-                                                   const float *stage) {
+                                                   const float *stage, int row_begin, int row_end) {
   constexpr int LDS = BN + 4;
   const int row = m0 + rl;
-  if (row >= m) return;
+  if (row >= m || rl < row_begin || rl >= row_end) return;  // rows this CTA stored
 #pragma unroll 1
   for (int j0 = 0; j0 < CW; j0 += 64) {
     double sx = 0.0, sxx = 0.0;

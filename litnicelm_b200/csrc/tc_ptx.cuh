@@ -138,6 +138,24 @@ __device__ __forceinline__ void mbar_arrive(unsigned bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// Thread-block cluster: barrier over all threads of all CTAs of the cluster (hardware barrier; the
+// CTAs of a cluster are co-scheduled), and 16-byte loads from the shared memory of the CTA of a
+// given rank at the same offset as a local address.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_cluster_f4(unsigned local_smem_addr, unsigned cta_rank) {
+  unsigned remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta_rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(remote)
+               : "memory");
+  return v;
+}
+
 // A operand read from tensor memory (lane = row, one column per k element).
 __device__ __forceinline__ void tc_mma_tf32_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long b_desc,
                                                unsigned idesc, unsigned accumulate) {
