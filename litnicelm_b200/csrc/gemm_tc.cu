@@ -458,7 +458,32 @@ void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const
     const char *e = std::getenv("LITNICE_B200_CLUSTER");  // 0: split-k through global scratch instead
     return !(e && e[0] == '0');
   }();
-  const int cluster_splits = (use_clusters && splits > 1 && splits <= 8 && ep.vt_hi == nullptr) ? splits : 1;
+  int cluster_splits = (use_clusters && splits > 1 && splits <= 8 && ep.vt_hi == nullptr) ? splits : 1;
+  if (cluster_splits > 1) {
+    // A cluster must sit inside one GPC: fewer clusters than SMs / splits may be resident at once. When
+    // the grid does not fit in one wave of clusters the scratch path (any SM will do) is the faster one.
+    static int max_clusters[9] = {};  // per cluster size; 0 = not asked yet (one device type per process)
+    if (max_clusters[cluster_splits] == 0) {
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = grid;
+      cfg.blockDim = dim3(tc_threads(BN));
+      cfg.dynamicSmemBytes = (size_t)L::TOTAL;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = (unsigned)cluster_splits;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int nc = 0;
+      if (cudaOccupancyMaxActiveClusters(&nc, gemm_tc_kernel<BN, STAGES, F16>, &cfg) != cudaSuccess || nc <= 0) {
+        (void)cudaGetLastError();
+        nc = -1;
+      }
+      max_clusters[cluster_splits] = nc;
+    }
+    if ((long long)grid.x * grid.y > max_clusters[cluster_splits]) cluster_splits = 1;
+  }
   launch_pdl_cluster(gemm_tc_kernel<BN, STAGES, F16>, grid, dim3(tc_threads(BN)), (size_t)L::TOTAL, st, g_pdl_enabled,
                      (unsigned)cluster_splits, a.hi, a.lo, b.hi, b.lo, ep, m, n, k, splits, part, counters, err,
                      a_inv_scale, b_inv_scale, cluster_splits);
