@@ -199,6 +199,13 @@ void launch_embed_pos(const float *tok_emb, const float *pos_emb, const int *ids
                       const LoopState *state, int n_streams, int s_host, int d, int vocab,
                       float *x, DevErr *err, cudaStream_t st, float *x_hi = nullptr, float *x_lo = nullptr,
                       double2 *stats = nullptr, const struct TcPairF16 *x_f16 = nullptr);
+// head_greedy.cu: final norm + output head + first-max selection + append +
+// state advance in one launch (greedy, few streams, vocabulary up to 1024).
+// `done` is a zero-initialised counter the kernel returns to zero.
+bool head_greedy_supports(int n_streams, int d, int vocab);
+void launch_head_greedy(const float *x, const float *gamma, const float *beta, const float *w, int d, int vocab,
+                        int n_streams, int s_host, const LoopState *dstate, LoopState *state, unsigned *done,
+                        int *ids, int ids_ld, int *out_tokens, int out_ld, float *logits, cudaStream_t st);
 void launch_gather_last_ln(const float *x, const float *gamma, const float *beta,
                            const LoopState *state, int n_streams, int s_host, int d, float *out,
                            float *out_lo, cudaStream_t st);

@@ -132,6 +132,7 @@ struct litnice_b200_session {
   // tensor-core path: low parts of the split activations (ln/ctx/h/xl hold the high parts)
   bool tc = false;
   bool pdl = true;         // early launch of dependent kernels (LITNICE_B200_PDL=0 disables)
+  bool fused_tail = true;  // greedy steps end in one launch: norm, head, selection, advance (LITNICE_B200_FUSED_TAIL=0 disables)
   bool use_graphs = true;  // replay one captured step per 64-token context bucket (LITNICE_B200_GRAPHS=0 disables)
   struct StepGraph {
     cudaGraphExec_t exec = nullptr;
@@ -748,6 +749,8 @@ int litnice_b200_session_create(const litnice_b200_dims *dims, int32_t max_strea
     s->pdl = !(pdl_env && pdl_env[0] == '0');
     const char *graph_env = std::getenv("LITNICE_B200_GRAPHS");
     s->use_graphs = !(graph_env && graph_env[0] == '0');
+    const char *tail_env = std::getenv("LITNICE_B200_FUSED_TAIL");
+    s->fused_tail = !(tail_env && tail_env[0] == '0');
     const char *tc_env = std::getenv("LITNICE_B200_TC");
     s->tc = !(tc_env && tc_env[0] == '0') && tc_runtime_available() && d.d_model % 64 == 0 && d.d_ff % 64 == 0;
     // Attention on the tensor cores needs head dimension 64; LITNICE_B200_TC_ATTN=0
@@ -785,7 +788,9 @@ int litnice_b200_session_create(const litnice_b200_dims *dims, int32_t max_strea
     must(cudaMalloc(reinterpret_cast<void **>(&s->ids), (size_t)max_streams * d.max_seq_len * 4));
     LB_CUDA(cudaMemsetAsync(s->ids, 0, (size_t)max_streams * d.max_seq_len * 4, s->st));
     must(cudaMalloc(reinterpret_cast<void **>(&s->mt), (size_t)max_streams * 625 * 4));
-    must(cudaMalloc(reinterpret_cast<void **>(&s->state), sizeof(LoopState)));
+    // the loop state, followed by the fused greedy tail's finished-CTA counter
+    must(cudaMalloc(reinterpret_cast<void **>(&s->state), sizeof(LoopState) + 16));
+    LB_CUDA(cudaMemsetAsync(s->state, 0, sizeof(LoopState) + 16, s->st));
     LB_CUDA(cudaStreamSynchronize(s->st));
     return LITNICE_B200_OK;
   });
@@ -984,8 +989,16 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
     // the device-side LoopState) and replayed for every step in the bucket, so
     // the host issues one launch per token instead of ~50.
     const bool graphs = s->use_graphs && !s->keep_logits;
+    const bool fused_tail = greedy && !s->keep_logits && s->fused_tail && head_greedy_supports(B, s->dims.d_model, V);
     auto enqueue_step = [&](int sl_cap, const LoopState *dstate, int step) {
       enqueue_body(s, B, sl_cap, dstate);
+      if (fused_tail) {
+        launch_head_greedy(s->x, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), P(s, s->lay.lm_head), s->dims.d_model, V, B,
+                           sl_cap, dstate, s->state, reinterpret_cast<unsigned *>(s->state + 1), s->ids,
+                           s->dims.max_seq_len, s->out_tokens, s->out_cap, s->logits, s->st);
+        ++s->launches;
+        return;
+      }
       enqueue_head_last(s, B, sl_cap, dstate);
       if (s->keep_logits) {
         LB_CUDA(cudaMemcpyAsync(s->step_logits + (long long)(s->cur_tokens + step) * B * V, s->logits,
