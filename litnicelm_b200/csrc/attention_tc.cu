@@ -47,6 +47,8 @@ constexpr float TA_NEG = -3.402823466e+38f;
 constexpr int TA_STAGE_LD = TA_DH + 4;  // row pitch of the output staging tile: conflict-free 16-byte accesses
 constexpr int TA_MAX_CHUNKS = 16;  // chunks one query tile's keys are cut into, at most
 constexpr int TA_PART = TA_BQ * TA_DH + 2 * TA_BQ;  // floats of one partial: o[128][64], m[128], l[128]
+constexpr int TA_O_BYTES = TA_BQ * TA_DH * 4;       // the o part of a partial
+constexpr int TA_MERGE_SLOTS = 6;  // partial outputs the merging CTA holds in shared memory at a time (the Q, K and V^T tiles)
 
 // shared memory (after 1024-byte alignment)
 constexpr int TA_SLAB = TA_BQ * 128;                    // one 32-wide k-block of a 128-row tile
@@ -59,7 +61,9 @@ constexpr int TA_K_OFF = TA_Q_OFF + TA_Q_BYTES;
 constexpr int TA_V_OFF = TA_K_OFF + TA_K_BYTES;
 constexpr int TA_BAR_OFF = TA_V_OFF + TA_V_BYTES;       // 7 barriers + holders
 constexpr int TA_XCH_OFF = TA_BAR_OFF + 128;            // [2 parities][max half 0, max half 1, sum half 0, sum half 1][128]
-constexpr int TA_SMEM = TA_XCH_OFF + 8 * TA_BQ * 4 + 1024;
+constexpr int TA_AMAX_OFF = TA_XCH_OFF + 8 * TA_BQ * 4;  // [2 halves][128 rows]: largest magnitudes of the output rows
+constexpr int TA_SMEM = TA_AMAX_OFF + 2 * TA_BQ * 4 + 1024;
+constexpr int TA_STAGE16_LD = TA_DH * 2 + 16;  // bytes per row of a staged fp16 tile: conflict-free 16-byte accesses
 
 // tensor-memory columns
 constexpr unsigned TA_S_COL = 0;      // S: 128 columns (keys)
@@ -86,7 +90,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
   unsigned char *base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const unsigned bar_base = base + TA_BAR_OFF;
   const unsigned q_full = bar_base, k_full = bar_base + 8, v_full = bar_base + 16, s_full = bar_base + 24,
-                 p_ready = bar_base + 32, o_full = bar_base + 40, s_read = bar_base + 48;
+                 p_ready = bar_base + 32, o_full = bar_base + 40, s_read = bar_base + 48, m_full = bar_base + 56;
   volatile unsigned *tmem_holder = reinterpret_cast<volatile unsigned *>(base_ptr + TA_BAR_OFF + 64);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + TA_BAR_OFF + 68);
   volatile int *last_flag = reinterpret_cast<volatile int *>(base_ptr + TA_BAR_OFF + 72);
@@ -112,9 +116,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
   const int row0 = b * s;  // first row of this stream in the packed activations
 
   pdl_launch_dependents();
-  // Measurement aid: CTA (0,0,0) stamps its milestones in timeline[0..7]; every
+  // Measurement aid: the CTA of head 0, stream 0 that takes the diagonal tile of the last query tile (it usually
+  // ends last and merges) stamps its milestones in timeline[0..7]; every
   // CTA contributes to the earliest start [8], the latest end [9] and the latest start [10].
-  const bool stamp = timeline != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  const bool stamp = timeline != nullptr && (int)blockIdx.x == ta_chunks_of(tiles - 1, kc) - 1 && blockIdx.y == 0 && blockIdx.z == 0;
   if (timeline != nullptr && threadIdx.x == 0) {
     const unsigned long long t = global_timer();
     atomicMin(timeline + 8, t);
@@ -129,6 +134,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
     mbar_init(p_ready, TA_SOFTMAX_THREADS / 32);  // one arrival per softmax warp
     mbar_init(o_full, 1);
     mbar_init(s_read, TA_SOFTMAX_THREADS / 32);
+    mbar_init(m_full, 1);
     *abort_flag = 0;
     *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -422,6 +428,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     bool finish = ok && !*abort_flag;
+    bool cta_out = true;  // uniform over the CTA: false for a chunk's CTA that does not merge
     float l_tot = l_run;
 
     if (nchunks > 1) {
@@ -438,23 +445,39 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
         mine[TA_BQ * TA_DH + TA_BQ + r] = l_tot;
       }
       if (stamp && warp == 2 && lane == 0) timeline[12] = global_timer();
-      __threadfence();
-      asm volatile("bar.sync 1, %0;" ::"n"(TA_SOFTMAX_THREADS) : "memory");
+      // The partial outputs come into the merging CTA's shared memory (the operand tiles are dead
+      // by then) as bulk copies that are all in flight together, so that the merge costs one L2
+      // round trip and not one per chunk; the maxima and sums are read directly meanwhile.
+      auto fetch = [&](int first) {
+        const int n = min(TA_MERGE_SLOTS, nchunks - first);
+        const bool own = chunk >= first && chunk < first + n;  // this CTA's chunk is still in its registers
+        asm volatile("fence.proxy.async;" ::: "memory");
+        mbar_expect_tx(m_full, (unsigned)((n - (own ? 1 : 0)) * TA_O_BYTES));
+        for (int j = 0; j < n; ++j)
+          if (first + j != chunk)
+            bulk_load(base + (unsigned)(j * TA_O_BYTES), part + (first_item + first + j) * TA_PART,
+                      (unsigned)TA_O_BYTES, m_full);
+      };
+      asm volatile("bar.sync 1, %0;" ::"n"(TA_SOFTMAX_THREADS) : "memory");  // every thread's stores are issued
       if (stamp && warp == 2 && lane == 0) timeline[13] = global_timer();
       int *counter = counters + bh * tiles + qt;
       if (warp == 2 && lane == 0) {
+        __threadfence();  // cumulative over the stores ordered before it by the barrier
         const int prev = atomicAdd(counter, 1);
         const int last = (prev == nchunks - 1) ? 1 : 0;
-        if (last) *counter = 0;  // ready for the next launch
+        if (last) {
+          *counter = 0;  // ready for the next launch
+          __threadfence();
+          fetch(0);
+        }
         *last_flag = last;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(TA_SOFTMAX_THREADS) : "memory");
-      finish = finish && (*last_flag != 0);
+      const bool merging = *last_flag != 0;  // uniform over the CTA
+      finish = finish && merging;
+      cta_out = merging;
       if (stamp && warp == 2 && lane == 0) timeline[14] = global_timer();
-      if (finish) {
-        __threadfence();
-        // All loads of a step are issued before their first use: the merge is a
-        // chain of L2 round trips otherwise. Chunks are combined in chunk order.
+      if (merging) {
         float wv[TA_MAX_CHUNKS], lv[TA_MAX_CHUNKS];
 #pragma unroll
         for (int j = 0; j < TA_MAX_CHUNKS; ++j) {
@@ -472,31 +495,42 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
           wv[j] = j < nchunks ? fast_exp2(wv[j] - mm) : 0.f;
           ll = fmaf(lv[j], wv[j], ll);
         }
-        if (stamp && warp == 2 && lane == 0) timeline[15] = global_timer();
+        float acc[32];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) o[c] = 0.f;
+        for (int c = 0; c < 32; ++c) acc[c] = 0.f;
+        // Chunks are combined in chunk order.
 #pragma unroll 1
-        for (int j = 0; j < TA_MAX_CHUNKS; j += 2) {
-          if (j < nchunks) {  // uniform over the CTA
-            const float4 *p0 = reinterpret_cast<const float4 *>(part + (first_item + j) * TA_PART) + g * 8 * TA_BQ + r;
-            const float4 *p1 =
-                reinterpret_cast<const float4 *>(part + (first_item + min(j + 1, nchunks - 1)) * TA_PART) + g * 8 * TA_BQ + r;
-            float4 t0[8], t1[8];
+        for (int first = 0, batch = 0; first < nchunks; first += TA_MERGE_SLOTS, ++batch) {
+          if (batch > 0) {
+            asm volatile("bar.sync 1, %0;" ::"n"(TA_SOFTMAX_THREADS) : "memory");  // the slots have been read
+            if (warp == 2 && lane == 0) fetch(first);
+          }
+          const bool got = mbar_wait_warp(m_full, (unsigned)batch & 1u, abort_flag, err, 20);
+          finish = finish && got;
+          if (stamp && batch == 0 && warp == 2 && lane == 0) timeline[15] = global_timer();
+          const int n = got ? min(TA_MERGE_SLOTS, nchunks - first) : 0;
+#pragma unroll 1
+          for (int j = 0; j < n; ++j) {
+            const float4 *ps = reinterpret_cast<const float4 *>(base_ptr + j * TA_O_BYTES) + g * 8 * TA_BQ + r;
+            const float w = wv[first + j];
+            if (first + j == chunk) {  // uniform over the CTA
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              t0[c] = __ldcg(p0 + c * TA_BQ);
-              t1[c] = __ldcg(p1 + c * TA_BQ);
-            }
-            const float w0 = wv[j], w1 = (j + 1 < TA_MAX_CHUNKS) ? wv[j + 1] : 0.f;  // w1 = 0 past the last chunk
+              for (int c = 0; c < 32; ++c) acc[c] = fmaf(o[c], w, acc[c]);
+            } else {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              o[4 * c] = fmaf(t1[c].x, w1, fmaf(t0[c].x, w0, o[4 * c]));
-              o[4 * c + 1] = fmaf(t1[c].y, w1, fmaf(t0[c].y, w0, o[4 * c + 1]));
-              o[4 * c + 2] = fmaf(t1[c].z, w1, fmaf(t0[c].z, w0, o[4 * c + 2]));
-              o[4 * c + 3] = fmaf(t1[c].w, w1, fmaf(t0[c].w, w0, o[4 * c + 3]));
+              for (int c = 0; c < 8; ++c) {
+                const float4 t = ps[c * TA_BQ];
+                acc[4 * c] = fmaf(t.x, w, acc[4 * c]);
+                acc[4 * c + 1] = fmaf(t.y, w, acc[4 * c + 1]);
+                acc[4 * c + 2] = fmaf(t.z, w, acc[4 * c + 2]);
+                acc[4 * c + 3] = fmaf(t.w, w, acc[4 * c + 3]);
+              }
             }
           }
         }
+#pragma unroll
+        for (int c = 0; c < 32; ++c) o[c] = acc[c];
+        asm volatile("bar.sync 1, %0;" ::"n"(TA_SOFTMAX_THREADS) : "memory");  // before the output is staged over the slots
         l_tot = ll;
       }
     }
@@ -504,42 +538,80 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
     if (stamp && warp == 2 && lane == 0) timeline[6] = global_timer();
     // Output: a thread holds 32 columns of one row, so direct stores would touch 32
     // different lines per instruction. Normalise, transpose through the (now idle) Q
-    // tile in shared memory, and store whole rows: 16 lanes x 16 bytes per row.
-    float *stage = reinterpret_cast<float *>(base_ptr + TA_Q_OFF);  // [128][TA_STAGE_LD]
-    if (finish) {
-      const float inv = 1.0f / l_tot;
+    // tile in shared memory, and store whole rows.
+    if (!cta_out) {
+      // nothing to store: another CTA merges this chunk
+    } else if (ctx_f16.hi != nullptr) {
+      // fp16 pair with one scale per row of this head's 64 columns. The two threads of a row
+      // exchange their largest magnitudes and convert before staging, so the store loop only copies.
+      float *amx = reinterpret_cast<float *>(base_ptr + TA_AMAX_OFF);  // [2][128]
+      unsigned char *st_hi = base_ptr + TA_Q_OFF;                      // [128][TA_STAGE16_LD] bytes
+      unsigned char *st_lo = st_hi + TA_BQ * TA_STAGE16_LD;
+      const float inv = finish ? 1.0f / l_tot : 0.f;
+      float am = 0.f;
 #pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<float4 *>(stage + r * TA_STAGE_LD + g * 32 + j) =
-            make_float4(o[j] * inv, o[j + 1] * inv, o[j + 2] * inv, o[j + 3] * inv);
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(TA_SOFTMAX_THREADS) : "memory");
-    finish = __all_sync(0xffffffffu, finish);  // whole warps store or skip together (the fp16 store shuffles)
-    if (finish) {
-      const int t2 = threadIdx.x - 64;
+      for (int j = 0; j < 32; ++j) {
+        o[j] *= inv;
+        am = fmaxf(am, fabsf(o[j]));
+      }
+      amx[g * TA_BQ + r] = am;
+      asm volatile("bar.sync 1, %0;" ::"n"(TA_SOFTMAX_THREADS) : "memory");
+      am = fmaxf(amx[r], amx[TA_BQ + r]);
+      float sinv;
+      const float scale = f16_block_scale(am, &sinv);
 #pragma unroll
-      for (int i = 0; i < TA_BQ * TA_DH / 4 / TA_SOFTMAX_THREADS; ++i) {
-        const int u = t2 + i * TA_SOFTMAX_THREADS;
-        const int row = u >> 4, c4 = u & 15;
-        if (ctx_f16.hi != nullptr) {
-          // fp16 pair with one scale per row of this head's 64 columns (16 lanes = one block)
-          const bool active = q0 + row < s;
-          const float4 v = active ? *reinterpret_cast<const float4 *>(stage + row * TA_STAGE_LD + c4 * 4)
-                                  : make_float4(0.f, 0.f, 0.f, 0.f);
-          const long long grow = (long long)row0 + q0 + row;
-          const long long off = grow * d_model + h * TA_DH + c4 * 4;
-          f16_store_block(v, active, ctx_f16.hi + off, ctx_f16.lo + off,
-                          ctx_f16.inv_scale + grow * (d_model / TC_F16_SLOT) + h);
-        } else if (q0 + row < s) {
-          const float4 v = *reinterpret_cast<const float4 *>(stage + row * TA_STAGE_LD + c4 * 4);
-          float4 hh, ll;
-          split_tf32(v.x, hh.x, ll.x);
-          split_tf32(v.y, hh.y, ll.y);
-          split_tf32(v.z, hh.z, ll.z);
-          split_tf32(v.w, hh.w, ll.w);
-          const long long off = ((long long)row0 + q0 + row) * d_model + h * TA_DH + c4 * 4;
-          *reinterpret_cast<float4 *>(ctx_hi + off) = hh;
-          *reinterpret_cast<float4 *>(ctx_lo + off) = ll;
+      for (int j = 0; j < 32; j += 8) {
+        uint2 h0, l0, h1, l1;
+        f16_pair4(make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]), scale, h0, l0);
+        f16_pair4(make_float4(o[j + 4], o[j + 5], o[j + 6], o[j + 7]), scale, h1, l1);
+        *reinterpret_cast<uint4 *>(st_hi + r * TA_STAGE16_LD + g * 64 + j * 2) = make_uint4(h0.x, h0.y, h1.x, h1.y);
+        *reinterpret_cast<uint4 *>(st_lo + r * TA_STAGE16_LD + g * 64 + j * 2) = make_uint4(l0.x, l0.y, l1.x, l1.y);
+      }
+      if (finish && g == 0 && q0 + r < s)
+        ctx_f16.inv_scale[((long long)row0 + q0 + r) * (d_model / TC_F16_SLOT) + h] = sinv;
+      asm volatile("bar.sync 1, %0;" ::"n"(TA_SOFTMAX_THREADS) : "memory");
+      if (finish) {
+        const int t2 = threadIdx.x - 64;
+#pragma unroll
+        for (int i = 0; i < TA_BQ * 8 / TA_SOFTMAX_THREADS; ++i) {  // 8 lanes x 16 bytes = one row of 64 halves
+          const int u = t2 + i * TA_SOFTMAX_THREADS;
+          const int row = u >> 3, seg = u & 7;
+          if (q0 + row < s) {
+            const long long off = ((long long)row0 + q0 + row) * d_model + h * TA_DH + seg * 8;
+            *reinterpret_cast<uint4 *>(ctx_f16.hi + off) =
+                *reinterpret_cast<const uint4 *>(st_hi + row * TA_STAGE16_LD + seg * 16);
+            *reinterpret_cast<uint4 *>(ctx_f16.lo + off) =
+                *reinterpret_cast<const uint4 *>(st_lo + row * TA_STAGE16_LD + seg * 16);
+          }
+        }
+      }
+    } else {
+      float *stage = reinterpret_cast<float *>(base_ptr + TA_Q_OFF);  // [128][TA_STAGE_LD]
+      if (finish) {
+        const float inv = 1.0f / l_tot;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4 *>(stage + r * TA_STAGE_LD + g * 32 + j) =
+              make_float4(o[j] * inv, o[j + 1] * inv, o[j + 2] * inv, o[j + 3] * inv);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(TA_SOFTMAX_THREADS) : "memory");
+      if (finish) {
+        const int t2 = threadIdx.x - 64;
+#pragma unroll 1  // runs once per CTA: a short loop is fetched once, eight copies of it eight times
+        for (int i = 0; i < TA_BQ * TA_DH / 4 / TA_SOFTMAX_THREADS; ++i) {
+          const int u = t2 + i * TA_SOFTMAX_THREADS;
+          const int row = u >> 4, c4 = u & 15;
+          if (q0 + row < s) {
+            const float4 v = *reinterpret_cast<const float4 *>(stage + row * TA_STAGE_LD + c4 * 4);
+            float4 hh, ll;
+            split_tf32(v.x, hh.x, ll.x);
+            split_tf32(v.y, hh.y, ll.y);
+            split_tf32(v.z, hh.z, ll.z);
+            split_tf32(v.w, hh.w, ll.w);
+            const long long off = ((long long)row0 + q0 + row) * d_model + h * TA_DH + c4 * 4;
+            *reinterpret_cast<float4 *>(ctx_hi + off) = hh;
+            *reinterpret_cast<float4 *>(ctx_lo + off) = ll;
+          }
         }
       }
     }

@@ -77,6 +77,13 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *map
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// Untiled bulk copy global -> this CTA's shared memory, completion counted in bytes on an
+// mbarrier. Both addresses 16-byte aligned, the size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(unsigned dst, const void *src, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
 __device__ __forceinline__ void tc_mma_tf32(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
                                             unsigned idesc, unsigned accumulate) {
   asm volatile(
