@@ -146,6 +146,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_holder;
   if (stamp && threadIdx.x == 0) ep.timeline[1] = global_timer();
+  // The store phase starts with the tile's per-column terms (immutable since the weights were
+  // loaded): bring their lines into L1 now, so that it does not start with an L2 round trip.
+  if (threadIdx.x < BN / 32) {
+    if (ep.bias != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(ep.bias + n0 + threadIdx.x * 32));
+    if (ep.ln_u != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(ep.ln_u + n0 + threadIdx.x * 32));
+  }
 
   // Whole warps take a role and stay converged (block-wide barriers count
   // warps, so a warp must never reach one in pieces); one lane issues.
@@ -319,22 +325,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   // partial tiles, then each stores its share of the rows, summing the partials in rank order from
   // its peers' shared memory. No scratch, no counters, and the store work is divided as well.
   int row_begin = 0, row_end = TC_BM;
+  if (stamp && warp == 2 && lane == 0) ep.timeline[10] = global_timer();
   if (cluster_splits > 1) {
-    cluster_sync_all();
     const int rows_each = ((TC_BM + cluster_splits - 1) / cluster_splits + 1) & ~1;
     row_begin = min(TC_BM, (int)blockIdx.z * rows_each);
     row_end = min(TC_BM, row_begin + rows_each);
   }
+  TcStoreFirst first;
+  tc_store_first<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, row_begin, row_end, first);
+  if (cluster_splits > 1) cluster_sync_all();
   const bool go = *store_flag != 0;
+  if (stamp && warp == 2 && lane == 0) ep.timeline[11] = global_timer();
   if (go && drains && ep.vt_hi != nullptr) tc_store_vt<BN, CW>(ep, m, m0, n0, col0, rl, stage, ln_st);
   if (go)
     tc_store_rows<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits, row_begin,
-                                      row_end);
+                                      row_end, first);
+  // This CTA has read what it needs of its peers' tiles; it leaves once they have read its own.
+  if (cluster_splits > 1) cluster_arrive_relaxed();
+  if (stamp && warp == 2 && lane == 0) ep.timeline[12] = global_timer();
   if (ep.stats_out != nullptr) {
     asm volatile("bar.sync 2, %0;" ::"n"(tc_threads(BN)) : "memory");
     if (go && drains) tc_store_row_stats<BN, CW>(ep, m, m0, n0, col0, rl, stage, row_begin, row_end);
   }
-  if (cluster_splits > 1) cluster_sync_all();  // peers have finished reading this CTA's tile
+  if (stamp && warp == 2 && lane == 0) ep.timeline[13] = global_timer();
+  if (cluster_splits > 1) cluster_wait();  // peers have finished reading this CTA's tile
   if (stamp && warp == 2 && lane == 0) ep.timeline[6] = global_timer();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();

@@ -7,6 +7,33 @@
 
 namespace lb {
 
+// What the store phase reads from global memory before its first arithmetic: the per-column
+// terms (bias, folded-LayerNorm u) and the residual rows of the first step. Loaded ahead of
+// it (before the wait for the cluster's partial tiles), because the store loop would
+// otherwise start with an L2 round trip. Same thread-to-element mapping as tc_store_rows.
+struct TcStoreFirst {
+  float4 res[2];
+  float4 uu, bb;
+};
+template <int BN, int NT>
+__device__ __forceinline__ void tc_store_first(const TcEpilogue &ep, int m, int n, int m0, int n0, int tid,
+                                               int row_begin, int row_end, TcStoreFirst &out) {
+  constexpr int PER_ROW = BN / 4;
+  constexpr int RPT = NT / PER_ROW;
+  const int c4 = tid % PER_ROW, r0 = tid / PER_ROW;
+  const int col = n0 + c4 * 4;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  out.uu = ep.ln_u != nullptr ? __ldg(reinterpret_cast<const float4 *>(ep.ln_u + col)) : zero4;
+  out.bb = ep.bias != nullptr ? __ldg(reinterpret_cast<const float4 *>(ep.bias + col)) : zero4;
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    const int rg = row_begin + r0 + g * RPT;
+    out.res[g] = (ep.residual != nullptr && rg < row_end && m0 + rg < m)
+                     ? __ldg(reinterpret_cast<const float4 *>(ep.residual + (long long)(m0 + rg) * n + col))
+                     : zero4;
+  }
+}
+
 // The store phase: NT threads (whole warps, thread index tid) walk the staged
 // 128 x BN fp32 tile row by row, a float4 each, apply the epilogue terms and
 // write the results in every requested format. A thread keeps its column for the
@@ -21,28 +48,28 @@ namespace lb {
 template <int BN, int NT>
 __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n, int m0, int n0, int tid,
                                               float *stage, const float2 *row_stats, int csplits, int row_begin,
-                                              int row_end) {
+                                              int row_end, const TcStoreFirst &first) {
   constexpr int LDS = BN + 4;
   constexpr int PER_ROW = BN / 4;
   static_assert(NT % PER_ROW == 0 && NT % 32 == 0, "a thread keeps its column; whole warps");
   constexpr int RPT = NT / PER_ROW;  // rows covered by the threads at once
-  constexpr int G = 2;
+  constexpr int G = 2;  // as tc_store_first
   const int c4 = tid % PER_ROW, r0 = tid / PER_ROW;
   const int col = n0 + c4 * 4;
   const bool col_active = !(ep.vt_hi != nullptr && col >= ep.vt_col0);  // V columns leave transposed, elsewhere
   const bool fold = ep.ln_u != nullptr;
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  const float4 uu = fold ? __ldg(reinterpret_cast<const float4 *>(ep.ln_u + col)) : zero4;
-  const float4 bb = ep.bias ? __ldg(reinterpret_cast<const float4 *>(ep.bias + col)) : zero4;
+  const float4 uu = first.uu, bb = first.bb;
   const float *res_col = ep.residual ? ep.residual + (long long)m0 * n + col : nullptr;
   auto residual_row = [&](int rg) {
     return (res_col != nullptr && rg < row_end && m0 + rg < m) ? __ldg(reinterpret_cast<const float4 *>(res_col + (long long)rg * n))
                                                                : zero4;
   };
+  // split-k over a cluster: the staged partial tiles of all ranks, through the cluster's shared window
   const unsigned stage_addr = smem_u32(stage);
   float4 res_next[G];
 #pragma unroll
-  for (int g = 0; g < G; ++g) res_next[g] = residual_row(row_begin + r0 + g * RPT);
+  for (int g = 0; g < G; ++g) res_next[g] = first.res[g];
 #pragma unroll 1
   for (int rr = row_begin + r0; rr < row_end; rr += G * RPT) {
     float4 v[G], res[G];
@@ -52,21 +79,42 @@ __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n
       res[g] = res_next[g];
       res_next[g] = residual_row(rr + (G + g) * RPT);
     }
+    if (csplits > 1) {
+      // All remote loads of a step are issued before the first is used: each is a round trip of
+      // several hundred clocks. Partials are added in rank order.
+#pragma unroll
+      for (int g = 0; g < G; ++g) v[g] = zero4;
+#pragma unroll
+      for (int z0 = 0; z0 < 8; z0 += 4) {
+        if (z0 < csplits) {  // uniform
+          float4 t[G][4];
+          unsigned peer[4];
+#pragma unroll
+          for (int z = 0; z < 4; ++z) peer[z] = cluster_map(stage_addr, (unsigned)min(z0 + z, csplits - 1));
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const int rg = rr + g * RPT;
+            const unsigned off = (unsigned)((rg < row_end ? rg : 0) * LDS + c4 * 4) * 4u;
+#pragma unroll
+            for (int z = 0; z < 4; ++z) t[g][z] = ld_cluster_mapped_f4(peer[z] + off);
+          }
+#pragma unroll
+          for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int z = 0; z < 4; ++z)
+              if (z0 + z < csplits) {
+                v[g].x += t[g][z].x; v[g].y += t[g][z].y; v[g].z += t[g][z].z; v[g].w += t[g][z].w;
+              }
+        }
+      }
+    }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       const int rg = rr + g * RPT;
       valid[g] = rg < row_end;  // the same for all lanes of a warp (a warp covers whole rows or a part of one)
       act[g] = valid[g] && m0 + rg < m && col_active;
       const int rc = valid[g] ? rg : 0;
-      if (csplits > 1) {
-        v[g] = zero4;
-        for (int z = 0; z < csplits; ++z) {
-          const float4 t = ld_cluster_f4(stage_addr + (unsigned)(rc * LDS + c4 * 4) * 4u, (unsigned)z);
-          v[g].x += t.x; v[g].y += t.y; v[g].z += t.z; v[g].w += t.w;
-        }
-      } else {
-        v[g] = *reinterpret_cast<const float4 *>(stage + rc * LDS + c4 * 4);
-      }
+      if (csplits <= 1) v[g] = *reinterpret_cast<const float4 *>(stage + rc * LDS + c4 * 4);
       if (fold) {  // inv_std * (x W' - mean * u); v comes in as the bias
         const float2 st = row_stats[rc];
         v[g].x = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.x, v[g].x));

@@ -1310,10 +1310,12 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
         const unsigned long long *u = t.data() + 32 * i;
         std::fprintf(stderr,
                      "projection launch %d (ns from CTA start): setup %lld, loads issued %lld, first stage %lld, mma "
-                     "issued %lld, drained %lld, stored %lld, end %lld; whole grid %lld\n",
+                     "issued %lld, drained %lld, staged %lld, peers staged %lld, rows stored %lld, statistics %lld, "
+                     "stored %lld, end %lld; whole grid %lld\n",
                      i, (long long)(u[1] - u[0]), (long long)(u[2] - u[0]), (long long)(u[3] - u[0]),
-                     (long long)(u[4] - u[0]), (long long)(u[5] - u[0]), (long long)(u[6] - u[0]),
-                     (long long)(u[7] - u[0]), (long long)(u[9] - u[8]));
+                     (long long)(u[4] - u[0]), (long long)(u[5] - u[0]), (long long)(u[10] - u[0]),
+                     (long long)(u[11] - u[0]), (long long)(u[12] - u[0]), (long long)(u[13] - u[0]),
+                     (long long)(u[6] - u[0]), (long long)(u[7] - u[0]), (long long)(u[9] - u[8]));
       }
     }
     if (s->attn_timeline) {

@@ -152,6 +152,31 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Split form for a barrier that orders no memory ("my peers have finished reading my shared
+// memory"): the releasing arrive of cluster_sync_all would first wait for every global store
+// the CTA has in flight, a microsecond after a store phase.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address in the cluster's shared window of this CTA's shared address in the CTA of the given rank.
+__device__ __forceinline__ unsigned cluster_map(unsigned local_smem_addr, unsigned cta_rank) {
+  unsigned remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta_rank));
+  return remote;
+}
+// No memory clobber: the caller orders these loads with the cluster barriers around the phase
+// that issues them, and several must be in flight at once (a remote load is a round trip of
+// several hundred clocks).
+__device__ __forceinline__ float4 ld_cluster_mapped_f4(unsigned cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr));
+  return v;
+}
 __device__ __forceinline__ float4 ld_cluster_f4(unsigned local_smem_addr, unsigned cta_rank) {
   unsigned remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta_rank));
