@@ -59,7 +59,7 @@ def reference_flops(d: formats.ModelDims, s: int) -> float:
 
 # dram__bytes_read.sum + dram__bytes_write.sum per projection launch from the ncu
 # capture summarised under profiles/ (mean over the four projections of a layer).
-NCU_DRAM_BYTES_PER_GEMM_LAUNCH = {"c2": 6.3e6}
+NCU_DRAM_BYTES_PER_GEMM_LAUNCH = {"c2": 6.4e6}
 
 
 def load_peaks():
