@@ -336,7 +336,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   if (cluster_splits > 1) cluster_sync_all();
   const bool go = *store_flag != 0;
   if (stamp && warp == 2 && lane == 0) ep.timeline[11] = global_timer();
-  if (go && drains && ep.vt_hi != nullptr) tc_store_vt<BN, CW>(ep, m, m0, n0, col0, rl, stage, ln_st);
+  if (go && ep.vt_hi != nullptr) tc_store_vt<BN, tc_threads(BN)>(ep, m, m0, n0, (int)threadIdx.x, stage, row_stats);
   if (go)
     tc_store_rows<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits, row_begin,
                                       row_end, first);

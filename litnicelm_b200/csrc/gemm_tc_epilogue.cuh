@@ -250,45 +250,44 @@ __device__ __forceinline__ bool tc_stage_tile(float (&acc)[CW], bool finish, con
   return finish;
 }
 
-// After the staged tile is visible to the drain warps (a barrier): the V^T
-// columns of a QKV projection leave transposed, thread = row (lanes = consecutive
-// positions of one column), element (row r = stream * s + t, column vt_col0 + c)
-// to vt[(stream * vt_rows + c) * vt_pitch + t]. A short loop, like the store phase.
-template <int BN, int CW>
-__device__ __forceinline__ void tc_store_vt(const TcEpilogue &ep, int m, int m0, int n0, int col0, int rl,
-                                            const float *stage, float2 ln_st) {
+// After the staged tile is visible to every warp (a barrier): the V^T columns of a QKV
+// projection leave transposed, element (row r = stream * s + t, column vt_col0 + c) to
+// vt[(stream * vt_rows + c) * vt_pitch + t]. All NT threads take part: a warp handles units
+// of 32 consecutive rows x 4 columns (lane = row, so the 32 lanes write consecutive positions
+// of one V^T row: whole 128-byte lines), a float4 of the staged tile per lane. vt_col0 is a
+// multiple of 64, so a unit is all V or not V.
+template <int BN, int NT>
+__device__ __forceinline__ void tc_store_vt(const TcEpilogue &ep, int m, int m0, int n0, int tid, const float *stage,
+                                            const float2 *row_stats) {
   constexpr int LDS = BN + 4;
-  const int row = m0 + rl;
-  if (row >= m || n0 + col0 + CW <= ep.vt_col0) return;
+  constexpr int UNITS = (BN / 4) * (TC_BM / 32);
+  if (n0 + BN <= ep.vt_col0) return;
+  const int warp = tid >> 5, lane = tid & 31;
   const int sl = ep.state ? ep.state->s : ep.vt_s;
-  const int v_stream = row / sl, v_tok = row - v_stream * sl;
-  if (v_stream >= ep.vt_streams) return;
-  const int first = n0 + col0 < ep.vt_col0 ? ep.vt_col0 - (n0 + col0) : 0;  // first V column of this thread's range
-  const long long at0 = ((long long)v_stream * ep.vt_rows + (n0 + col0 + first - ep.vt_col0)) * ep.vt_pitch + v_tok;
-  float *out_hi = ep.vt_hi + at0, *out_lo = ep.vt_lo + at0;
-  const float *up = ep.ln_u ? ep.ln_u + n0 + col0 + first : nullptr;
-  const float *bp = ep.bias ? ep.bias + n0 + col0 + first : nullptr;
-  const float *sp = stage + rl * LDS + col0 + first;
-  const float fold_scale = ep.ln_u ? ln_st.y : 1.f, fold_mean = ep.ln_u ? ln_st.x : 0.f;
+  const bool fold = ep.ln_u != nullptr;
 #pragma unroll 1
-  for (int j = first; j < CW; j += 4) {
-    const float4 t = *reinterpret_cast<const float4 *>(sp);
-    const float4 u4 = up ? __ldg(reinterpret_cast<const float4 *>(up)) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 b4 = bp ? __ldg(reinterpret_cast<const float4 *>(bp)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int u = warp; u < UNITS; u += NT / 32) {
+    const int cg = u / (TC_BM / 32), rg = u - cg * (TC_BM / 32);
+    const int col = n0 + cg * 4;
+    if (col < ep.vt_col0) continue;  // uniform over the warp
+    const int rl = rg * 32 + lane, row = m0 + rl;
+    const int v_stream = row / sl, v_tok = row - v_stream * sl;
+    const bool act = row < m && v_stream < ep.vt_streams;
+    const float4 t = *reinterpret_cast<const float4 *>(stage + rl * LDS + cg * 4);
+    const float4 u4 = fold ? __ldg(reinterpret_cast<const float4 *>(ep.ln_u + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 b4 = ep.bias ? __ldg(reinterpret_cast<const float4 *>(ep.bias + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float2 st = fold ? row_stats[rl] : make_float2(0.f, 1.f);
+    if (!act) continue;
     const float vals[4] = {t.x, t.y, t.z, t.w}, us[4] = {u4.x, u4.y, u4.z, u4.w}, bs[4] = {b4.x, b4.y, b4.z, b4.w};
+    const long long at0 = ((long long)v_stream * ep.vt_rows + (col - ep.vt_col0)) * ep.vt_pitch + v_tok;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const float val = up ? __fmul_rn(fold_scale, __fmaf_rn(-fold_mean, us[e], vals[e])) : vals[e];
+      const float val = fold ? __fmul_rn(st.y, __fmaf_rn(-st.x, us[e], vals[e])) : vals[e];
       float hh, ll;
       split_tf32(val + bs[e], hh, ll);
-      out_hi[(long long)e * ep.vt_pitch] = hh;
-      out_lo[(long long)e * ep.vt_pitch] = ll;
+      ep.vt_hi[at0 + (long long)e * ep.vt_pitch] = hh;
+      ep.vt_lo[at0 + (long long)e * ep.vt_pitch] = ll;
     }
-    sp += 4;
-    if (up) up += 4;
-    if (bp) bp += 4;
-    out_hi += 4LL * ep.vt_pitch;
-    out_lo += 4LL * ep.vt_pitch;
   }
 }
 
