@@ -345,7 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   if (stamp && warp == 2 && lane == 0) ep.timeline[12] = global_timer();
   if (ep.stats_out != nullptr) {
     asm volatile("bar.sync 2, %0;" ::"n"(tc_threads(BN)) : "memory");
-    if (go && drains) tc_store_row_stats<BN, CW>(ep, m, m0, n0, col0, rl, stage, row_begin, row_end);
+    if (go) tc_store_row_stats<BN, tc_threads(BN)>(ep, m, m0, n0, (int)threadIdx.x, stage, row_begin, row_end);
   }
   if (stamp && warp == 2 && lane == 0) ep.timeline[13] = global_timer();
   if (cluster_splits > 1) cluster_wait();  // peers have finished reading this CTA's tile

@@ -292,26 +292,42 @@ __device__ __forceinline__ void tc_store_vt(const TcEpilogue &ep, int m, int m0,
 }
 
 // After the store phase has put the final values back into the staged tile (a
-// barrier): row statistics for a LayerNorm folded into the next product, thread =
-// row, sums over slots of 64 columns in column order.
-template <int BN, int CW>
-__device__ __forceinline__ void tc_store_row_stats(const TcEpilogue &ep, int m, int m0, int n0, int col0, int rl,
+// barrier): row statistics for a LayerNorm folded into the next product, (sum x,
+// sum x^2) in double per row and slot of 64 columns. By all NT threads: four
+// consecutive lanes share a (row, slot), each sums 16 columns in column order and
+// the first adds the four partial sums in order (a fixed order, so the statistics
+// do not depend on the tile plan).
+template <int BN, int NT>
+__device__ __forceinline__ void tc_store_row_stats(const TcEpilogue &ep, int m, int m0, int n0, int tid,
                                                    const float *stage, int row_begin, int row_end) {
   constexpr int LDS = BN + 4;
-  const int row = m0 + rl;
-  if (row >= m || rl < row_begin || rl >= row_end) return;  // rows this CTA stored
+  constexpr int SLOTS = BN / 64;
+  const int total = (row_end - row_begin) * SLOTS;
+  const int q = tid & 3;
 #pragma unroll 1
-  for (int j0 = 0; j0 < CW; j0 += 64) {
+  for (int u0 = (tid >> 5) * 8; u0 < total; u0 += NT / 4) {  // the warp's first unit: the trip count is per warp
+    const int u = u0 + ((tid & 31) >> 2);
+    const bool valid = u < total;
+    const int rl = row_begin + (valid ? u / SLOTS : 0), slot = valid ? u % SLOTS : 0;
+    const float *sp = stage + rl * LDS + slot * 64 + q * 16;
     double sx = 0.0, sxx = 0.0;
-#pragma unroll 2
-    for (int j = 0; j < 64; j += 4) {
-      const float4 t = *reinterpret_cast<const float4 *>(stage + rl * LDS + col0 + j0 + j);
+#pragma unroll
+    for (int j = 0; j < 16; j += 4) {
+      const float4 t = *reinterpret_cast<const float4 *>(sp + j);
       sx += (double)t.x; sxx += (double)t.x * (double)t.x;
       sx += (double)t.y; sxx += (double)t.y * (double)t.y;
       sx += (double)t.z; sxx += (double)t.z * (double)t.z;
       sx += (double)t.w; sxx += (double)t.w * (double)t.w;
     }
-    ep.stats_out[(long long)row * TC_STAT_SLOTS + (n0 + col0 + j0) / 64] = make_double2(sx, sxx);
+    double tx = sx, txx = sxx;
+#pragma unroll
+    for (int d = 1; d < 4; ++d) {
+      tx += __shfl_down_sync(0xffffffffu, sx, d);
+      txx += __shfl_down_sync(0xffffffffu, sxx, d);
+    }
+    const int row = m0 + rl;
+    if (valid && q == 0 && row < m)
+      ep.stats_out[(long long)row * TC_STAT_SLOTS + (n0 + slot * 64) / 64] = make_double2(tx, txx);
   }
 }
 
