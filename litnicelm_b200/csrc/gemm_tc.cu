@@ -104,6 +104,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   const int rl = q * 32 + lane;                             // its row inside the tile
   const int row = m0 + rl;
   float2 ln_st = make_float2(0.f, 1.f);
+  float acc[CW];        // the drain warps' accumulated columns (kept past the role code for the cluster's exchange)
+  bool pushes = false;  // this thread sends partial sums to the rows' owners
   float *stage = reinterpret_cast<float *>(base_ptr);       // the tile, once the pipeline stages are idle
   float2 *row_stats = reinterpret_cast<float2 *>(base_ptr + L::ROWSTATS_OFFSET);
   // With split-k (gridDim.z CTAs per tile) this CTA owns k-blocks [kb0, kb0 + kblocks).
@@ -279,7 +281,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     // sums its producer left (read while the first tiles are still in flight)
     if (ep.ln_u != nullptr && row < m)
       ln_st = ln_row_stats(ep.ln_stats + (long long)row * TC_STAT_SLOTS, ep.ln_slots, k);
-    float acc[CW];
 #pragma unroll
     for (int j = 0; j < CW; ++j) acc[j] = 0.f;
     // fp16 pairs: every chain (one 64-wide k-block) carries the product of its operands' block scales
@@ -312,43 +313,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
       if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
     }
     if (stamp && warp == 2 && lane == 0) ep.timeline[5] = global_timer();
-    static_assert(TC_BM * (BN + 4) * 4 <= L::TILES_BYTES, "staging tile must fit in the pipeline stages");
-    // (with a cluster per tile every CTA stages its partial tile and the sum happens in the store phase)
-    tc_stage_tile<BN, CW, DRAIN_THREADS>(acc, ok && !*abort_flag, ep, col0, rl, warp == 2 && lane == 0,
-                                         cluster_splits > 1 ? 1 : splits, part, counters, last_flag, store_flag, stage,
-                                         ln_st, row_stats);
+    // (a cluster's ranks cover up to 140 rows between them: rows_each is rounded up to even)
+    static_assert((TC_BM + 16) * (BN + 4) * 4 <= L::TILES_BYTES, "staging tile must fit in the pipeline stages");
+    // (with a cluster per tile the partial sums stay in registers until the peers' operand tiles are dead)
+    pushes = tc_stage_tile<BN, CW, DRAIN_THREADS>(acc, ok && !*abort_flag, ep, col0, rl, warp == 2 && lane == 0,
+                                                  cluster_splits > 1 ? 1 : splits, part, counters, last_flag,
+                                                  store_flag, stage, ln_st, row_stats, cluster_splits > 1) &&
+             cluster_splits > 1;
   }
   // Store phase, by every warp of the CTA (role and helper warps included: this phase is bound
   // by instruction latency, not bandwidth, and speeds up with the number of warps).
   asm volatile("bar.sync 2, %0;" ::"n"(tc_threads(BN)) : "memory");
-  // Split-k over a cluster: the CTAs of a tile (ranks = blockIdx.z) wait for each other's staged
-  // partial tiles, then each stores its share of the rows, summing the partials in rank order from
-  // its peers' shared memory. No scratch, no counters, and the store work is divided as well.
-  int row_begin = 0, row_end = TC_BM;
+  // Split-k over a cluster: the CTAs of a tile (ranks = blockIdx.z) each store a share of its rows.
+  // Once every CTA of the cluster is past its k loop (first barrier: the staging area overlays the
+  // operand tiles), each sends its partial sums of a row to the CTA that stores the row; after the
+  // second barrier every CTA adds what it received, in rank order, from its own shared memory. No
+  // scratch, no counters, no remote loads, and the store work is divided as well.
+  int row_begin = 0, row_end = TC_BM, rows_each = TC_BM;
   if (stamp && warp == 2 && lane == 0) ep.timeline[10] = global_timer();
   if (cluster_splits > 1) {
-    const int rows_each = ((TC_BM + cluster_splits - 1) / cluster_splits + 1) & ~1;
+    rows_each = ((TC_BM + cluster_splits - 1) / cluster_splits + 1) & ~1;
     row_begin = min(TC_BM, (int)blockIdx.z * rows_each);
     row_end = min(TC_BM, row_begin + rows_each);
   }
   TcStoreFirst first;
   tc_store_first<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, row_begin, row_end, first);
-  if (cluster_splits > 1) cluster_sync_all();
+  if (cluster_splits > 1) {
+    cluster_arrive_relaxed();
+    cluster_wait();
+    if (pushes) tc_push_tile<BN, CW>(acc, stage, col0, rl, rows_each);
+    cluster_sync_all();
+  }
   const bool go = *store_flag != 0;
   if (stamp && warp == 2 && lane == 0) ep.timeline[11] = global_timer();
   if (go && ep.vt_hi != nullptr) tc_store_vt<BN, tc_threads(BN)>(ep, m, m0, n0, (int)threadIdx.x, stage, row_stats);
   if (go)
-    tc_store_rows<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits, row_begin,
-                                      row_end, first);
-  // This CTA has read what it needs of its peers' tiles; it leaves once they have read its own.
-  if (cluster_splits > 1) cluster_arrive_relaxed();
+    tc_store_rows<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits, rows_each,
+                                      row_begin, row_end, first);
   if (stamp && warp == 2 && lane == 0) ep.timeline[12] = global_timer();
   if (ep.stats_out != nullptr) {
     asm volatile("bar.sync 2, %0;" ::"n"(tc_threads(BN)) : "memory");
     if (go) tc_store_row_stats<BN, tc_threads(BN)>(ep, m, m0, n0, (int)threadIdx.x, stage, row_begin, row_end);
   }
   if (stamp && warp == 2 && lane == 0) ep.timeline[13] = global_timer();
-  if (cluster_splits > 1) cluster_wait();  // peers have finished reading this CTA's tile
   if (stamp && warp == 2 && lane == 0) ep.timeline[6] = global_timer();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();

@@ -42,13 +42,14 @@ __device__ __forceinline__ void tc_store_first(const TcEpilogue &ep, int m, int 
 // deliberately not unrolled (this code runs once per CTA: as straight-line code
 // it ran at the speed of instruction fetch), with the residual rows of the next
 // trip requested before this trip's arithmetic.
-// csplits > 1: the CTAs of a cluster each staged the partial tile of one k range at the
-// same shared-memory offset; this CTA stores rows [row_begin, row_end) (even bounds) and
-// adds the partials of all ranks in rank order, read through distributed shared memory.
+// csplits > 1 (split-k over a cluster): this CTA stores rows [row_begin, row_end) of the tile;
+// every rank has pushed its partial sums of those rows into this CTA's staging area, rank z
+// at rows [z * rows_each, z * rows_each + row_end - row_begin), and they are added in rank
+// order. Otherwise the area holds the tile itself (row_begin 0).
 template <int BN, int NT>
 __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n, int m0, int n0, int tid,
-                                              float *stage, const float2 *row_stats, int csplits, int row_begin,
-                                              int row_end, const TcStoreFirst &first) {
+                                              float *stage, const float2 *row_stats, int csplits, int rows_each,
+                                              int row_begin, int row_end, const TcStoreFirst &first) {
   constexpr int LDS = BN + 4;
   constexpr int PER_ROW = BN / 4;
   static_assert(NT % PER_ROW == 0 && NT % 32 == 0, "a thread keeps its column; whole warps");
@@ -65,8 +66,6 @@ __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n
     return (res_col != nullptr && rg < row_end && m0 + rg < m) ? __ldg(reinterpret_cast<const float4 *>(res_col + (long long)rg * n))
                                                                : zero4;
   };
-  // split-k over a cluster: the staged partial tiles of all ranks, through the cluster's shared window
-  const unsigned stage_addr = smem_u32(stage);
   float4 res_next[G];
 #pragma unroll
   for (int g = 0; g < G; ++g) res_next[g] = first.res[g];
@@ -79,42 +78,18 @@ __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n
       res[g] = res_next[g];
       res_next[g] = residual_row(rr + (G + g) * RPT);
     }
-    if (csplits > 1) {
-      // All remote loads of a step are issued before the first is used: each is a round trip of
-      // several hundred clocks. Partials are added in rank order.
-#pragma unroll
-      for (int g = 0; g < G; ++g) v[g] = zero4;
-#pragma unroll
-      for (int z0 = 0; z0 < 8; z0 += 4) {
-        if (z0 < csplits) {  // uniform
-          float4 t[G][4];
-          unsigned peer[4];
-#pragma unroll
-          for (int z = 0; z < 4; ++z) peer[z] = cluster_map(stage_addr, (unsigned)min(z0 + z, csplits - 1));
-#pragma unroll
-          for (int g = 0; g < G; ++g) {
-            const int rg = rr + g * RPT;
-            const unsigned off = (unsigned)((rg < row_end ? rg : 0) * LDS + c4 * 4) * 4u;
-#pragma unroll
-            for (int z = 0; z < 4; ++z) t[g][z] = ld_cluster_mapped_f4(peer[z] + off);
-          }
-#pragma unroll
-          for (int g = 0; g < G; ++g)
-#pragma unroll
-            for (int z = 0; z < 4; ++z)
-              if (z0 + z < csplits) {
-                v[g].x += t[g][z].x; v[g].y += t[g][z].y; v[g].z += t[g][z].z; v[g].w += t[g][z].w;
-              }
-        }
-      }
-    }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       const int rg = rr + g * RPT;
       valid[g] = rg < row_end;  // the same for all lanes of a warp (a warp covers whole rows or a part of one)
       act[g] = valid[g] && m0 + rg < m && col_active;
-      const int rc = valid[g] ? rg : 0;
-      if (csplits <= 1) v[g] = *reinterpret_cast<const float4 *>(stage + rc * LDS + c4 * 4);
+      const int rc = valid[g] ? rg : row_begin;
+      const float *sp = stage + (rc - row_begin) * LDS + c4 * 4;
+      v[g] = *reinterpret_cast<const float4 *>(sp);
+      for (int z = 1; z < csplits; ++z) {
+        const float4 t = *reinterpret_cast<const float4 *>(sp + z * rows_each * LDS);
+        v[g].x += t.x; v[g].y += t.y; v[g].z += t.z; v[g].w += t.w;
+      }
       if (fold) {  // inv_std * (x W' - mean * u); v comes in as the bias
         const float2 st = row_stats[rc];
         v[g].x = __fmul_rn(st.y, __fmaf_rn(-st.x, uu.x, v[g].x));
@@ -147,7 +122,8 @@ __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n
         *reinterpret_cast<float4 *>(ep.c_hi + off) = hh;
         *reinterpret_cast<float4 *>(ep.c_lo + off) = ll;
       }
-      if (ep.stats_out != nullptr) *reinterpret_cast<float4 *>(stage + rg * LDS + c4 * 4) = v[g];  // final values
+      if (ep.stats_out != nullptr)  // final values, over the thread's own rank-0 partial
+        *reinterpret_cast<float4 *>(stage + (rg - row_begin) * LDS + c4 * 4) = v[g];
     }
     if (ep.c_f16.hi != nullptr) {
       // fp16 pair: the 16 lanes of a 64-column block of a row agree on its scale
@@ -186,7 +162,7 @@ __device__ __forceinline__ bool tc_stage_tile(float (&acc)[CW], bool finish, con
                                               bool leader, int splits, float *__restrict__ part,
                                               int *__restrict__ counters, volatile int *last_flag,
                                               volatile int *store_flag, float *stage, float2 ln_st,
-                                              float2 *row_stats) {
+                                              float2 *row_stats, bool defer_stage) {
   finish = __all_sync(0xffffffffu, finish);
   if (splits > 1) {
     // Partial tiles are laid out [column / 4][row][4] so that the 32 rows of a
@@ -241,13 +217,33 @@ __device__ __forceinline__ bool tc_stage_tile(float (&acc)[CW], bool finish, con
   }
   constexpr int LDS = BN + 4;
   if (finish) {
+    if (!defer_stage) {
 #pragma unroll
-    for (int j = 0; j < CW; j += 4)
-      *reinterpret_cast<float4 *>(stage + rl * LDS + col0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      for (int j = 0; j < CW; j += 4)
+        *reinterpret_cast<float4 *>(stage + rl * LDS + col0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+    }
     if (ep.ln_u != nullptr && col0 == 0) row_stats[rl] = ln_st;
   }
   if (leader) *store_flag = finish ? 1 : 0;
   return finish;
+}
+
+// Split-k over a cluster: a drain thread sends its CW partial sums of tile row rl to the CTA
+// that stores that row (rank rl / rows_each), into the slot of this CTA's rank, with remote
+// shared-memory stores: nothing waits for them but the cluster barrier that follows, whereas
+// the owner pulling the rows cost a remote round trip of over a microsecond at the start of
+// its store phase. Only after a cluster barrier that says every CTA's operand tiles are dead
+// (the staging area overlays them).
+template <int BN, int CW>
+__device__ __forceinline__ void tc_push_tile(const float (&acc)[CW], const float *stage, int col0, int rl,
+                                             int rows_each) {
+  constexpr int LDS = BN + 4;
+  const int owner = rl / rows_each, local = rl - owner * rows_each;
+  const unsigned at = cluster_map(smem_u32(stage) + (unsigned)(((int)blockIdx.z * rows_each + local) * LDS + col0) * 4u,
+                                  (unsigned)owner);
+#pragma unroll
+  for (int j = 0; j < CW; j += 4)
+    st_cluster_f4(at + (unsigned)j * 4u, make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]));
 }
 
 // After the staged tile is visible to every warp (a barrier): the V^T columns of a QKV
@@ -309,7 +305,7 @@ __device__ __forceinline__ void tc_store_row_stats(const TcEpilogue &ep, int m, 
     const int u = u0 + ((tid & 31) >> 2);
     const bool valid = u < total;
     const int rl = row_begin + (valid ? u / SLOTS : 0), slot = valid ? u % SLOTS : 0;
-    const float *sp = stage + rl * LDS + slot * 64 + q * 16;
+    const float *sp = stage + (rl - row_begin) * LDS + slot * 64 + q * 16;
     double sx = 0.0, sxx = 0.0;
 #pragma unroll
     for (int j = 0; j < 16; j += 4) {

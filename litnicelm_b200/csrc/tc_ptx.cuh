@@ -177,6 +177,11 @@ __device__ __forceinline__ float4 ld_cluster_mapped_f4(unsigned cluster_addr) {
                : "r"(cluster_addr));
   return v;
 }
+__device__ __forceinline__ void st_cluster_f4(unsigned cluster_addr, float4 v) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w)
+               : "memory");
+}
 __device__ __forceinline__ float4 ld_cluster_f4(unsigned local_smem_addr, unsigned cta_rank) {
   unsigned remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta_rank));
