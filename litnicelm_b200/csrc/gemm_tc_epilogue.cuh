@@ -11,8 +11,10 @@ namespace lb {
 // terms (bias, folded-LayerNorm u) and the residual rows of the first step. Loaded ahead of
 // it (before the wait for the cluster's partial tiles), because the store loop would
 // otherwise start with an L2 round trip. Same thread-to-element mapping as tc_store_rows.
+constexpr int TC_STORE_G = 2;  // rows a thread of the store phase has in flight per trip
+
 struct TcStoreFirst {
-  float4 res[2];
+  float4 res[TC_STORE_G];
   float4 uu, bb;
 };
 template <int BN, int NT>
@@ -26,7 +28,7 @@ __device__ __forceinline__ void tc_store_first(const TcEpilogue &ep, int m, int 
   out.uu = ep.ln_u != nullptr ? __ldg(reinterpret_cast<const float4 *>(ep.ln_u + col)) : zero4;
   out.bb = ep.bias != nullptr ? __ldg(reinterpret_cast<const float4 *>(ep.bias + col)) : zero4;
 #pragma unroll
-  for (int g = 0; g < 2; ++g) {
+  for (int g = 0; g < TC_STORE_G; ++g) {
     const int rg = row_begin + r0 + g * RPT;
     out.res[g] = (ep.residual != nullptr && rg < row_end && m0 + rg < m)
                      ? __ldg(reinterpret_cast<const float4 *>(ep.residual + (long long)(m0 + rg) * n + col))
@@ -54,7 +56,7 @@ __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n
   constexpr int PER_ROW = BN / 4;
   static_assert(NT % PER_ROW == 0 && NT % 32 == 0, "a thread keeps its column; whole warps");
   constexpr int RPT = NT / PER_ROW;  // rows covered by the threads at once
-  constexpr int G = 2;  // as tc_store_first
+  constexpr int G = TC_STORE_G;
   const int c4 = tid % PER_ROW, r0 = tid / PER_ROW;
   const int col = n0 + c4 * 4;
   const bool col_active = !(ep.vt_hi != nullptr && col >= ep.vt_col0);  // V columns leave transposed, elsewhere
