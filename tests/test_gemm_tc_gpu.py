@@ -78,6 +78,28 @@ def test_tensor_core_epilogue(project, relu):
         np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-4)
 
 
+# Few tiles and a long k: the CTAs of a tile form a cluster of 2..8 k ranges (how many depends on the
+# tile count and on the operand type's k-block), each sends its partial sums of a row to the CTA that
+# stores the row. The shapes give row shares of 64 down to 16 rows, even and uneven, and a ragged last tile.
+CLUSTER_SHAPES = [(256, 512, 1024), (640, 2048, 512), (256, 1024, 512), (128, 1280, 640),
+                  (300, 2048, 512), (128, 1792, 768), (200, 2048, 256), (77, 4096, 128)]
+
+
+@pytest.mark.parametrize("m,k,n", CLUSTER_SHAPES)
+def test_cluster_split_k_with_epilogue(project, m, k, n):
+    rng = np.random.default_rng(m + k + n)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((k, n)) * 0.05).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = rng.standard_normal((m, n)).astype(np.float32)
+    want = np.maximum(a.astype(np.float64) @ w.astype(np.float64) + bias + res, 0)
+    for engine in (1, 2):
+        got = project(engine, a, w, bias, res, True)
+        np.testing.assert_allclose(got, want, rtol=1e-5, atol=2e-5 * np.sqrt(k), err_msg=f"engine {engine}")
+        again = project(engine, a, w, bias, res, True)
+        assert np.array_equal(got, again), "partial sums are added in rank order: bit-identical between runs"
+
+
 def test_tensor_core_engine_rejects_unsupported_shapes(project):
     lib = plugin.load_library()
     a = np.zeros((4, 48), np.float32)
