@@ -651,6 +651,15 @@ AttentionPlan attention_tc_plan(int n_streams, int s, int n_heads) {
     if (per_cta < 1) per_cta = 1;
     if (per_cta < tiles) kc = (int)per_cta;
   }
+  // The rounding of the chunk counts can still leave more CTAs than SMs (8 heads x 8 tiles at 2 key
+  // tiles per CTA: 160): a second wave costs more than a longer walk.
+  auto ctas_at = [&](int c) {
+    long long n = 0;
+    for (int qt = 0; qt < tiles; ++qt) n += ta_chunks_of(qt, c);
+    return n * bh;
+  };
+  if (kc < tiles)
+    while (kc < tiles && ctas_at(kc) > 148) ++kc;
   while (ta_chunks_of(tiles - 1, kc) > TA_MAX_CHUNKS) ++kc;
   p.kc = kc;
   int ctas = 0;
