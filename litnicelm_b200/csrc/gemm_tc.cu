@@ -458,6 +458,15 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// LITNICE_B200_CLUSTER=0: split-k through global scratch instead of clusters.
+bool tc_clusters_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("LITNICE_B200_CLUSTER");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 template <int BN, int STAGES, bool F16>
 void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const TcEpilogue &ep, int splits,
                 float *part, int *counters, DevErr *err, cudaStream_t st, const float *a_inv_scale = nullptr,
@@ -475,10 +484,7 @@ void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const
   // The CTAs that share a tile form a cluster and reduce through distributed shared memory when
   // they can (at most 8 per cluster; the transposed-V store reads the summed tile locally, so it
   // keeps the reduction through global scratch).
-  static const bool use_clusters = [] {
-    const char *e = std::getenv("LITNICE_B200_CLUSTER");  // 0: split-k through global scratch instead
-    return !(e && e[0] == '0');
-  }();
+  const bool use_clusters = tc_clusters_enabled();
   int cluster_splits = (use_clusters && splits > 1 && splits <= 8 && ep.vt_hi == nullptr) ? splits : 1;
   if (cluster_splits > 1) {
     // A cluster must sit inside one GPC: fewer clusters than SMs / splits may be resident at once. When
@@ -548,7 +554,40 @@ void tc_make_map_f16(CUtensorMap *map, const __half *base, unsigned long long ro
     throw std::runtime_error("litnice_b200: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
 }
 
-TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256, int k_block) {
+// How many clusters of 2..8 CTAs of these kernels the device holds at once (a cluster sits inside
+// one GPC); -1 where the runtime cannot say. Every configuration runs one CTA per SM, so one of them
+// stands for all.
+const int *tc_cluster_capacity() {
+  static int cap[9] = {};
+  static std::once_flag once;
+  std::call_once(once, []() {
+    using L = TcSmem<128, 3>;
+    for (int cs = 2; cs <= 8; ++cs) {
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(1, 1, (unsigned)cs);
+      cfg.blockDim = dim3(tc_threads(128));
+      cfg.dynamicSmemBytes = (size_t)L::TOTAL;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = (unsigned)cs;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int nc = 0;
+      if (cudaFuncSetAttribute(gemm_tc_kernel<128, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) !=
+              cudaSuccess ||
+          cudaOccupancyMaxActiveClusters(&nc, gemm_tc_kernel<128, 3, true>, &cfg) != cudaSuccess || nc <= 0) {
+        (void)cudaGetLastError();
+        nc = -1;
+      }
+      cap[cs] = nc;
+    }
+  });
+  return cap;
+}
+
+TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256, int k_block, bool clusters_ok) {
   TcPlan p{};
   const long long mt = (m + TC_BM - 1) / TC_BM;
   // One thread issues every tcgen05.mma of a CTA, at most one per ~40 ns, and a
@@ -568,6 +607,28 @@ TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256, int k_
     if (splits < 1) splits = 1;
     const int per = (kb + splits - 1) / splits;
     splits = (kb + per - 1) / per;  // no empty split
+    // A long k on few tiles: a 128-column tile halves the tile count, so twice the k ranges fit,
+    // and it reads less shared memory per flop; its larger epilogue costs about three k-blocks.
+    // Only as clusters (the partial sums of a wide tile through global scratch are too slow).
+    if (clusters_ok && tc_clusters_enabled() && p.bn == 64 && has128) {
+      const int *cap = tc_cluster_capacity();
+      const long long wide = mt * (n / 128);
+      int s2 = (int)(148 / wide);
+      if (s2 > kb / 4) s2 = kb / 4;
+      if (s2 > 8) s2 = 8;
+      while (s2 >= 2 && (cap[s2] <= 0 || wide > cap[s2])) --s2;
+      if (s2 >= 2) {
+        const int per2 = (kb + s2 - 1) / s2;
+        s2 = (kb + per2 - 1) / per2;
+        if (per2 + 2 <= per && cap[s2] > 0 && wide <= cap[s2]) {
+          p.bn = 128;
+          p.splits = s2;
+          p.scratch_floats = (size_t)wide * s2 * TC_BM * 128;
+          p.counters = (size_t)wide;
+          return p;
+        }
+      }
+    }
   }
   p.splits = splits;
   p.scratch_floats = splits > 1 ? (size_t)ctas * splits * TC_BM * p.bn : 0;

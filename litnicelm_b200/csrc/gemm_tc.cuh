@@ -96,7 +96,9 @@ struct TcPlan {
   size_t counters;
 };
 // k_block: k elements per pipeline stage (32 for TF32 pairs, 64 for fp16 pairs).
-TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256, int k_block = TC_BK);
+// clusters_ok: the epilogue allows split-k over a thread-block cluster (not with the transposed-V store).
+TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256, int k_block = TC_BK,
+               bool clusters_ok = true);
 
 // Requires n % plan.bn == 0, k % 32 == 0; a maps must use box rows 128, b maps
 // box rows plan.bn.
