@@ -646,7 +646,9 @@ AttentionPlan attention_tc_plan(int n_streams, int s, int n_heads) {
   // One CTA per SM (all of tensor memory, 192 KB of tiles). Without a split the
   // longest CTA walks `tiles` key tiles; split when that leaves SMs idle.
   int kc = tiles;
-  if (bh * tiles < 148) {
+  // Two key tiles a CTA walks itself: one more tile (2 us) costs less than the publish / fetch /
+  // merge round trip of a split (5 us); from three tiles on the split is as fast or faster.
+  if (bh * tiles < 148 && tiles > 2) {
     long long per_cta = (units + 147) / 148;
     if (per_cta < 1) per_cta = 1;
     if (per_cta < tiles) kc = (int)per_cta;
