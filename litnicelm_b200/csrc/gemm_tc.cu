@@ -346,7 +346,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   }
   const bool go = *store_flag != 0;
   if (stamp && warp == 2 && lane == 0) ep.timeline[11] = global_timer();
-  if (go && ep.vt_hi != nullptr) tc_store_vt<BN, tc_threads(BN)>(ep, m, m0, n0, (int)threadIdx.x, stage, row_stats);
+  if (go && ep.vt_hi != nullptr)
+    tc_store_vt<BN, tc_threads(BN)>(ep, m, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits, rows_each, row_begin,
+                                    row_end);
   if (go && !(ep.vt_hi != nullptr && n0 >= ep.vt_col0))  // a tile of V columns only has left already
     tc_store_rows<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits, rows_each,
                                       row_begin, row_end, first);
@@ -482,10 +484,9 @@ void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const
   }
   dim3 grid(n / BN, (m + TC_BM - 1) / TC_BM, splits);
   // The CTAs that share a tile form a cluster and reduce through distributed shared memory when
-  // they can (at most 8 per cluster; the transposed-V store reads the summed tile locally, so it
-  // keeps the reduction through global scratch).
+  // they can (at most 8 per cluster).
   const bool use_clusters = tc_clusters_enabled();
-  int cluster_splits = (use_clusters && splits > 1 && splits <= 8 && ep.vt_hi == nullptr) ? splits : 1;
+  int cluster_splits = (use_clusters && splits > 1 && splits <= 8) ? splits : 1;
   if (cluster_splits > 1) {
     // A cluster must sit inside one GPC: fewer clusters than SMs / splits may be resident at once. When
     // the grid does not fit in one wave of clusters the scratch path (any SM will do) is the faster one.

@@ -96,7 +96,7 @@ struct TcPlan {
   size_t counters;
 };
 // k_block: k elements per pipeline stage (32 for TF32 pairs, 64 for fp16 pairs).
-// clusters_ok: the epilogue allows split-k over a thread-block cluster (not with the transposed-V store).
+// clusters_ok: false plans for split-k through global scratch only.
 TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256, int k_block = TC_BK,
                bool clusters_ok = true);
 

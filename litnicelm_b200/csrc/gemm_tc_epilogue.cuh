@@ -256,22 +256,32 @@ __device__ __forceinline__ void tc_push_tile(const float (&acc)[CW], const float
 // multiple of 64, so a unit is all V or not V.
 template <int BN, int NT>
 __device__ __forceinline__ void tc_store_vt(const TcEpilogue &ep, int m, int m0, int n0, int tid, const float *stage,
-                                            const float2 *row_stats) {
+                                            const float2 *row_stats, int csplits, int rows_each, int row_begin,
+                                            int row_end) {
   constexpr int LDS = BN + 4;
-  constexpr int UNITS = (BN / 4) * (TC_BM / 32);
   if (n0 + BN <= ep.vt_col0) return;
+  // the rows this CTA stores (all of the tile without a cluster), and the partial sums of every rank as tc_store_rows
+  const int rows = row_end - row_begin, rgroups = (rows + 31) / 32;
+  const int units = (BN / 4) * rgroups;
   const int warp = tid >> 5, lane = tid & 31;
   const int sl = ep.state ? ep.state->s : ep.vt_s;
   const bool fold = ep.ln_u != nullptr;
 #pragma unroll 1
-  for (int u = warp; u < UNITS; u += NT / 32) {
-    const int cg = u / (TC_BM / 32), rg = u - cg * (TC_BM / 32);
+  for (int u = warp; u < units; u += NT / 32) {
+    const int cg = u / rgroups, rg = u - cg * rgroups;
     const int col = n0 + cg * 4;
     if (col < ep.vt_col0) continue;  // uniform over the warp
-    const int rl = rg * 32 + lane, row = m0 + rl;
+    const int local = rg * 32 + lane;
+    const bool valid = local < rows;
+    const int rl = row_begin + (valid ? local : 0), row = m0 + rl;
     const int v_stream = row / sl, v_tok = row - v_stream * sl;
-    const bool act = row < m && v_stream < ep.vt_streams;
-    const float4 t = *reinterpret_cast<const float4 *>(stage + rl * LDS + cg * 4);
+    const bool act = valid && row < m && v_stream < ep.vt_streams;
+    const float *sp = stage + (rl - row_begin) * LDS + cg * 4;
+    float4 t = *reinterpret_cast<const float4 *>(sp);
+    for (int z = 1; z < csplits; ++z) {
+      const float4 tz = *reinterpret_cast<const float4 *>(sp + z * rows_each * LDS);
+      t.x += tz.x; t.y += tz.y; t.z += tz.z; t.w += tz.w;
+    }
     const float4 u4 = fold ? __ldg(reinterpret_cast<const float4 *>(ep.ln_u + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
     const float4 b4 = ep.bias ? __ldg(reinterpret_cast<const float4 *>(ep.bias + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
     const float2 st = fold ? row_stats[rl] : make_float2(0.f, 1.f);

@@ -410,7 +410,7 @@ void projection(litnice_b200_session *s, AKind ak, long long rows, int k, const 
     } else {
       ep.c = c;
     }
-    const TcPlan plan = tc_plan((int)rows, n, k, tw->has64, tw->has128, tw->has256, TC_BK, ep.vt_hi == nullptr);
+    const TcPlan plan = tc_plan((int)rows, n, k, tw->has64, tw->has128, tw->has256);
     launch_gemm_tc(s->a_map[ak], plan.bn == 256 ? tw->m256 : plan.bn == 128 ? tw->m128 : tw->m64, (int)rows, n, k, plan, ep, s->tc_scratch,
                    s->tc_counters, s->err_dev, s->st);
     return;
@@ -430,7 +430,7 @@ void projection_f16(litnice_b200_session *s, PairKind pk, long long rows, int k,
   if (s->profiling) s->gemm_flops += 2.0 * (double)rows * n * k;
   ++s->launches;
   const TcPairF16 &a = pk == PAIR_LN ? s->pair_ln : pk == PAIR_CTX ? s->pair_ctx : s->pair_h;
-  const TcPlan plan = tc_plan((int)rows, n, k, tw->has64, tw->has128, tw->has256, TC_F16_SLOT, ep.vt_hi == nullptr);
+  const TcPlan plan = tc_plan((int)rows, n, k, tw->has64, tw->has128, tw->has256, TC_F16_SLOT);
   TcEpilogue e = ep;
   if (s->profiling && s->gemm_timeline && s->gemm_timeline_used < litnice_b200_session::kTimelineSlots)
     e.timeline = s->gemm_timeline + 32 * s->gemm_timeline_used++;
