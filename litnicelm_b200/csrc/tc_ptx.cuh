@@ -167,30 +167,10 @@ __device__ __forceinline__ unsigned cluster_map(unsigned local_smem_addr, unsign
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta_rank));
   return remote;
 }
-// No memory clobber: the caller orders these loads with the cluster barriers around the phase
-// that issues them, and several must be in flight at once (a remote load is a round trip of
-// several hundred clocks).
-__device__ __forceinline__ float4 ld_cluster_mapped_f4(unsigned cluster_addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(cluster_addr));
-  return v;
-}
 __device__ __forceinline__ void st_cluster_f4(unsigned cluster_addr, float4 v) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(v.x), "f"(v.y), "f"(v.z),
                "f"(v.w)
                : "memory");
-}
-__device__ __forceinline__ float4 ld_cluster_f4(unsigned local_smem_addr, unsigned cta_rank) {
-  unsigned remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta_rank));
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(remote)
-               : "memory");
-  return v;
 }
 
 // A operand read from tensor memory (lane = row, one column per k element).
