@@ -146,15 +146,14 @@ __device__ __forceinline__ void mbar_arrive(unsigned bar) {
 }
 
 // Thread-block cluster: barrier over all threads of all CTAs of the cluster (hardware barrier; the
-// CTAs of a cluster are co-scheduled), and 16-byte loads from the shared memory of the CTA of a
-// given rank at the same offset as a local address.
+// CTAs of a cluster are co-scheduled), and 16-byte stores into the shared memory of the CTA of a
+// given rank.
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Split form for a barrier that orders no memory ("my peers have finished reading my shared
-// memory"): the releasing arrive of cluster_sync_all would first wait for every global store
-// the CTA has in flight, a microsecond after a store phase.
+// Split form for a barrier that orders no memory of this CTA ("every CTA of the cluster is past
+// its k loop"): a relaxed arrive does not wait for the stores the CTA has in flight.
 __device__ __forceinline__ void cluster_arrive_relaxed() {
   asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 }
