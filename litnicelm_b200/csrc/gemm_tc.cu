@@ -1,20 +1,30 @@
 // Tensor-core projection GEMM for sm_100a (tcgen05 + TMEM + TMA), fp32 accuracy
-// by the three-product TF32 split. Replaces, on the hot path, the sequence
-// gemm_ranked_matrix_rhs + add_bias_rowwise (+ReLU) + add of the reference
-// (litnicelm src/model/backend/device_backend.cpp:1112-1131, 840-940, 752-813).
+// by three products of operand pairs (fp16 pairs with block scales, or TF32
+// pairs). Replaces, on the hot path, the sequence gemm_ranked_matrix_rhs +
+// add_bias_rowwise (+ReLU) + add of the reference (litnicelm
+// src/model/backend/device_backend.cpp:1112-1131, 840-940, 752-813).
 //
-// One CTA computes a 128 x BN tile of C. Warp roles:
-//   warp 0      one lane issues the TMA loads of the four operand tiles
-//               (A_hi, A_lo, B_hi, B_lo; 128-byte swizzle) into a ring of stages
-//   warp 1      allocates tensor memory; one lane issues the tcgen05.mma
-//               instructions (3 products x 4 k-steps per stage) and commits
-//   warps 2..5  epilogue: tcgen05.ld of each finished accumulation chunk (one
-//               TMEM lane quarter each) added into fp32 registers, then bias /
-//               residual / ReLU and the stores (optionally as a hi/lo split for
-//               the next GEMM)
+// One CTA computes a 128 x BN tile of C (or its partial sums over one k range).
+// Warp roles:
+//   warp 0        one lane issues the TMA loads of the four operand tiles
+//                 (A_hi, A_lo, B_hi, B_lo; 128-byte swizzle) into a ring of stages
+//   warp 1        allocates tensor memory; one lane issues the tcgen05.mma
+//                 instructions (3 products x 4 k-steps per stage) and commits
+//   drain warps   tcgen05.ld of each finished accumulation chain (one TMEM lane
+//                 quarter each) added into fp32 registers
+//   helper warps  nothing until the store phase
+// Store phase, by all warps: the tile is staged in shared memory (over the idle
+// pipeline stages) and leaves row by row with every epilogue term applied (folded
+// LayerNorm, bias, residual, ReLU; fp32 and / or the next product's operand pair;
+// row statistics; the V third of a QKV projection transposed).
+// Split-k: the CTAs of a tile form a thread-block cluster, each sends its partial
+// sums of a row to the CTA that stores the row (remote shared-memory stores between
+// two cluster barriers); through global scratch and a last-CTA reduction where a
+// cluster cannot be used. No TMA multicast.
 // Every wait on an mbarrier is bounded (about one second); a wait that runs out
 // sets the error word, lets the pipeline drain and the kernel returns after
-// freeing its tensor memory. No cluster launch and no multicast is used.
+// freeing its tensor memory (the cluster barriers are executed unconditionally by
+// every thread, so a CTA that gave up cannot leave its peers waiting).
 #include "gemm_tc.cuh"
 #include "tc_ptx.cuh"
 #include "gemm_tc_epilogue.cuh"
