@@ -117,6 +117,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   float acc[CW];        // the drain warps' accumulated columns (kept past the role code for the cluster's exchange)
   bool pushes = false;  // this thread sends partial sums to the rows' owners
   float *stage = reinterpret_cast<float *>(base_ptr);       // the tile, once the pipeline stages are idle
+  constexpr bool LOCAL_COPY = BN <= 128;                    // split-k over a cluster: room for a copy of the own tile
+  float *stage_local = stage + (TC_BM + 16) * (BN + 4);     // behind the area the cluster's ranks write into
   float2 *row_stats = reinterpret_cast<float2 *>(base_ptr + L::ROWSTATS_OFFSET);
   // With split-k (gridDim.z CTAs per tile) this CTA owns k-blocks [kb0, kb0 + kblocks).
   const int kb_total = k / KBE;
@@ -325,11 +327,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     if (stamp && warp == 2 && lane == 0) ep.timeline[5] = global_timer();
     // (a cluster's ranks cover up to 140 rows between them: rows_each is rounded up to even)
     static_assert((TC_BM + 16) * (BN + 4) * 4 <= L::TILES_BYTES, "staging tile must fit in the pipeline stages");
-    // (with a cluster per tile the partial sums stay in registers until the peers' operand tiles are dead)
+    static_assert(!LOCAL_COPY || (2 * TC_BM + 16) * (BN + 4) * 4 <= L::TILES_BYTES, "exchange area + local copy");
+    // With a cluster per tile the partial sums wait for the peers' operand tiles to be dead: as a copy of
+    // the tile in this CTA's own shared memory behind the exchange area, or (256-column tiles, which have
+    // no room for that) in the registers.
+    const bool clustered = cluster_splits > 1;
     pushes = tc_stage_tile<BN, CW, DRAIN_THREADS>(acc, ok && !*abort_flag, ep, col0, rl, warp == 2 && lane == 0,
-                                                  cluster_splits > 1 ? 1 : splits, part, counters, last_flag,
-                                                  store_flag, stage, ln_st, row_stats, cluster_splits > 1) &&
-             cluster_splits > 1;
+                                                  clustered ? 1 : splits, part, counters, last_flag, store_flag,
+                                                  clustered && LOCAL_COPY ? stage_local : stage, ln_st, row_stats,
+                                                  clustered && !LOCAL_COPY) &&
+             clustered && !LOCAL_COPY;
   }
   // Store phase, by every warp of the CTA (role and helper warps included: this phase is bound
   // by instruction latency, not bandwidth, and speeds up with the number of warps).
@@ -351,7 +358,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   if (cluster_splits > 1) {
     cluster_arrive_relaxed();
     cluster_wait();
-    if (pushes) tc_push_tile<BN, CW>(acc, stage, col0, rl, rows_each);
+    if (LOCAL_COPY) {
+      if (*store_flag != 0) tc_push_rows<BN, tc_threads(BN)>(stage_local, stage, (int)threadIdx.x, rows_each);
+    } else if (pushes) {
+      tc_push_tile<BN, CW>(acc, stage, col0, rl, rows_each);
+    }
     cluster_sync_all();
   }
   const bool go = *store_flag != 0;
