@@ -58,7 +58,9 @@ def reference_flops(d: formats.ModelDims, s: int) -> float:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per projection launch from the ncu
-# capture summarised under profiles/ (mean over the four projections of a layer).
+# capture summarised under profiles/ (mean over the four projections of a layer at
+# context 640). A figure of that capture, not of the run that prints it; other
+# workloads have none and report null.
 NCU_DRAM_BYTES_PER_GEMM_LAUNCH = {"c2": 6.4e6}
 
 
@@ -187,9 +189,13 @@ def run_reference_arm(args, rank, world):
     d, arena, prompts, seeds, (streams, plen, max_new, temp, top_k, top_p) = make_inputs(args.workload, 0)
     full = np.concatenate([prompts[0], formats.zipf_prompt(d.vocab, d.max_seq, 999)])[:d.max_seq]
     sample_lens = [16, 48] if d.d_model >= 512 else [min(d.max_seq, 24), min(d.max_seq, 56)]
-    # With N GPUs the workload is N independent replicas; the CPU arm runs as
-    # many of them side by side as it has cores for.
-    conc = max(1, min(world, os.cpu_count() or 1))
+    # The job is `job_streams` independent streams (N replicas of the per-GPU count, or the 512
+    # streams of config 5 whatever N is). The reference decodes one stream per process on one
+    # thread, so the CPU arm runs as many streams side by side as it has cores for (bounded by
+    # host memory at the large model) and its throughput is that many times one stream's.
+    _, per_gpu, scaling = rank_streams(args.workload, world, 0)
+    job_streams = streams if scaling == "strong" else streams * world
+    conc = max(1, min(job_streams, os.cpu_count() or 1, 8 if d.d_model <= 512 else 2))
     for _ in range(args.warmup):
         time_reference_sample(d, arena, full, sample_lens[:1], conc)
     t0 = time.time()
@@ -197,18 +203,19 @@ def run_reference_arm(args, rank, world):
     for _ in range(args.steps):
         samples = time_reference_sample(d, arena, full, sample_lens, conc)
         r, _ = extrapolate_reference_tokens_per_s(d, samples, plen, max_new)
-        rates.append(r * streams * conc)
+        rates.append(r * conc)
     wall = time.time() - t0
     value = statistics.mean(rates)
     sample = (f"per step: single reference forwards at context {sample_lens} of the workload's model, "
               f"cost per executed flop applied to the schedule s={plen}..{plen + max_new - 1} "
-              "(extrapolated from subsample)")
+              f"(extrapolated from subsample); {conc} stream(s) side by side, one core each")
     line = {
         "impl": "reference", "metric": "generated tokens/s (greedy decode)", "value": value,
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * wall / max(1, args.steps), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": 1e3 * wall / max(1, args.steps), "higher_is_better": True, "scaling": scaling,
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args.workload, streams, plen, max_new), "l2": "not applicable (CPU)"},
+        "config": {"workload": workload_name(args.workload, per_gpu, plen, max_new), "l2": "not applicable (CPU)",
+                   "sampling": {"temp": temp, "top_k": top_k, "top_p": top_p}},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": conc, "kind": "reference", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -223,107 +230,245 @@ def workload_name(workload, streams, plen, max_new):
             "whole-context recomputation per token")
 
 
-def run_b200_arm(args, rank, local_rank, world):
-    import torch
-    from litnicelm_b200.plugin import Session
+DTYPE = "f32 storage; projections and attention as three 16-bit tensor-core products per fp32 product (fp16 / tf32 pairs, 22-bit operands), fp32 accumulate"
 
-    os.environ["LITNICE_B200_DEVICE"] = str(local_rank)
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    d, arena, prompts, seeds, (streams, plen, max_new, temp, top_k, top_p) = make_inputs(args.workload, rank)
-    peaks = load_peaks()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
 
-    def barrier():
-        torch.cuda.synchronize()
+def rank_streams(workload: str, world: int, rank: int):
+    """(first stream, count, scaling) of this rank. Config 5 is one job of 512
+    streams cut into contiguous blocks over the GPUs (strong scaling); the other
+    workloads give every GPU its own copy of the per-GPU stream count (weak)."""
+    from litnicelm_b200.streams import partition_streams
+    streams = WORKLOADS[workload][1]
+    if workload == "c5":
+        first, count = partition_streams(streams, world, rank)
+        return first, count, "strong"
+    return rank * streams, streams, "weak"
+
+
+def make_rank_inputs(workload: str, first: int, count: int):
+    key, _, plen, max_new, temp, top_k, top_p, cidx = WORKLOADS[workload]
+    d = formats.CONFIG_DIMS[key]
+    arena = formats.make_param_arena(d, 1000 + cidx)
+    prompts = np.stack([formats.zipf_prompt(d.vocab, plen, 2000 * cidx + first + i) for i in range(count)])
+    seeds = np.array([3000 + first + i for i in range(count)], dtype=np.uint32)
+    return d, arena, prompts, seeds, (plen, max_new, temp, top_k, top_p)
+
+
+def check_against_fixture(workload: str, first: int, tokens: np.ndarray):
+    """Tokens of the timed run against the committed fixture of the same inputs
+    (tests/golden/, made by the oracle). Greedy: identical up to a first
+    mismatch, whose top-2 gap in the oracle is reported. Returns None when this
+    rank holds none of the fixture's streams."""
+    gold = os.path.join(ROOT, "tests", "golden")
+    try:
+        if workload == "c2" and first == 0:
+            z = np.load(os.path.join(gold, "c2_full.npz"))
+            ref, got, gaps = z["greedy_tokens"], tokens[0], z["top2_gap"]
+            name = "tests/golden/c2_full.npz"
+        elif workload == "c5" and first == 0:
+            z = np.load(os.path.join(gold, "c5_dims.npz"))
+            ref, gaps = z["greedy_tokens"], z["top2_gap"]
+            got = tokens[0][:len(ref)]
+            name = "tests/golden/c5_dims.npz (stream 0, first 8 tokens)"
+        elif workload == "c3" and first == 0:
+            z = np.load(os.path.join(gold, "c3_streams.npz"))
+            which = [int(i) for i in z["streams"]]
+            n = z["sampled_tokens"].shape[1]
+            agree = [int(np.argmin(np.append(tokens[i][:n] == z["sampled_tokens"][j], False)))
+                     for j, i in enumerate(which)]
+            return {"fixture": "tests/golden/c3_streams.npz", "streams": which, "tokens_compared": n,
+                    "tokens_equal_per_stream": agree}
+        else:
+            return None
+    except (OSError, KeyError) as e:
+        return {"unavailable": str(e)}
+    n = min(len(ref), len(got))
+    neq = np.nonzero(got[:n] != ref[:n])[0]
+    first_bad = int(neq[0]) if len(neq) else None
+    return {"fixture": name, "tokens_compared": int(n), "tokens_equal": int(n if first_bad is None else first_bad),
+            "first_mismatch_step": first_bad,
+            "first_mismatch_gap": None if first_bad is None else float(gaps[first_bad])}
+
+
+class Box:
+    """torch / torch.distributed plumbing shared by the measurements of one process."""
+
+    def __init__(self, rank, local_rank, world):
+        import torch
+        self.torch = torch
+        self.rank, self.local_rank, self.world = rank, local_rank, world
+        os.environ["LITNICE_B200_DEVICE"] = str(local_rank)
+        torch.cuda.set_device(local_rank)
+        self.dist = None
         if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            self.dist = dist
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
 
-    def max_over_ranks(x: float) -> float:
-        if world == 1:
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.dist:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def reduce(self, x: float, op: str = "max") -> float:
+        if not self.dist:
             return x
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX if op == "max" else self.dist.ReduceOp.SUM)
         return float(t.item())
 
-    sess = Session(d, streams)
+    def close(self):
+        if self.dist:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def measure_generation(box: Box, workload: str, steps: int, warmup: int, sample_clocks: bool):
+    """W warm-up and K timed generations of this rank's streams, device-timed with
+    the prompts resident, then K more through litnice_b200_generate with pinned
+    host buffers. Returns the figures of the job over all ranks and the session."""
+    import ctypes as C
+    from litnicelm_b200.plugin import B200Sampling, Session
+    torch = box.torch
+    first, count, scaling = rank_streams(workload, box.world, box.rank)
+    d, arena, prompts, seeds, (plen, max_new, temp, top_k, top_p) = make_rank_inputs(workload, first, count)
+    sess = Session(d, count)
     sess.load_params(arena)
     pinned_prompts = torch.from_numpy(prompts.copy()).pin_memory()
-    pinned_out = torch.zeros((streams, max_new), dtype=torch.int32).pin_memory()
+    pinned_out = torch.zeros((count, max_new), dtype=torch.int32).pin_memory()
 
     # ---- device-resident pass: prompts already in HBM when the clock starts ----
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         sess.upload_prompts(prompts, seeds)
         sess.run(max_new, temp, top_k, top_p)
-    clocks = ClockSampler(local_rank)
-    barrier()
-    if rank == 0:
+    clocks = ClockSampler(box.local_rank) if sample_clocks and box.rank == 0 else None
+    box.barrier()
+    if clocks:
         clocks.start()
     dev_ms, launches, tokens = 0.0, 0, 0
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        flush.fill_(1)
+    for _ in range(steps):
+        box.flush.fill_(1)
         torch.cuda.synchronize()
         sess.upload_prompts(prompts, seeds)          # untimed: not inside the event bracket
-        produced = sess.run(max_new, temp, top_k, top_p)
+        sess.run(max_new, temp, top_k, top_p)
         st = sess.stats()
         dev_ms += st.device_ms
         launches += st.kernel_launches
         tokens += st.tokens
-    barrier()
+    box.barrier()
     wall_s = time.perf_counter() - t0
-    clock_info = clocks.stop() if rank == 0 else None
-    dev_ms = max_over_ranks(dev_ms)
-    value = world * tokens / (dev_ms * 1e-3)
+    clock_info = clocks.stop() if clocks else None
+    dev_ms = box.reduce(dev_ms, "max")
+    total_tokens = box.reduce(float(tokens), "sum")
+    value = total_tokens / (dev_ms * 1e-3)
 
     # ---- end-to-end pass: host buffers in, host buffers out, copies inside the clock ----
-    import ctypes as C
-    from litnicelm_b200.plugin import B200Sampling
     sp = B200Sampling(temp, top_k, top_p)
-    count = C.c_int32(0)
+    produced = C.c_int32(0)
     i32p = C.POINTER(C.c_int32)
     seeds_p = seeds.ctypes.data_as(C.POINTER(C.c_uint32))
 
     def e2e_once():
-        rc = sess.lib.litnice_b200_generate(sess.h, C.cast(pinned_prompts.data_ptr(), i32p), streams, plen,
+        rc = sess.lib.litnice_b200_generate(sess.h, C.cast(pinned_prompts.data_ptr(), i32p), count, plen,
                                             max_new, C.byref(sp), seeds_p,
-                                            C.cast(pinned_out.data_ptr(), i32p), C.byref(count))
+                                            C.cast(pinned_out.data_ptr(), i32p), C.byref(produced))
         if rc != 0:
             raise RuntimeError(sess.lib.litnice_b200_last_error(sess.h).decode())
 
-    e2e_once()
-    barrier()
+    if warmup > 1:
+        e2e_once()
+    box.barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        flush.fill_(1)
+    for _ in range(steps):
+        box.flush.fill_(1)
         torch.cuda.synchronize()
         e2e_once()
-    barrier()
-    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    box.barrier()
+    e2e_s = box.reduce(time.perf_counter() - t0, "max")
     st = sess.stats()
-    e2e_value = world * args.steps * streams * count.value / e2e_s
-    first_tokens = pinned_out[0, :8].tolist()
+    e2e_tokens = box.reduce(float(steps * count * produced.value), "sum")
+    out = pinned_out.numpy()[:, :produced.value].copy()
+    parity = check_against_fixture(workload, first, out)
+    return {
+        "dims": d, "arena": arena, "prompts": prompts, "sess": sess, "scaling": scaling,
+        "streams_this_rank": count, "plen": plen, "max_new": max_new,
+        "sampling": {"temp": temp, "top_k": top_k, "top_p": top_p},
+        "value": value, "dev_ms_per_step": dev_ms / steps, "launches": int(launches),
+        "e2e": {"value": e2e_tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(st.h2d_bytes),
+                "d2h_bytes_per_step": int(st.d2h_bytes)},
+        "clocks": clock_info, "wall_s": wall_s, "first_tokens": out[0, :8].tolist(), "parity": parity,
+    }
 
+
+def whole_loop_flops(d, streams_total: int, plen: int, max_new: int) -> float:
+    return sum(algorithmic_flops(d, streams_total, s) for s in range(plen, plen + max_new))
+
+
+def hbm_block(peaks):
+    """The few-row product of the output head at the config-4/5 shape (1024 x 32000 fp32
+    weights, 131 MB): the kernel of the path that HBM bandwidth bounds. 50 launches back to
+    back between one pair of CUDA events, each on the next of a ring of weight copies that
+    exceeds three times the L2, so every launch reads its matrix from HBM."""
+    from litnicelm_b200.plugin import gemv_time
+    k, n = 1024, 32000
+    out = {"kernel": "gemv_tma_kernel: out[m, 32000] = x[m, 1024] . W (output head of configs 4/5)",
+           "algorithmic_bytes_per_launch": 4 * k * n + 4 * (k + n), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+           "peak_source": f"copy bandwidth, {peaks['source']}", "launches_timed": 50,
+           "l2": "ring of weight copies larger than three times the L2: every launch reads HBM"}
+    for m in (1, 8):
+        try:
+            us, nl = gemv_time(m, k, n, 50, 2)
+            gbs = (4.0 * k * n + 4.0 * m * (k + n)) / (us * 1e-6) / 1e9
+            out[f"m{m}"] = {"us_per_launch": us, "achieved": gbs, "frac": gbs / peaks["hbm_gbs"], "kernels_per_call": nl}
+        except Exception as e:
+            out[f"m{m}"] = {"unavailable": str(e)}
+    return out
+
+
+def run_b200_arm(args, rank, local_rank, world):
+    box = Box(rank, local_rank, world)
+    peaks = load_peaks()
+    main = measure_generation(box, args.workload, args.steps, args.warmup, sample_clocks=True)
+    sess, d = main["sess"], main["dims"]
+    plen, max_new = main["plen"], main["max_new"]
+    streams_total = WORKLOADS[args.workload][1] * (1 if main["scaling"] == "strong" else world)
     line = None
     if rank == 0:
-        # ---- roofline of the dominant kernel (the projection GEMM), events per launch ----
+        # ---- roofline of the dominant kernel (the projection GEMM) ----
         s_mid = plen + max_new // 2
-        prof = sess.profile_step(streams, s_mid, 3)
-        gemm_tflops = prof.gemm_flops / (prof.gemm_ms * 1e-3) / 1e12 if prof.gemm_ms > 0 else 0.0
+        prof = sess.profile_step(main["streams_this_rank"], s_mid, 3)
+        isolated = prof.gemm_flops / (prof.gemm_ms * 1e-3) / 1e12 if prof.gemm_ms > 0 else 0.0
+        in_loop = prof.gemm_span_flops / (prof.gemm_span_ms * 1e-3) / 1e12 if prof.gemm_span_ms > 0 else None
+        whole = whole_loop_flops(d, streams_total, plen, max_new) / (main["dev_ms_per_step"] * 1e-3) / 1e12
+        achieved = in_loop if in_loop is not None else isolated
         roofline = {
-            "bound": "tensor", "kernel": "projection GEMM (gemm_tc_kernel: tcgen05 + TMEM, three products of fp16 pairs)",
-            "achieved": gemm_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-            "frac": gemm_tflops / peaks["bf16_tflops"], "peak_source": f"bf16 burst, {peaks['source']}",
-            # fp32-grade products execute three fp16 MMAs (22-bit operand pairs) per algorithmic
-            # flop, so algorithmic flops cannot exceed 1/3 of the dense 16-bit peak
+            "bound": "tensor",
+            "kernel": "projection GEMM (gemm_tc_kernel: tcgen05 + TMEM, three products of fp16 pairs)",
+            "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+            "frac": achieved / peaks["bf16_tflops"], "peak_source": f"bf16 burst, {peaks['source']}",
+            # fp32-grade products execute three 16-bit MMAs per algorithmic flop, so algorithmic
+            # flops cannot exceed 1/3 of the dense 16-bit peak
             "ceiling_frac_3_products": 1.0 / 3.0,
+            "executed_mma_frac": 3.0 * achieved / peaks["bf16_tflops"],
+            "how": (f"in the loop: algorithmic 2*M*N*K flops of the {prof.gemm_span_launches} projection launches of "
+                    f"one step at context {s_mid} / the sum of their device-clock spans (earliest CTA start to "
+                    f"latest CTA end, {prof.gemm_span_ms:.3f} ms; launches overlap as in the token loop; "
+                    f"attention {prof.attn_span_launches} launches {prof.attn_span_ms:.3f} ms; whole step "
+                    f"{prof.step_span_ms:.3f} ms)") if in_loop is not None else
+                   "CUDA events around each launch (the device-clock spans need the tensor-core path)",
+            "isolated": {"achieved": isolated, "frac": isolated / peaks["bf16_tflops"],
+                         "how": f"{prof.gemm_launches} launches, CUDA events around each, {prof.gemm_ms:.3f} ms"},
+            "whole_loop": {"achieved": whole, "frac": whole / peaks["bf16_tflops"],
+                           "frac_of_sustained": whole / peaks["bf16_tflops_sustained"],
+                           "how": "all algorithmic flops of a generation (projections on every row, causal-useful "
+                                  "attention, head on the last rows) / ms_per_step"},
             "traffic": NCU_DRAM_BYTES_PER_GEMM_LAUNCH.get(args.workload),
-            "note": (f"algorithmic 2*M*N*K flops of {prof.gemm_launches} launches at context {s_mid} / "
-                     f"{prof.gemm_ms:.3f} ms (CUDA events around each launch on the session stream); "
-                     f"attention: {prof.attn_launches} launches, {prof.attn_ms:.3f} ms"),
+            "traffic_source": ("profiles/gemm_tc_c2_context640_and_c5shape.md (ncu dram__bytes_read + write, mean "
+                               "per projection launch at context 640)")
+            if args.workload in NCU_DRAM_BYTES_PER_GEMM_LAUNCH else None,
         }
         # The same kernel where the path's definition puts it on the tensor roofline (many rows): the
         # QKV projection of the config-4/5 model on 16 384 rows, warm, back to back.
@@ -337,40 +482,61 @@ def run_b200_arm(args, rank, local_rank, world):
                                     "frac_of_3_product_ceiling": 3.0 * big / peaks["bf16_tflops"]}
         except Exception as e:
             roofline["at_scale"] = {"unavailable": str(e)}
-        # ---- CPU baseline: the reference itself on a bounded sample ----
-        cpu = None
-        if not args.no_cpu_baseline:
-            try:
-                full = np.concatenate([prompts[0], formats.zipf_prompt(d.vocab, d.max_seq, 999)])[:d.max_seq]
-                lens = [32, 96] if d.d_model >= 512 else [min(d.max_seq, 24), min(d.max_seq, 56)]
-                samples = time_reference_sample(d, arena, full, lens)
-                rate, per_flop = extrapolate_reference_tokens_per_s(d, samples, plen, max_new)
-                cpu = {"value": rate * streams, "unit": "tokens/s", "cores": 1, "kind": "reference",
-                       "host_cores_present": os.cpu_count(),
-                       "sample": (f"reference CPU backend, single forwards at context {lens} "
-                                  f"({', '.join(f'{t:.2f}s' for _, t in samples)}); {per_flop * 1e9:.3f} ns per "
-                                  "executed flop applied to the full schedule (extrapolated from subsample)")}
-            except Exception as e:  # the bench line must still be printed
-                cpu = {"value": None, "unit": "tokens/s", "cores": 1, "kind": "reference",
-                       "sample": f"unavailable: {e}"}
-        line = {
-            "metric": "generated tokens/s (greedy decode)", "value": value, "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload_name(args.workload, streams, plen, max_new),
-                       "l2": "256 MB buffer written between timed steps (L2 flush)",
-                       "sampling": {"temp": temp, "top_k": top_k, "top_p": top_p}},
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": int(st.h2d_bytes),
-                    "d2h_bytes_per_step": int(st.d2h_bytes)},
-            "gpu_launches": int(launches),
-            "roofline": roofline, "cpu_baseline": cpu, "clocks": clock_info,
-            "wall_s_timed_region": wall_s, "first_tokens": first_tokens,
-        }
     sess.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    hbm = None
+    if rank == 0 and not args.no_extras:
+        hbm = hbm_block(peaks)
+    # ---- CPU baseline: the reference itself on a bounded sample ----
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline:
+        try:
+            prompts = main["prompts"]
+            full = np.concatenate([prompts[0], formats.zipf_prompt(d.vocab, d.max_seq, 999)])[:d.max_seq]
+            lens = [32, 96, 256] if d.d_model == 512 else ([32, 96] if d.d_model > 512 else
+                                                           [min(d.max_seq, 24), min(d.max_seq, 56)])
+            samples = time_reference_sample(d, main["arena"], full, lens)
+            rate, per_flop = extrapolate_reference_tokens_per_s(d, samples, plen, max_new)
+            cpu = {"value": rate, "unit": "tokens/s", "cores": 1, "kind": "reference",
+                   "host_cores_present": os.cpu_count(),
+                   "sample": (f"reference CPU backend, single forwards at context {lens} "
+                              f"({', '.join(f'{t:.2f}s' for _, t in samples)}); {per_flop * 1e9:.3f} ns per "
+                              "executed flop applied to the full schedule (extrapolated from subsample)")}
+        except Exception as e:  # the bench line must still be printed
+            cpu = {"value": None, "unit": "tokens/s", "cores": 1, "kind": "reference",
+                   "sample": f"unavailable: {e}"}
+    # ---- the other halves of the metric: 64 lockstep streams (config 3) and the 512-stream job of
+    # config 5 cut over the GPUs; one warm-up and one timed generation each ----
+    extra = {}
+    if args.workload == "c2" and not args.no_extras:
+        for name in ("c3", "c5"):
+            r = measure_generation(box, name, 1, 1, sample_clocks=True)
+            r["sess"].close()
+            total = WORKLOADS[name][1] * (1 if r["scaling"] == "strong" else world)
+            wl = whole_loop_flops(r["dims"], total, r["plen"], r["max_new"]) / (r["dev_ms_per_step"] * 1e-3) / 1e12
+            extra["c5_split" if name == "c5" else name] = {
+                "workload": workload_name(name, r["streams_this_rank"], r["plen"], r["max_new"]),
+                "value": r["value"], "unit": "tokens/s", "scaling": r["scaling"],
+                "streams_total": total, "streams_per_gpu": r["streams_this_rank"],
+                "ms_per_step": r["dev_ms_per_step"], "steps": 1, "warmup": 1, "e2e": r["e2e"],
+                "gpu_launches": r["launches"], "sampling": r["sampling"],
+                "whole_loop_tflops": wl, "whole_loop_frac": wl / peaks["bf16_tflops"], "clocks": r["clocks"],
+                "parity": r["parity"],
+            }
+    if rank == 0:
+        line = {
+            "metric": "generated tokens/s (greedy decode)", "value": main["value"], "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": main["dev_ms_per_step"], "higher_is_better": True, "scaling": main["scaling"],
+            "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+            "config": {"workload": workload_name(args.workload, main["streams_this_rank"], plen, max_new),
+                       "l2": "256 MB buffer written between timed steps (L2 flush)",
+                       "sampling": main["sampling"]},
+            "e2e": main["e2e"], "gpu_launches": main["launches"],
+            "roofline": roofline, "hbm": hbm, "cpu_baseline": cpu, "clocks": main["clocks"],
+            "parity": main["parity"], "extra": extra,
+            "wall_s_timed_region": main["wall_s"], "first_tokens": main["first_tokens"],
+        }
+    box.close()
     if line is not None:
         print(json.dumps(line), flush=True)
 
@@ -468,6 +634,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the output-head bandwidth block and the config-3 / config-5 side measurements")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -171,6 +171,16 @@ typedef struct litnice_b200_stats {
   double gemm_flops;         /* algorithmic flops of those launches */
   double attn_ms;
   int64_t attn_launches;
+  /* litnice_b200_profile_step, one step without events: per launch the span from the
+   * earliest CTA start to the latest CTA end on the device clock (launches overlap as in
+   * the token loop), summed per kernel class, and the span of the whole step. Filled for
+   * the tensor-core kernels only. */
+  double gemm_span_ms;
+  int64_t gemm_span_launches;
+  double gemm_span_flops;
+  double attn_span_ms;
+  int64_t attn_span_launches;
+  double step_span_ms;
 } litnice_b200_stats;
 
 /* Builds a session on the current CUDA device (or LITNICE_B200_DEVICE) for up
@@ -179,6 +189,13 @@ typedef struct litnice_b200_stats {
  * (inference_memory_manager.cpp:7-33). */
 int litnice_b200_session_create(const litnice_b200_dims *dims, int32_t max_streams,
                                 litnice_b200_session **out);
+/* The same on an explicit CUDA device ordinal (LITNICE_B200_DEVICE is not consulted): what a
+ * host that runs one thread per GPU calls, each thread with its own share of the streams
+ * (the reference runs one stream per process, inference.cpp:362-405; streams never
+ * exchange data, so the shares need no collective). Every call on a session selects the
+ * session's device first, so a session may be driven from any one thread at a time. */
+int litnice_b200_session_create_on(const litnice_b200_dims *dims, int32_t max_streams, int32_t device,
+                                   litnice_b200_session **out);
 void litnice_b200_session_destroy(litnice_b200_session *s);
 const char *litnice_b200_last_error(const litnice_b200_session *s);
 
@@ -237,6 +254,38 @@ int litnice_b200_sample_logits(litnice_b200_session *s, const float *logits, int
 
 int litnice_b200_get_stats(const litnice_b200_session *s, litnice_b200_stats *out);
 
+/* No counterpart in the reference. Few-row product out[m, n] = x[m, k] * W[k, n]
+ * (+ bias[n]) for callers that cannot allocate device memory while they run:
+ * a host that has already given all device memory to its own arenas, or a
+ * loop that cannot afford the device-wide stall of an allocation. It calls no
+ * cudaMalloc / cudaFree or any other allocating routine; the split-k partial
+ * sums live in a 1.5 MiB array built into the library image (held by every GPU
+ * that loads the library until the process exits).
+ *   x [m, k], W [k, n] row-major, bias [n] or NULL, out [m, n]: device pointers
+ *   owned by the caller; m must be 1, 2, 4 or 8; stream is a cudaStream_t
+ *   (NULL = default stream). The call only enqueues work on that stream.
+ * Returns 0, LITNICE_B200_EINVAL, LITNICE_B200_ECUDA, or LITNICE_B200_ETOOBIG
+ * when m, k, n would need more than the 393216 floats of built-in scratch
+ * (a line on stderr says how much was needed). The kernel cuts k into
+ * min(ceil(296 / ceil(n / 128)), ceil(k / 64)) ranges when n < 18944 and keeps
+ * ranges * m * n partial sums, so in practice only m = 8 is ever refused: with
+ * 16385..18816 columns and k > 128 (3 ranges), or 12289..12544 columns and k > 192
+ * (4 ranges). Shapes with n >= 18944 or k <= 64 need no scratch at all.
+ * The first call on each device looks up the device address of the built-in
+ * array (and loads the kernels): make that first call before any stream
+ * capture begins. All calls share the one array: it keeps the previous call's
+ * partial sums, which is harmless because each call overwrites every entry it
+ * later reads, but two calls whose kernels overlap on the GPU (different
+ * streams, or different host threads) race on it. */
+int litnice_b200_gemv_noalloc(const float *x, int32_t m, const float *w, int32_t k, int32_t n,
+                              const float *bias, float *out, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* 3. Diagnostics and measurement aids.                                       */
+/*    None of these is part of the token loop and a host binds none of them;  */
+/*    the tests, bench.py and the profiling commands call them.               */
+/* ------------------------------------------------------------------------ */
+
 /* Runs one step at context length seq_len for n_streams streams with CUDA
  * events around each projection and attention launch, `repeats` times, and
  * fills the gemm_* / attn_* fields of the stats. Measurement aid. */
@@ -261,29 +310,29 @@ int litnice_b200_projection_host(int32_t engine, const float *a, int32_t m, int3
 int litnice_b200_projection_time(int32_t engine, const float *a, int32_t m, int32_t k, const float *w, int32_t n,
                                  float *c, int32_t repeats, double *avg_us);
 
-/* No counterpart in the reference. Few-row product out[m, n] = x[m, k] * W[k, n]
- * (+ bias[n]) for callers that cannot allocate device memory while they run:
- * a host that has already given all device memory to its own arenas, or a
- * loop that cannot afford the device-wide stall of an allocation. It calls no
- * cudaMalloc / cudaFree or any other allocating routine; the split-k partial
- * sums live in a 1.5 MiB array built into the library image (held by every GPU
- * that loads the library until the process exits).
- *   x [m, k], W [k, n] row-major, bias [n] or NULL, out [m, n]: device pointers
- *   owned by the caller; m must be 1, 2, 4 or 8; stream is a cudaStream_t
- *   (NULL = default stream). The call only enqueues work on that stream.
- * Returns 0, LITNICE_B200_EINVAL, LITNICE_B200_ECUDA, or LITNICE_B200_ETOOBIG
- * when m, k, n would need more than the 393216 floats of built-in scratch
- * (a line on stderr says how much was needed). In practice only m = 8 with
- * 16385..18816 columns and k > 128 is refused; shapes with n >= 18944 or
- * k <= 64 need no scratch at all.
- * The first call on each device looks up the device address of the built-in
- * array (and loads the kernels): make that first call before any stream
- * capture begins. All calls share the one array: it keeps the previous call's
- * partial sums, which is harmless because each call overwrites every entry it
- * later reads, but two calls whose kernels overlap on the GPU (different
- * streams, or different host threads) race on it. */
-int litnice_b200_gemv_noalloc(const float *x, int32_t m, const float *w, int32_t k, int32_t n,
-                              const float *bias, float *out, void *stream);
+/* The few-row product out[m, n] = x[m, k] * W[k, n] (+ bias[n]) (+ residual[m, n])
+ * (ReLU when relu != 0), m <= 8, on host buffers: the M <= 8 case of
+ * gemm_ranked_matrix_rhs (device_backend.cpp:1112-1131) as the output head uses it
+ * on the last rows (output_head.cpp:58-70), followed by add_bias_rowwise / add /
+ * relu (:840-908, 752-813, 978-1001). Allocates and frees its own device buffers. */
+int litnice_b200_gemv_host(const float *x, int32_t m, const float *w, int32_t k, int32_t n,
+                           const float *bias, const float *residual, int32_t relu, float *out);
+
+/* Device time of that product. cold_l2 = 2: `repeats` calls back to back between one
+ * pair of CUDA events, each on the next of a ring of weight copies larger than three
+ * times the L2 (every call reads its matrix from HBM); 1: events around each call
+ * with a 256 MB buffer written before it; 0: the same matrix every call. force_tn
+ * (0, 128, 256) and force_splits (0 = planned; negative: that many k ranges joined through
+ * scratch and a second kernel instead of a thread-block cluster) override the tile plan. *avg_us: mean
+ * microseconds per call; *launches: kernels per call. */
+int litnice_b200_gemv_time(int32_t m, int32_t k, int32_t n, int32_t repeats, int32_t cold_l2,
+                           int32_t force_tn, int32_t force_splits, double *avg_us, int32_t *launches);
+
+/* Self-test of the bounded waits: a one-CTA kernel waits on a barrier that nothing
+ * completes, with a limit of limit_us microseconds (1..1000). It must come back on
+ * its own with *code == 2 (a wait ran out), *detail == 99 and *waited_us >= limit_us,
+ * and the device must stay usable. */
+int litnice_b200_selftest_wait_timeout(int32_t limit_us, int32_t *code, int32_t *detail, double *waited_us);
 
 #ifdef __cplusplus
 }

@@ -156,6 +156,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
     // ---- TMA producer: Q once, then K and V^T of each key tile as their buffers free up ----
     pdl_wait();
     if (lane == 0) {
+      if (timeline != nullptr) atomicMin(timeline + 16, global_timer());  // the predecessor has completed
       mbar_expect_tx(q_full, (unsigned)TA_Q_BYTES);
       for (int kb = 0; kb < TA_DH / 32; ++kb) {
         tma_load_2d(base + TA_Q_OFF + kb * TA_SLAB, &map_qk_hi, h * TA_DH + kb * 32, row0 + q0, q_full);

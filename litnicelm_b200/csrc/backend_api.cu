@@ -7,9 +7,10 @@
 // All work of one backend instance is issued on one stream. The only host
 // synchronisation points are the host<->device copies, which the host requires
 // to be complete on return (host_tensor_stage.hpp:120-124, checkpoint.cpp:214-218).
-// Training entries are not implemented and throw; nothing falls back to the CPU.
+// Nothing falls back to the CPU.
 #include "common.cuh"
 
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <fstream>
@@ -31,6 +32,8 @@ struct Backend {
   std::map<uintptr_t, uint64_t> allocs;             // user pointer -> bytes, for every live allocation
   int ctx_iteration = 0, ctx_group = 0;
   long long launches = 0;
+  void *scratch = nullptr;  // partial sums and row statistics of the training entries
+  size_t scratch_bytes = 0;
 
   // Read-ahead for row-by-row read-back. The host reads logits one row per
   // copy_device2host call (host_tensor_stage.hpp:101-125: s calls of V floats per
@@ -79,6 +82,9 @@ void raise_device_error(Backend *b) {
   if (code == DEVERR_BAD_TOKEN_ID)
     throw std::runtime_error("litnice_b200::embedding_lookup: embedding id out of range (id=" +
                              std::to_string(detail) + ")");
+  if (code == DEVERR_BAD_TARGET)
+    throw std::runtime_error("litnice_b200::cross_entropy: target out of range (target=" + std::to_string(detail) +
+                             ")");
   throw std::runtime_error("litnice_b200: device error code " + std::to_string(code));
 }
 
@@ -101,11 +107,6 @@ RowView flat_view(LitniceView t) {
   v.cols = view_numel(t);
   v.cs = 4;
   return v;
-}
-
-[[noreturn]] void training_entry(const char *name) {
-  throw std::runtime_error(std::string("litnice_b200: ") + name +
-                           " belongs to training and is not implemented by this inference plugin");
 }
 
 // ---- lifecycle ---------------------------------------------------------------
@@ -152,6 +153,7 @@ void api_destroy(void *h) {
   }
   if (b->err_host) cudaFreeHost(b->err_host);
   if (b->shadow) cudaFreeHost(b->shadow);
+  if (b->scratch) cudaFree(b->scratch);
   delete b;
 }
 
@@ -615,25 +617,263 @@ void api_causal_softmax_ctx(void *h, LitniceView scores, float scale, LitniceVie
   api_causal_softmax(h, scores, scale, out);
 }
 
-// ---- training entries: not implemented ---------------------------------------------
+// ---- training entries ------------------------------------------------------------------
+// What `litnicelm train` calls beyond the inference entries. Kernels in training.cu.
 
-float api_sum_squares(void *, LitniceView) { training_entry("sum_squares_f32"); }
-void api_relu_backward(void *, LitniceView, LitniceView, LitniceView) { training_entry("relu_backward"); }
-void api_relu_backward_inplace(void *, LitniceView, LitniceView) { training_entry("relu_backward_inplace"); }
-void api_row_sum(void *, LitniceView, LitniceView) { training_entry("row_sum"); }
-void api_gemm_ranked_matrix_rhs_t(void *, LitniceView, LitniceView, LitniceView) { training_entry("gemm_ranked_matrix_rhs_t"); }
-void api_gemm_ranked_reduce_lhs_t(void *, LitniceView, LitniceView, LitniceView) { training_entry("gemm_ranked_reduce_lhs_t"); }
-void api_gemm_batched_lhs_t(void *, LitniceView, LitniceView, LitniceView) { training_entry("gemm_batched_lhs_t"); }
-void api_gemm_batched_lhs_t_ctx(void *, LitniceView, LitniceView, LitniceView) { training_entry("gemm_batched_lhs_t_exec_context"); }
-void api_layernorm_backward(void *, LitniceView, LitniceView, LitniceView, LitniceView, LitniceView, LitniceView) { training_entry("layernorm_backward"); }
-void api_accumulate_embedding_grads(void *, LitniceView, LitniceView, LitniceView, LitniceView) { training_entry("accumulate_embedding_grads"); }
-void api_cross_entropy_mean(void *, LitniceView, LitniceView, LitniceView) { training_entry("cross_entropy_mean"); }
-void api_cross_entropy_mean_backward_inplace(void *, LitniceView, LitniceView, LitniceView) { training_entry("cross_entropy_mean_backward_inplace"); }
-void api_backward_from_logits_targets(void *, LitniceView, LitniceView) { training_entry("backward_from_logits_targets"); }
-void api_softmax_backward_rows(void *, LitniceView, LitniceView, LitniceView) { training_entry("softmax_backward_rows"); }
-void api_softmax_backward_causal_rows(void *, LitniceView, LitniceView, LitniceView) { training_entry("softmax_backward_causal_rows"); }
-void api_softmax_backward_causal_rows_ctx(void *, LitniceView, LitniceView, LitniceView) { training_entry("softmax_backward_causal_rows_exec_context"); }
-void api_adamw_step(void *, LitniceView, LitniceView, LitniceView, LitniceView, uint64_t, float, float, float, float, uint32_t) { training_entry("adamw_step"); }
+void *scratch_for(Backend *b, long long rows, long long cols) {
+  const size_t need = training_scratch_bytes(rows, cols);
+  if (need > b->scratch_bytes) {
+    LB_CUDA(cudaStreamSynchronize(b->st));
+    if (b->scratch) cudaFree(b->scratch);
+    b->scratch = nullptr;
+    b->scratch_bytes = 0;
+    const size_t grown = need + need / 2;
+    if (cudaMalloc(&b->scratch, grown) != cudaSuccess) {
+      (void)cudaGetLastError();
+      throw std::runtime_error("litnice_b200: device allocation of " + std::to_string(grown) + " bytes of scratch failed");
+    }
+    b->scratch_bytes = grown;
+  }
+  return b->scratch;
+}
+
+void require_index(LitniceView t, const char *who) {
+  if (t == nullptr) throw std::invalid_argument(std::string(who) + ": null view");
+  if (t->device != 1u) throw std::runtime_error(std::string(who) + " requires a GPU tensor");
+  if (t->dtype > 1u) throw std::runtime_error(std::string(who) + ": unsupported index dtype");
+}
+
+// device_backend.cpp:966-976: double accumulation, synchronous float result.
+float api_sum_squares(void *h, LitniceView x) {
+  Backend *b = self_reader(h);
+  require_gpu_f32(x, "litnice_b200::sum_squares_f32");
+  if (!view_is_contiguous(x)) throw std::runtime_error("litnice_b200::sum_squares_f32 requires a contiguous tensor");
+  bind(b);
+  const long long n = view_numel(x);
+  char *scr = static_cast<char *>(scratch_for(b, 1, 1));
+  double *result = reinterpret_cast<double *>(scr + 148 * 8 * sizeof(double));
+  launch_sum_squares(static_cast<const float *>(x->data), n, scr, result, b->st);
+  b->launches += 2;
+  double v = 0.0;
+  LB_CUDA(cudaMemcpyAsync(&v, result, sizeof(double), cudaMemcpyDeviceToHost, b->st));
+  sync_and_check(b);
+  return static_cast<float>(v);
+}
+
+// device_backend.cpp:1003-1060
+void relu_backward_op(void *h, LitniceView preact, LitniceView dout, LitniceView dx, const char *who) {
+  Backend *b = self(h);
+  require_gpu_f32(preact, who);
+  require_gpu_f32(dout, who);
+  require_gpu_f32(dx, who);
+  bind(b);
+  if (view_numel(preact) != view_numel(dout) || view_numel(preact) != view_numel(dx))
+    throw std::runtime_error(std::string(who) + ": numel mismatch");
+  if (view_is_contiguous(preact) && view_is_contiguous(dout) && view_is_contiguous(dx)) {
+    RowView fb = flat_view(dout);
+    launch_rowwise(EW_RELU_BWD, flat_view(preact), &fb, 0, 0.f, flat_view(dx), b->st);
+  } else {
+    RowView rp = make_row_view(preact, who), rd = make_row_view(dout, who), rx = make_row_view(dx, who);
+    if (rp.cols != rd.cols || rp.cols != rx.cols || rp.rows != rd.rows || rp.rows != rx.rows)
+      throw std::runtime_error(std::string(who) + ": shape mismatch");
+    launch_rowwise(EW_RELU_BWD, rp, &rd, 0, 0.f, rx, b->st);
+  }
+  ++b->launches;
+}
+void api_relu_backward(void *h, LitniceView preact, LitniceView dout, LitniceView dx) {
+  relu_backward_op(h, preact, dout, dx, "litnice_b200::relu_backward");
+}
+void api_relu_backward_inplace(void *h, LitniceView preact, LitniceView dout_dx) {
+  relu_backward_op(h, preact, dout_dx, dout_dx, "litnice_b200::relu_backward_inplace");
+}
+
+// device_backend.cpp:1062-1094: out[c] = sum over every row of x[.., c].
+void api_row_sum(void *h, LitniceView x, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(x, "litnice_b200::row_sum(x)");
+  require_gpu_f32(out, "litnice_b200::row_sum(out)");
+  bind(b);
+  RowView rx = make_row_view(x, "row_sum(x)");
+  if (view_numel(out) != rx.cols) throw std::runtime_error("litnice_b200::row_sum: semantic shape mismatch");
+  launch_column_sum(rx, static_cast<char *>(out->data), out->strides_bytes[out->rank - 1],
+                    scratch_for(b, rx.rows, rx.cols), b->st);
+  b->launches += 2;
+}
+
+// device_backend.cpp:1133-1152: out[p, r, c] = sum_k a[p, r, k] * b[c, k]
+void api_gemm_ranked_matrix_rhs_t(void *h, LitniceView a, LitniceView bb, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(a, "litnice_b200::gemm_ranked_matrix_rhs_t(a)");
+  require_gpu_f32(bb, "litnice_b200::gemm_ranked_matrix_rhs_t(b)");
+  require_gpu_f32(out, "litnice_b200::gemm_ranked_matrix_rhs_t(out)");
+  run_gemm(b, make_mat_view(a, "gemm_ranked_matrix_rhs_t(a)"),
+           transposed(shared_matrix(bb, "gemm_ranked_matrix_rhs_t(b)")),
+           make_mat_view(out, "gemm_ranked_matrix_rhs_t(out)"), "litnice_b200::gemm_ranked_matrix_rhs_t");
+}
+
+// device_backend.cpp:1154-1173: out[r, c] = sum over p and k of a[p, k, r] * b[p, k, c] (weight
+// gradients). One product per leading index, each added to the sum of those before it.
+void api_gemm_ranked_reduce_lhs_t(void *h, LitniceView a, LitniceView bb, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(a, "litnice_b200::gemm_ranked_reduce_lhs_t(a)");
+  require_gpu_f32(bb, "litnice_b200::gemm_ranked_reduce_lhs_t(b)");
+  require_gpu_f32(out, "litnice_b200::gemm_ranked_reduce_lhs_t(out)");
+  MatView av = make_mat_view(a, "gemm_ranked_reduce_lhs_t(a)"), bv = make_mat_view(bb, "gemm_ranked_reduce_lhs_t(b)");
+  MatView ov = make_mat_view(out, "gemm_ranked_reduce_lhs_t(out)");
+  if (av.batch != bv.batch || av.rows != bv.rows || ov.batch != 1 || ov.rows != av.cols || ov.cols != bv.cols)
+    throw std::runtime_error("litnice_b200::gemm_ranked_reduce_lhs_t: shape mismatch");
+  bind(b);
+  for (long long p = 0; p < av.batch; ++p) {
+    MatView ap = av, bp = bv;
+    ap.data = av.data + batch_offset(av, p);
+    bp.data = bv.data + batch_offset(bv, p);
+    ap.nb = bp.nb = 0;
+    ap.batch = bp.batch = 1;
+    GemmEpilogue ep;
+    if (p > 0) ep.residual = reinterpret_cast<const float *>(ov.data);  // in place: every element by one thread
+    launch_gemm_simt(transposed(ap), bp, ov, ov.rows, ov.cols, av.rows, ep, b->st);
+    ++b->launches;
+  }
+}
+
+// device_backend.cpp:1195-1214: out[p] = a[p]^T * b[p]
+void api_gemm_batched_lhs_t(void *h, LitniceView a, LitniceView bb, LitniceView out) {
+  Backend *b = self(h);
+  require_gpu_f32(a, "litnice_b200::gemm_batched_lhs_t(a)");
+  require_gpu_f32(bb, "litnice_b200::gemm_batched_lhs_t(b)");
+  require_gpu_f32(out, "litnice_b200::gemm_batched_lhs_t(out)");
+  run_gemm(b, transposed(make_mat_view(a, "gemm_batched_lhs_t(a)")), make_mat_view(bb, "gemm_batched_lhs_t(b)"),
+           make_mat_view(out, "gemm_batched_lhs_t(out)"), "litnice_b200::gemm_batched_lhs_t");
+}
+void api_gemm_batched_lhs_t_ctx(void *h, LitniceView a, LitniceView bb, LitniceView out) {
+  require_group(h, "litnice_b200::gemm_batched_lhs_t_exec_context");
+  api_gemm_batched_lhs_t(h, a, bb, out);
+}
+
+// device_backend.cpp:1281-1343
+void api_layernorm_backward(void *h, LitniceView x, LitniceView gamma, LitniceView dout, LitniceView dx,
+                            LitniceView dgamma, LitniceView dbeta) {
+  Backend *b = self(h);
+  const char *who = "litnice_b200::layernorm_backward";
+  for (LitniceView t : {x, gamma, dout, dx, dgamma, dbeta}) require_gpu_f32(t, who);
+  bind(b);
+  RowView rx = make_row_view(x, who), rd = make_row_view(dout, who), ro = make_row_view(dx, who);
+  if (rd.rows != rx.rows || rd.cols != rx.cols || ro.rows != rx.rows || ro.cols != rx.cols ||
+      view_numel(gamma) != rx.cols || view_numel(dgamma) != rx.cols || view_numel(dbeta) != rx.cols)
+    throw std::runtime_error(std::string(who) + ": shape mismatch");
+  launch_layernorm_backward(rx, static_cast<const char *>(gamma->data), gamma->strides_bytes[gamma->rank - 1], rd, ro,
+                            static_cast<char *>(dgamma->data), dgamma->strides_bytes[dgamma->rank - 1],
+                            static_cast<char *>(dbeta->data), dbeta->strides_bytes[dbeta->rank - 1],
+                            scratch_for(b, rx.rows, rx.cols), b->st);
+  b->launches += 3;
+}
+
+// device_backend.cpp:1368-1389
+void api_accumulate_embedding_grads(void *h, LitniceView ids, LitniceView d_cur, LitniceView d_tok, LitniceView d_pos) {
+  Backend *b = self(h);
+  const char *who = "litnice_b200::accumulate_embedding_grads";
+  require_index(ids, who);
+  require_gpu_f32(d_cur, who);
+  require_gpu_f32(d_tok, who);
+  require_gpu_f32(d_pos, who);
+  if (d_tok->rank != 2 || d_pos->rank != 2) throw std::runtime_error(std::string(who) + ": tables must be rank 2");
+  bind(b);
+  RowView iv = make_row_view(ids, who), rc = make_row_view(d_cur, who);
+  auto table = [](LitniceView t) {  // keep the (row, column) axes apart
+    RowView v{};
+    v.data = static_cast<char *>(t->data);
+    v.np = 1;
+    v.pd[0] = t->dims[0];
+    v.ps[0] = t->strides_bytes[0];
+    v.rows = t->dims[0];
+    v.cols = t->dims[1];
+    v.cs = t->strides_bytes[1];
+    return v;
+  };
+  RowView rt = table(d_tok), rp = table(d_pos);
+  const long long tokens = iv.rows * iv.cols, seq = ids->dims[ids->rank - 1];
+  if (rc.rows != tokens || rt.cols != rc.cols || rp.cols != rc.cols || rp.rows < seq)
+    throw std::runtime_error(std::string(who) + ": shape mismatch");
+  launch_embedding_grads(static_cast<const char *>(ids->data), ids->dtype == 0u ? 1 : 0, iv, rc, rt, rp, seq,
+                         b->err_dev, b->st);
+  b->launches += 2;
+}
+
+// device_backend.cpp:1391-1464
+void cross_entropy_op(void *h, LitniceView logits, LitniceView targets, LitniceView out_loss, bool loss, bool backward,
+                      const char *who) {
+  Backend *b = self(h);
+  require_gpu_f32(logits, who);
+  require_index(targets, who);
+  if (loss) require_gpu_f32(out_loss, who);
+  bind(b);
+  RowView rl = make_row_view(logits, who), rt = make_row_view(targets, who);
+  const long long tokens = rt.rows * rt.cols;
+  if (rl.rows != tokens) throw std::runtime_error(std::string(who) + ": logits rows and target count differ");
+  launch_cross_entropy(rl, static_cast<const char *>(targets->data), targets->dtype == 0u ? 1 : 0, rt, loss, backward,
+                       loss ? static_cast<float *>(out_loss->data) : nullptr, scratch_for(b, tokens, 1), b->err_dev,
+                       b->st);
+  b->launches += loss ? 2 : 1;
+}
+void api_cross_entropy_mean(void *h, LitniceView logits, LitniceView targets, LitniceView out_loss) {
+  cross_entropy_op(h, logits, targets, out_loss, true, false, "litnice_b200::cross_entropy_mean");
+}
+void api_cross_entropy_mean_backward_inplace(void *h, LitniceView logits, LitniceView targets, LitniceView out_loss) {
+  cross_entropy_op(h, logits, targets, out_loss, true, true, "litnice_b200::cross_entropy_mean_backward_inplace");
+}
+void api_backward_from_logits_targets(void *h, LitniceView logits, LitniceView targets) {
+  cross_entropy_op(h, logits, targets, nullptr, false, true, "litnice_b200::backward_from_logits_targets");
+}
+
+// device_backend.cpp:1519-1552, :1649-1673
+void softmax_backward_op(void *h, LitniceView sm, LitniceView dout, LitniceView dx, bool causal, const char *who) {
+  Backend *b = self(h);
+  require_gpu_f32(sm, who);
+  require_gpu_f32(dout, who);
+  require_gpu_f32(dx, who);
+  bind(b);
+  RowView rs = make_row_view(sm, who), rd = make_row_view(dout, who), rx = make_row_view(dx, who);
+  if (rs.rows != rd.rows || rs.cols != rd.cols || rs.rows != rx.rows || rs.cols != rx.cols)
+    throw std::runtime_error(std::string(who) + ": shape mismatch");
+  launch_softmax_backward(rs, rd, rx, causal, b->st);
+  ++b->launches;
+}
+void api_softmax_backward_rows(void *h, LitniceView sm, LitniceView dout, LitniceView dx) {
+  softmax_backward_op(h, sm, dout, dx, false, "litnice_b200::softmax_backward_rows");
+}
+void api_softmax_backward_causal_rows(void *h, LitniceView sm, LitniceView dout, LitniceView dx) {
+  softmax_backward_op(h, sm, dout, dx, true, "litnice_b200::softmax_backward_causal_rows");
+}
+void api_softmax_backward_causal_rows_ctx(void *h, LitniceView sm, LitniceView dout, LitniceView dx) {
+  require_group(h, "litnice_b200::softmax_backward_causal_rows_exec_context");
+  softmax_backward_op(h, sm, dout, dx, true, "litnice_b200::softmax_backward_causal_rows_exec_context");
+}
+
+// device_backend.cpp:1699-1750
+void api_adamw_step(void *h, LitniceView params, LitniceView grads, LitniceView m, LitniceView v, uint64_t step,
+                    float learning_rate, float beta1, float beta2, float weight_decay, uint32_t apply_weight_decay) {
+  Backend *b = self(h);
+  const char *who = "litnice_b200::adamw_step";
+  for (LitniceView t : {params, grads, m, v}) {
+    require_gpu_f32(t, who);
+    if (!view_is_contiguous(t)) throw std::runtime_error(std::string(who) + " requires contiguous tensors");
+    if (t->rank < 2 || t->dims[0] != params->dims[0] || t->dims[1] != params->dims[1])
+      throw std::runtime_error(std::string(who) + ": params/grads/m/v shape mismatch");
+  }
+  if (step < 1) throw std::runtime_error(std::string(who) + ": step must be >= 1");
+  if (!(learning_rate > 0.0f)) throw std::runtime_error(std::string(who) + ": learning_rate must be > 0");
+  if (!(beta1 >= 0.0f && beta1 < 1.0f)) throw std::runtime_error(std::string(who) + ": beta1 must be in [0,1)");
+  if (!(beta2 >= 0.0f && beta2 < 1.0f)) throw std::runtime_error(std::string(who) + ": beta2 must be in [0,1)");
+  const double t = static_cast<double>(step);
+  const float b1_corr = 1.0f - static_cast<float>(std::pow(static_cast<double>(beta1), t));
+  const float b2_corr = 1.0f - static_cast<float>(std::pow(static_cast<double>(beta2), t));
+  if (!(b1_corr > 0.0f && b2_corr > 0.0f)) throw std::runtime_error(std::string(who) + ": invalid bias correction");
+  bind(b);
+  launch_adamw(static_cast<float *>(params->data), static_cast<const float *>(grads->data),
+               static_cast<float *>(m->data), static_cast<float *>(v->data), params->dims[0] * params->dims[1],
+               learning_rate, beta1, beta2, b1_corr, b2_corr, weight_decay, apply_weight_decay ? 1 : 0, b->st);
+  ++b->launches;
+}
 
 // device_backend.cpp:1426-1428: synchronous scalar read.
 float api_read_scalar(void *h, LitniceView x) {
@@ -646,8 +886,8 @@ float api_read_scalar(void *h, LitniceView x) {
   return v;
 }
 
-// device_backend.cpp:1752-1775. No caller exists in the host code; the file
-// range is staged through host memory and copied to the device.
+// device_backend.cpp:1752-1775. No caller exists in the host code. The range goes to the device
+// in pieces through pinned memory, file reads overlapping the copies.
 uint32_t api_file2device_supported(void *h) {
   self(h);
   return 1u;
@@ -657,15 +897,14 @@ void api_read_file2device(void *h, const char *path, void *dst, uint64_t size, u
   if (size == 0) return;
   if (dst == nullptr || path == nullptr)
     throw std::invalid_argument("litnice_b200::read_file2device: null argument");
-  std::ifstream in(path, std::ios::binary);
-  if (!in) throw std::runtime_error("litnice_b200::read_file2device: failed to open file");
-  in.seekg(static_cast<std::streamoff>(file_offset), std::ios::beg);
-  if (!in) throw std::runtime_error("litnice_b200::read_file2device: failed to seek file");
-  std::vector<char> buf(static_cast<size_t>(size));
-  in.read(buf.data(), static_cast<std::streamsize>(size));
-  if (in.gcount() != static_cast<std::streamsize>(size))
-    throw std::runtime_error("litnice_b200::read_file2device: short read");
-  api_h2d(b, dst, buf.data(), size);
+  bind(b);
+  try {
+    file_to_device(path, file_offset, size, dst, b->st, false);
+  } catch (const CudaError &) {
+    throw;
+  } catch (const std::exception &e) {
+    throw std::runtime_error(std::string("litnice_b200::read_file2device: ") + e.what());
+  }
 }
 
 const BackendApiV1 kApi = {

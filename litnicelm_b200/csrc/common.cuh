@@ -34,6 +34,7 @@ enum DevErrCode : int {
   DEVERR_BAD_TOKEN_ID = 1,   // embedding id outside [0, vocab)
   DEVERR_WAIT_TIMEOUT = 2,   // a bounded mbarrier / TMEM wait ran out
   DEVERR_BAD_ARGUMENT = 3,
+  DEVERR_BAD_TARGET = 4,     // cross-entropy target outside [0, vocab)
 };
 struct DevErr {
   int code;
@@ -154,9 +155,10 @@ long long view_numel(const BackendTensorView *t);
 // ---- kernel families (host launchers) ---------------------------------------
 
 // elementwise.cu
-enum EwOp : int { EW_COPY = 0, EW_ADD, EW_ADD_BIAS, EW_ADD_BIAS_RELU, EW_RELU, EW_MUL_SCALAR, EW_FILL };
-// out[row, c] = op(a[row, c], b[...]); b is a full tensor (EW_ADD), a [rows_b, cols]
-// table indexed by row % rows_b (broadcast add), or a bias row.
+enum EwOp : int { EW_COPY = 0, EW_ADD, EW_ADD_BIAS, EW_ADD_BIAS_RELU, EW_RELU, EW_MUL_SCALAR, EW_FILL, EW_RELU_BWD };
+// out[row, c] = op(a[row, c], b[...]); b is a full tensor (EW_ADD; EW_RELU_BWD:
+// out = a > 0 ? b : 0), a [rows_b, cols] table indexed by row % rows_b (broadcast
+// add), or a bias row.
 void launch_rowwise(EwOp op, const RowView &a, const RowView *b, long long b_mod_rows,
                     float scalar, const RowView &out, cudaStream_t st);
 void launch_causal_mask(const MatView &scores, float neg_inf, cudaStream_t st);
@@ -184,6 +186,30 @@ struct GemmEpilogue {
 // come from the three MatViews' batch axes (b_batch may be null for a shared B).
 void launch_gemm_simt(const MatView &a, const MatView &bmat, const MatView &c, long long m,
                       long long n, long long k, const GemmEpilogue &ep, cudaStream_t st);
+
+// ingest.cu: `bytes` of a file from file_offset on into device memory at dst, in pieces through
+// pinned buffers so that reading and the host-to-device copies overlap; returns when everything has
+// arrived. check_finite_f32: the bytes are floats and a NaN or infinity raises std::domain_error
+// (the destination is then partly written). Other failures raise std::runtime_error.
+void file_to_device(const char *path, uint64_t file_offset, uint64_t bytes, void *dst, cudaStream_t st,
+                    bool check_finite_f32);
+
+// training.cu: backward and optimiser operators of the plugin table. `scratch` is device
+// memory of at least training_scratch_bytes(rows, cols) for the operand at hand.
+size_t training_scratch_bytes(long long rows, long long cols);
+void launch_sum_squares(const float *x, long long n, void *scratch, double *result_dev, cudaStream_t st);
+void launch_column_sum(const RowView &x, char *out, long long out_cs, void *scratch, cudaStream_t st);
+void launch_layernorm_backward(const RowView &x, const char *gamma, long long gamma_cs, const RowView &dout,
+                               const RowView &dx, char *dgamma, long long dgamma_cs, char *dbeta, long long dbeta_cs,
+                               void *scratch, cudaStream_t st);
+void launch_embedding_grads(const char *ids, int ids_is_f32, const RowView &ids_rows, const RowView &d_cur,
+                            const RowView &d_tok, const RowView &d_pos, long long seq, DevErr *err, cudaStream_t st);
+void launch_cross_entropy(const RowView &logits, const char *targets, int targets_is_f32, const RowView &targets_rows,
+                          bool want_loss, bool want_backward, float *loss_out, void *scratch, DevErr *err,
+                          cudaStream_t st);
+void launch_softmax_backward(const RowView &sm, const RowView &dout, const RowView &dx, bool causal, cudaStream_t st);
+void launch_adamw(float *params, const float *grads, float *m, float *v, long long n, float lr, float beta1,
+                  float beta2, float b1_corr, float b2_corr, float weight_decay, int apply_decay, cudaStream_t st);
 
 // native-loop kernels (dense row-major activations) ---------------------------
 
@@ -218,10 +244,15 @@ void launch_layernorm_dense(const float *x, const float *gamma, const float *bet
 
 // gemv.cu: out[m, n] = x[m, :] . W[:, n] for m <= 8 rows; W row-major [k, n].
 // scratch must hold gemv_scratch_floats(m, n, k) floats when the launcher
-// decides to split k across CTAs.
+// decides to split k across CTAs. x must hold 1, 2, 4 or 8 rows (m rounded up).
+// err (optional) receives DEVERR_WAIT_TIMEOUT if a bounded wait of the
+// streaming kernel runs out. Returns the number of kernels launched.
 size_t gemv_scratch_floats(int m, int n, int k);
-void launch_gemv(const float *x, int m, const float *w, int k, int n, const float *bias,
-                 float *out, float *scratch, cudaStream_t st);
+// residual ([m, n] dense, added after the bias) and relu finish the product as the layer wiring of
+// the reference does (add_bias_rowwise, add, relu).
+int launch_gemv(const float *x, int m, const float *w, int k, int n, const float *bias,
+                float *out, float *scratch, cudaStream_t st, DevErr *err = nullptr,
+                const float *residual = nullptr, int relu = 0);
 
 // attention.cu: ctx[r, h*dh + :] for rows r = b*s + t of qkv [rows, 3*d].
 // ctx_lo != nullptr: ctx receives the TF32 high part and ctx_lo the low part.
@@ -238,6 +269,24 @@ AttentionPlan attention_plan(int n_streams, int s, int n_heads, int dh);
 // as the actual context length state->s.
 void launch_attention(const float *qkv, float *ctx, float *ctx_lo, int n_streams, int s, int n_heads, int d_model,
                       float *scratch, int *counters, const LoopState *state, cudaStream_t st);
+
+// decode.cu: the one-row-per-stream kernels of the opt-in cached mode. Caches are
+// [n_streams][cap][d] per layer; s (state->s when state is set, else s_host) is the context
+// length including the newest token, whose K and V the attention kernel appends.
+struct DecodeAttnPlan {
+  int keys_per_chunk;
+  int chunks;
+  size_t scratch_floats;
+};
+DecodeAttnPlan attn_decode_plan(int n_streams, int s, int n_heads, int dh);
+void launch_embed_last_ln(const float *tok_emb, const float *pos_emb, const int *ids, int ids_ld,
+                          const LoopState *state, int s_host, int n_streams, int d, int vocab, const float *gamma,
+                          const float *beta, float *x, float *ln, DevErr *err, cudaStream_t st);
+void launch_kv_store(const float *qkv, const LoopState *state, int s_host, int n_streams, int d, int cap, float *kc,
+                     float *vc, cudaStream_t st);
+// Returns the number of kernels launched (2 when the keys are cut into chunks).
+int launch_attn_decode(const float *qkv, float *kc, float *vc, int cap, int d_model, int n_heads, int n_streams,
+                       const LoopState *state, int s_host, float *part, float *ctx, cudaStream_t st);
 
 // sampler.cu
 struct SamplerParams {

@@ -9,11 +9,15 @@
 //
 //   litnice_b200_run infer   --config cfg.yaml [--prompt TEXT | --ids-file ids.i32]
 //                            [--max_new N] [--temp T] [--top_k K] [--top_p P] [--seed S]
-//                            [--streams N] [--out-ids-file out.i32]
+//                            [--streams N] [--gpus G] [--out-ids-file out.i32]
 //   litnice_b200_run inspect --config cfg.yaml [--prompt TEXT | --ids-file ids.i32]
+//   litnice_b200_run partition --streams N --gpus G      (prints the split; needs no GPU)
 //
 // --ids-file holds int32 token ids, streams*len of them (row-major); with
 // --streams N the N rows are decoded in lockstep with seeds seed, seed+1, ...
+// With --gpus G the streams are cut into G contiguous blocks, one host thread
+// per GPU decodes its block on its own session (weights replicated, nothing is
+// exchanged between GPUs), and the threads are joined before anything is printed.
 #include <dlfcn.h>
 
 #include <algorithm>
@@ -26,8 +30,10 @@
 #include <iostream>
 #include <map>
 #include <sstream>
+#include <chrono>
 #include <stdexcept>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../../../include/litnice_backend_b200.h"
@@ -173,9 +179,17 @@ void report(const char *event, uint32_t step, float value, const std::string &ms
             << "\n";
 }
 
+// Contiguous blocks; the first total % parts blocks carry one stream more.
+void partition_streams(int total, int parts, int index, int *first, int *count) {
+  const int base = total / parts, extra = total % parts;
+  *count = base + (index < extra ? 1 : 0);
+  *first = index * base + std::min(index, extra);
+}
+
 struct Api {
   void *handle = nullptr;
   decltype(&litnice_b200_session_create) create = nullptr;
+  decltype(&litnice_b200_session_create_on) create_on = nullptr;
   decltype(&litnice_b200_session_destroy) destroy = nullptr;
   decltype(&litnice_b200_last_error) last_error = nullptr;
   decltype(&litnice_b200_load_checkpoint) load_checkpoint = nullptr;
@@ -191,6 +205,7 @@ struct Api {
   field = reinterpret_cast<decltype(field)>(dlsym(handle, sym));   \
   if (!field) throw std::runtime_error(std::string("missing symbol ") + sym)
     RESOLVE(create, "litnice_b200_session_create");
+    RESOLVE(create_on, "litnice_b200_session_create_on");
     RESOLVE(destroy, "litnice_b200_session_destroy");
     RESOLVE(last_error, "litnice_b200_last_error");
     RESOLVE(load_checkpoint, "litnice_b200_load_checkpoint");
@@ -207,6 +222,16 @@ int run(int argc, char **argv) {
   const std::string mode = argv[1];
   std::map<std::string, std::string> opt;
   for (int i = 2; i + 1 < argc; i += 2) opt[argv[i]] = argv[i + 1];
+  if (mode == "partition") {
+    const int total = std::stoi(opt.at("--streams")), parts = std::stoi(opt.at("--gpus"));
+    if (total < 0 || parts <= 0) throw std::runtime_error("partition needs --streams >= 0 and --gpus >= 1");
+    for (int g = 0; g < parts; ++g) {
+      int first = 0, count = 0;
+      partition_streams(total, parts, g, &first, &count);
+      std::cout << "gpu " << g << " first " << first << " count " << count << "\n";
+    }
+    return 0;
+  }
   if (!opt.count("--config")) throw std::runtime_error("--config is required");
   auto cfg = parse_yaml(opt["--config"]);
   auto get = [&](const char *flag, const char *key) { return opt.count(flag) ? opt[flag] : cfg.at(key); };
@@ -228,6 +253,8 @@ int run(int argc, char **argv) {
                            std::stof(get("--top_p", "inference.top_p"))};
   const uint32_t seed = (uint32_t)std::stoul(get("--seed", "inference.seed"));
   const int streams = opt.count("--streams") ? std::stoi(opt["--streams"]) : 1;
+  const int gpus = opt.count("--gpus") ? std::stoi(opt["--gpus"]) : 1;
+  if (streams <= 0 || gpus <= 0) throw std::runtime_error("--streams and --gpus must be positive");
 
   std::vector<int32_t> ids;
   if (opt.count("--ids-file")) {
@@ -248,6 +275,70 @@ int run(int argc, char **argv) {
 
   Api api(cfg.at("backend.library"));
   std::cout << "[DeviceBackend] Loaded backend library: " << cfg.at("backend.library") << " (native loop)\n";
+  const std::string ckpt = cfg.at("paths.model_file_best");
+
+  if (mode == "infer" && gpus > 1) {
+    // One host thread per GPU, each with its own session and its own block of streams.
+    std::vector<uint32_t> seeds((size_t)streams);
+    for (int i = 0; i < streams; ++i) seeds[(size_t)i] = seed + (uint32_t)i;
+    std::vector<int32_t> out((size_t)streams * (size_t)std::max(1, max_new));
+    std::vector<int> counts((size_t)gpus, 0);
+    std::vector<std::string> errors((size_t)gpus);
+    std::vector<double> device_ms((size_t)gpus, 0.0);
+    const auto t0 = std::chrono::steady_clock::now();
+    std::vector<std::thread> workers;
+    for (int g = 0; g < gpus; ++g) {
+      workers.emplace_back([&, g]() {
+        int first = 0, n = 0;
+        partition_streams(streams, gpus, g, &first, &n);
+        if (n == 0) return;
+        litnice_b200_session *ws = nullptr;
+        auto fail = [&](const char *what, int code) {
+          errors[(size_t)g] = std::string(what) + " failed on GPU " + std::to_string(g) + " (" + std::to_string(code) +
+                              "): " + api.last_error(ws);
+          if (ws) api.destroy(ws);
+        };
+        int rc = api.create_on(&d, n, g, &ws);
+        if (rc != LITNICE_B200_OK) return fail("session_create", rc);
+        rc = api.load_checkpoint(ws, ckpt.c_str());
+        if (rc != LITNICE_B200_OK) return fail("load_checkpoint", rc);
+        rc = api.generate(ws, ids.data() + (size_t)first * len, n, len, max_new, &sp, seeds.data() + first,
+                          out.data() + (size_t)first * std::max(1, max_new), &counts[(size_t)g]);
+        if (rc != LITNICE_B200_OK) return fail("generate", rc);
+        litnice_b200_stats stt{};
+        api.get_stats(ws, &stt);
+        device_ms[(size_t)g] = stt.device_ms;
+        api.destroy(ws);
+      });
+    }
+    for (auto &w : workers) w.join();
+    const double wall_ms =
+        std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    for (auto &e : errors)
+      if (!e.empty()) throw std::runtime_error(e);
+    const int count = counts[0];
+    report("START", 0, 0.0f, "Inference started: " + std::to_string(streams) + " streams on " + std::to_string(gpus) +
+                                 " GPUs, max_new=" + std::to_string(max_new));
+    for (int b = 0; b < streams; ++b) {
+      std::string text;
+      for (int i = 0; i < len; ++i) text += tok.decode(ids[(size_t)b * len + i]);
+      for (int i = 0; i < count; ++i) text += tok.decode(out[(size_t)b * max_new + i]);
+      if (b == 0) report("END", (uint32_t)(len + count), 0.0f, "Inference complete");
+      report("TOKEN_GEN", 0, 0.0f, text);
+    }
+    if (opt.count("--out-ids-file")) {
+      std::ofstream o(opt["--out-ids-file"], std::ios::binary);
+      for (int b = 0; b < streams; ++b)
+        o.write(reinterpret_cast<const char *>(out.data() + (size_t)b * max_new), (std::streamsize)count * 4);
+    }
+    const double slowest = *std::max_element(device_ms.begin(), device_ms.end());
+    std::fprintf(stderr,
+                 "[litnice_b200] %d streams x %d tokens on %d GPUs: slowest GPU %.3f ms on device (%.1f tokens/s), "
+                 "%.1f ms wall including weight loading\n",
+                 streams, count, gpus, slowest, slowest > 0 ? (double)streams * count * 1e3 / slowest : 0.0, wall_ms);
+    return 0;
+  }
+
   litnice_b200_session *s = nullptr;
   int rc = api.create(&d, streams, &s);
   auto check = [&](int code, const char *what) {
@@ -258,7 +349,7 @@ int run(int argc, char **argv) {
     }
   };
   check(rc, "session_create");
-  check(api.load_checkpoint(s, cfg.at("paths.model_file_best").c_str()), "load_checkpoint");
+  check(api.load_checkpoint(s, ckpt.c_str()), "load_checkpoint");
 
   if (mode == "infer") {
     std::ostringstream start;

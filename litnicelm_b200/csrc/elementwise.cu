@@ -19,6 +19,7 @@ __device__ __forceinline__ float ew_apply(float a, float b, float s) {
   }
   if (OP == EW_RELU) return a > 0.0f ? a : 0.0f;
   if (OP == EW_MUL_SCALAR) return a * s;
+  if (OP == EW_RELU_BWD) return a > 0.0f ? b : 0.0f;  // device_backend.cpp:1003-1060
   return s;  // EW_FILL
 }
 
@@ -30,7 +31,7 @@ template <int OP, int VEC>
 __global__ void rowwise_kernel(RowView a, RowView b, long long b_mod_rows, float scalar,
                                RowView out, long long chunks_per_row, long long total_chunks) {
   constexpr bool HAS_A = OP != EW_FILL;
-  constexpr bool HAS_B = OP == EW_ADD || OP == EW_ADD_BIAS || OP == EW_ADD_BIAS_RELU;
+  constexpr bool HAS_B = OP == EW_ADD || OP == EW_ADD_BIAS || OP == EW_ADD_BIAS_RELU || OP == EW_RELU_BWD;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_chunks;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long row = idx / chunks_per_row;
@@ -71,7 +72,7 @@ template <int OP>
 void launch_rowwise_op(const RowView &a, const RowView *b, long long b_mod_rows, float scalar,
                        const RowView &out, cudaStream_t st) {
   constexpr bool HAS_A = OP != EW_FILL;
-  constexpr bool HAS_B = OP == EW_ADD || OP == EW_ADD_BIAS || OP == EW_ADD_BIAS_RELU;
+  constexpr bool HAS_B = OP == EW_ADD || OP == EW_ADD_BIAS || OP == EW_ADD_BIAS_RELU || OP == EW_RELU_BWD;
   bool vec = vec4_ok(out);
   if (HAS_A) vec = vec && vec4_ok(a);
   if (HAS_B) vec = vec && vec4_ok(*b);
@@ -152,6 +153,7 @@ void launch_rowwise(EwOp op, const RowView &a, const RowView *b, long long b_mod
     case EW_RELU: launch_rowwise_op<EW_RELU>(a, b, b_mod_rows, scalar, out, st); break;
     case EW_MUL_SCALAR: launch_rowwise_op<EW_MUL_SCALAR>(a, b, b_mod_rows, scalar, out, st); break;
     case EW_FILL: launch_rowwise_op<EW_FILL>(a, b, b_mod_rows, scalar, out, st); break;
+    case EW_RELU_BWD: launch_rowwise_op<EW_RELU_BWD>(a, b, b_mod_rows, scalar, out, st); break;
   }
 }
 

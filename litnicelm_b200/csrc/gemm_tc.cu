@@ -185,6 +185,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     }
     pdl_wait();
     if (lane == 0) {
+      if (ep.timeline != nullptr) atomicMin(ep.timeline + 14, global_timer());  // the predecessor has completed
       for (int kb = 0; kb < pre; ++kb) {
         const unsigned stage = base + (unsigned)kb * L::STAGE_BYTES;
         const int kx = (kb0 + kb) * KBE;
@@ -495,13 +496,19 @@ void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const
                 float *part, int *counters, DevErr *err, cudaStream_t st, const float *a_inv_scale = nullptr,
                 const float *b_inv_scale = nullptr) {
   using L = TcSmem<BN, STAGES>;
+  // Sessions on several host threads (one per GPU) may launch at the same time: the per-device
+  // set-up below and the occupancy cache are guarded by one mutex per kernel configuration.
+  static std::mutex cfg_mu;
   static bool configured[64] = {};
   int dev = 0;
   LB_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
-    LB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 L::TOTAL));
-    configured[dev] = true;
+  {
+    std::lock_guard<std::mutex> lock(cfg_mu);
+    if (dev >= 64 || !configured[dev]) {
+      LB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   L::TOTAL));
+      if (dev < 64) configured[dev] = true;
+    }
   }
   dim3 grid(n / BN, (m + TC_BM - 1) / TC_BM, splits);
   // The CTAs that share a tile form a cluster and reduce through distributed shared memory when
@@ -512,6 +519,7 @@ void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const
     // A cluster must sit inside one GPC: fewer clusters than SMs / splits may be resident at once. When
     // the grid does not fit in one wave of clusters the scratch path (any SM will do) is the faster one.
     static int max_clusters[9] = {};  // per cluster size; 0 = not asked yet (one device type per process)
+    std::lock_guard<std::mutex> lock(cfg_mu);
     if (max_clusters[cluster_splits] == 0) {
       cudaLaunchConfig_t cfg{};
       cfg.gridDim = grid;
@@ -571,6 +579,24 @@ void tc_make_map_f16(CUtensorMap *map, const __half *base, unsigned long long ro
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw std::runtime_error("litnice_b200: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+}
+
+void tc_make_map_plain(CUtensorMap *map, const float *base, unsigned long long rows, unsigned long long cols,
+                       unsigned box_rows, unsigned box_cols) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) throw std::runtime_error("litnice_b200: cuTensorMapEncodeTiled is not available");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || cols % 4 != 0 || box_rows == 0 || box_rows > 256 ||
+      box_cols == 0 || box_cols > 256 || (box_cols * 4) % 16 != 0)
+    throw std::invalid_argument("litnice_b200: tensor map operand must be 16-byte aligned with cols % 4 == 0");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 4};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     throw std::runtime_error("litnice_b200: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));

@@ -85,6 +85,11 @@ void tc_make_map(CUtensorMap *map, const float *base, unsigned long long rows, u
 void tc_make_map_f16(CUtensorMap *map, const __half *base, unsigned long long rows, unsigned long long k,
                      unsigned box_rows);
 
+// Tensor map over a dense row-major fp32 array [rows, cols] with boxes of box_rows x box_cols
+// elements stored as they lie (no swizzle); cols % 4 == 0, base 16-byte aligned.
+void tc_make_map_plain(CUtensorMap *map, const float *base, unsigned long long rows, unsigned long long cols,
+                       unsigned box_rows, unsigned box_cols);
+
 // How one product is tiled: tile width (64, 128 or 256 columns), how many CTAs share
 // the k range of a tile, and the scratch that sharing needs (floats of partial
 // tiles; int counters that must be zero before the first launch and are left

@@ -6,15 +6,26 @@
 // bandwidth: every weight byte is read exactly once with 16-byte coalesced
 // loads, 4*k*n bytes per call.
 //
-// A CTA owns 128 consecutive output columns (32 lanes x float4) and a slice of
-// k; its 8 warps take interleaved rows of that slice and combine through shared
-// memory. When n/128 CTAs cannot fill the GPU, k is also split across CTAs:
-// partial sums go to scratch [split][m][n] and a second kernel adds them in a
-// fixed order, so results do not depend on scheduling.
+// Two kernels. The streaming kernel (gemv_tma_kernel) takes every shape whose
+// operands TMA can address (n % 4 == 0, k % 4 == 0, 16-byte aligned pointers,
+// at least one tile of columns and one stage of rows): a CTA owns 128 or 256
+// consecutive columns and a range of k; one producer thread moves boxes of W
+// (16 KB: 32 rows x 128 columns or 16 rows x 256 columns) and the matching
+// pieces of x into a ring of six shared-memory stages with TMA / bulk copies
+// that complete on mbarriers, so each CTA keeps up to 96 KB of weight bytes in
+// flight whatever its warps are doing; eight consumer warps read the stages
+// with conflict-free 16-byte loads. The plain kernel (gemv_kernel) takes the
+// rest with 16-byte __ldg loads: a CTA owns 128 columns and a slice of k, its
+// 8 warps take interleaved rows. In both, when the column tiles alone cannot
+// fill the GPU, k is also split across CTAs: partial sums go to scratch
+// [split][m][n] and a second kernel adds them in a fixed order, so results do
+// not depend on scheduling.
 #include "common.cuh"
+#include "tc_ptx.cuh"
 
 #include <cstdio>
 #include <mutex>
+#include <vector>
 
 namespace lb {
 
@@ -28,7 +39,7 @@ template <int M, bool VEC>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 gemv_kernel(const float *__restrict__ x, const float *__restrict__ w, int k, int n,
             int k_per_split, const float *__restrict__ bias, float *__restrict__ out,
-            float *__restrict__ partial) {
+            float *__restrict__ partial, const float *__restrict__ residual, int relu) {
   __shared__ __align__(16) float xs[M][GV_XCHUNK];
   __shared__ __align__(16) float red[GV_WARPS][M][GV_COLS];
   pdl_launch_dependents();
@@ -93,13 +104,18 @@ gemv_kernel(const float *__restrict__ x, const float *__restrict__ w, int k, int
       partial[((long long)blockIdx.y * M + i) * n + col] = v;
     } else {
       if (bias) v += bias[col];
+      if (residual) v += residual[(long long)i * n + col];
+      if (relu) v = v > 0.f ? v : 0.f;
       out[(long long)i * n + col] = v;
     }
   }
 }
 
+// Adds the k ranges' partial sums in range order, then bias, residual and ReLU
+// (add_bias_rowwise / add / relu of the reference, device_backend.cpp:840-908,752-813,978-1001).
 __global__ void gemv_reduce_kernel(const float *__restrict__ partial, int splits, int m, int n,
-                                   const float *__restrict__ bias, float *__restrict__ out) {
+                                   const float *__restrict__ bias, float *__restrict__ out,
+                                   const float *__restrict__ residual, int relu) {
   pdl_launch_dependents();
   pdl_wait();
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -107,10 +123,12 @@ __global__ void gemv_reduce_kernel(const float *__restrict__ partial, int splits
   float v = 0.f;
   for (int s = 0; s < splits; ++s) v += partial[(long long)s * m * n + idx];
   if (bias) v += bias[idx % n];
+  if (residual) v += residual[idx];
+  if (relu) v = v > 0.f ? v : 0.f;
   out[idx] = v;
 }
 
-int choose_splits(int n, int k) {
+int choose_splits(int n, int k) {  // plain kernel
   const int col_blocks = (n + GV_COLS - 1) / GV_COLS;
   if (col_blocks >= 148) return 1;
   int splits = (2 * 148 + col_blocks - 1) / col_blocks;
@@ -121,8 +139,8 @@ int choose_splits(int n, int k) {
 }
 
 template <int M>
-void launch_m(const float *x, const float *w, int k, int n, const float *bias, float *out,
-              float *scratch, cudaStream_t st) {
+int launch_m(const float *x, const float *w, int k, int n, const float *bias, float *out,
+             float *scratch, cudaStream_t st, const float *residual, int relu) {
   const int splits = scratch ? choose_splits(n, k) : 1;
   const int k_per_split = (k + splits - 1) / splits;
   dim3 grid((n + GV_COLS - 1) / GV_COLS, splits);
@@ -130,34 +148,360 @@ void launch_m(const float *x, const float *w, int k, int n, const float *bias, f
   const bool vec = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
   if (vec)
     launch_pdl(gemv_kernel<M, true>, grid, dim3(GV_WARPS * 32), 0, st, g_pdl_enabled, x, w, k, n, k_per_split, bias, out,
-               partial);
+               partial, residual, relu);
   else
     launch_pdl(gemv_kernel<M, false>, grid, dim3(GV_WARPS * 32), 0, st, g_pdl_enabled, x, w, k, n, k_per_split, bias, out,
-               partial);
+               partial, residual, relu);
   if (splits > 1) {
     const long long total = (long long)M * n;
     launch_pdl(gemv_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, g_pdl_enabled,
-               (const float *)partial, splits, M, n, bias, out);
+               (const float *)partial, splits, M, n, bias, out, residual, relu);
+    return 2;
   }
+  return 1;
 }
 
-}  // namespace
-
-size_t gemv_scratch_floats(int m, int n, int k) {
+size_t plain_scratch_floats(int m, int n, int k) {
   const int splits = choose_splits(n, k);
   const int mm = m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8));
   return splits > 1 ? (size_t)splits * mm * n : 0;
 }
 
-void launch_gemv(const float *x, int m, const float *w, int k, int n, const float *bias,
-                 float *out, float *scratch, cudaStream_t st) {
+int launch_gemv_plain(const float *x, int m, const float *w, int k, int n, const float *bias,
+                      float *out, float *scratch, cudaStream_t st, const float *residual = nullptr, int relu = 0) {
   // Rows beyond m up to the template width read as zeros inside the kernel only
   // if x holds them; callers pass buffers padded to 8 rows.
-  if (m <= 1) launch_m<1>(x, w, k, n, bias, out, scratch, st);
-  else if (m <= 2) launch_m<2>(x, w, k, n, bias, out, scratch, st);
-  else if (m <= 4) launch_m<4>(x, w, k, n, bias, out, scratch, st);
-  else if (m <= 8) launch_m<8>(x, w, k, n, bias, out, scratch, st);
-  else throw std::invalid_argument("launch_gemv: m must be <= 8");
+  if (m <= 1) return launch_m<1>(x, w, k, n, bias, out, scratch, st, residual, relu);
+  if (m <= 2) return launch_m<2>(x, w, k, n, bias, out, scratch, st, residual, relu);
+  if (m <= 4) return launch_m<4>(x, w, k, n, bias, out, scratch, st, residual, relu);
+  if (m <= 8) return launch_m<8>(x, w, k, n, bias, out, scratch, st, residual, relu);
+  throw std::invalid_argument("launch_gemv: m must be <= 8");
+}
+
+// ---------------------------------------------------------------------------
+// Streaming kernel: W through TMA into a shared-memory ring.
+// ---------------------------------------------------------------------------
+
+constexpr int GT_CONSUMERS = 8;        // consumer warps; warp GT_CONSUMERS is the producer
+constexpr int GT_STAGES = 6;
+constexpr int GT_W_BYTES = 16384;      // one box of W
+
+template <int M, int TN>
+struct GtShape {
+  static constexpr int COLG = TN / 128;             // groups of 128 columns (one warp wide)
+  static constexpr int KG = GT_CONSUMERS / COLG;    // warps that share a column group take 4 rows each
+  static constexpr int ROWS = KG * 4;               // rows of W per stage
+  static constexpr int X_BYTES = (M * ROWS * 4 + 127) / 128 * 128;
+  static constexpr int STAGE = GT_W_BYTES + X_BYTES;
+  static constexpr int TOTAL = GT_STAGES * STAGE;
+  static_assert(ROWS * TN * 4 == GT_W_BYTES, "a box of W is 16 KB");
+  static_assert((KG + 1) * M * TN * 4 <= TOTAL, "the final reduction reuses the ring");
+};
+
+__device__ __forceinline__ bool gt_wait(unsigned bar, unsigned parity, volatile int *abort_flag, DevErr *err,
+                                        int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_limit(bar, parity, abort_flag, err, where, WAIT_LIMIT_NS);
+}
+
+// bias, residual and ReLU on four finished sums (add_bias_rowwise, add and relu of the reference,
+// device_backend.cpp:840-908, 752-813, 978-1001, in that order).
+__device__ __forceinline__ void gt_finish(float4 &v, const float *bias, const float *residual, int relu,
+                                          long long idx, int col) {
+  if (bias) {
+    const float4 b = *reinterpret_cast<const float4 *>(&bias[col]);
+    v.x += b.x;
+    v.y += b.y;
+    v.z += b.z;
+    v.w += b.w;
+  }
+  if (residual) {
+    const float4 r = *reinterpret_cast<const float4 *>(&residual[idx]);
+    v.x += r.x;
+    v.y += r.y;
+    v.z += r.z;
+    v.w += r.w;
+  }
+  if (relu) {
+    v.x = v.x > 0.f ? v.x : 0.f;
+    v.y = v.y > 0.f ? v.y : 0.f;
+    v.z = v.z > 0.f ? v.z : 0.f;
+    v.w = v.w > 0.f ? v.w : 0.f;
+  }
+}
+
+template <int M, int TN>
+__global__ void __launch_bounds__((GT_CONSUMERS + 1) * 32)
+gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap, int k, int n,
+                int k_per_split, const float *__restrict__ bias, float *__restrict__ out,
+                float *__restrict__ partial, DevErr *err, const float *__restrict__ residual, int relu,
+                int cluster_splits) {
+  using S = GtShape<M, TN>;
+  extern __shared__ __align__(1024) unsigned char gt_smem[];
+  __shared__ __align__(8) unsigned long long bar_full[GT_STAGES], bar_empty[GT_STAGES];
+  __shared__ int abort_flag;
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int n0 = blockIdx.x * TN;
+  const int kb = blockIdx.z * k_per_split;
+  const int ke = min(k, kb + k_per_split);
+  const int n_iter = (ke - kb + S::ROWS - 1) / S::ROWS;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < GT_STAGES; ++i) {
+      mbar_init(smem_u32(&bar_full[i]), 1);
+      mbar_init(smem_u32(&bar_empty[i]), GT_CONSUMERS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (wid == GT_CONSUMERS) {
+    // Producer. The weights never change while the loop runs, so their first boxes
+    // are requested before the wait for the preceding kernel; x is that kernel's output.
+    if (lane == 0) {
+      // One box of W [ROWS, TN] and one of x [M, ROWS] per stage (a copy per row of x made the
+      // TMA unit the bound at 8 rows); both count their whole boxes on the stage's barrier and
+      // read zeros past the end of k.
+      const int ahead = n_iter < GT_STAGES ? n_iter : GT_STAGES;
+      for (int it = 0; it < ahead; ++it) {
+        const unsigned full = smem_u32(&bar_full[it]);
+        mbar_expect_tx(full, GT_W_BYTES + M * S::ROWS * 4);
+        tma_load_2d(smem_u32(gt_smem + it * S::STAGE), &wmap, n0, kb + it * S::ROWS, full);
+      }
+      pdl_wait();
+      for (int it = 0; it < ahead; ++it)
+        tma_load_2d(smem_u32(gt_smem + it * S::STAGE + GT_W_BYTES), &xmap, kb + it * S::ROWS, 0,
+                    smem_u32(&bar_full[it]));
+      for (int it = GT_STAGES; it < n_iter; ++it) {
+        const int st = it % GT_STAGES;
+        if (!gt_wait(smem_u32(&bar_empty[st]), ((it / GT_STAGES) - 1) & 1, &abort_flag, err, 1)) break;
+        const int k0 = kb + it * S::ROWS;
+        const unsigned full = smem_u32(&bar_full[st]);
+        mbar_expect_tx(full, GT_W_BYTES + M * S::ROWS * 4);
+        tma_load_2d(smem_u32(gt_smem + st * S::STAGE), &wmap, n0, k0, full);
+        tma_load_2d(smem_u32(gt_smem + st * S::STAGE + GT_W_BYTES), &xmap, k0, 0, full);
+      }
+    }
+    if (cluster_splits <= 1) return;
+  } else {
+    // Consumers: warp -> (column group, 4 rows of every stage); lane -> 4 columns.
+    const int colg = wid % S::COLG, kg = wid / S::COLG;
+    float acc[M][4];
+#pragma unroll
+    for (int i = 0; i < M; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int it = 0; it < n_iter; ++it) {
+      const int st = it % GT_STAGES;
+      const bool ok = gt_wait(smem_u32(&bar_full[st]), (it / GT_STAGES) & 1, &abort_flag, err, 2);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      const int rv = min(S::ROWS, ke - (kb + it * S::ROWS));
+      if (kg * 4 < rv) {  // a ragged last stage ends on a multiple of 4 rows (k % 4 == 0)
+        const unsigned char *wt = gt_smem + st * S::STAGE;
+        const float *xs = reinterpret_cast<const float *>(wt + GT_W_BYTES);
+        float4 wv[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+          wv[r] = *reinterpret_cast<const float4 *>(wt + ((kg * 4 + r) * TN + colg * 128 + lane * 4) * 4);
+#pragma unroll
+        for (int i = 0; i < M; ++i) {
+          const float4 xv = *reinterpret_cast<const float4 *>(xs + i * S::ROWS + kg * 4);
+          const float xr[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            acc[i][0] = fmaf(xr[r], wv[r].x, acc[i][0]);
+            acc[i][1] = fmaf(xr[r], wv[r].y, acc[i][1]);
+            acc[i][2] = fmaf(xr[r], wv[r].z, acc[i][2]);
+            acc[i][3] = fmaf(xr[r], wv[r].w, acc[i][3]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_empty[st]));
+    }
+    // Every load the producer issued has been waited for above, so the ring is free:
+    // the k groups of a column meet in it and are added in a fixed order.
+    asm volatile("bar.sync 1, %0;" ::"n"(GT_CONSUMERS * 32) : "memory");
+    float *red = reinterpret_cast<float *>(gt_smem);  // [KG][M][TN]
+#pragma unroll
+    for (int i = 0; i < M; ++i)
+      *reinterpret_cast<float4 *>(&red[(kg * M + i) * TN + colg * 128 + lane * 4]) =
+          make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    asm volatile("bar.sync 1, %0;" ::"n"(GT_CONSUMERS * 32) : "memory");
+    if (cluster_splits <= 1) {
+      if (abort_flag) return;
+      for (int e = threadIdx.x; e < M * (TN / 4); e += GT_CONSUMERS * 32) {
+        const int i = e / (TN / 4), c4 = e - i * (TN / 4);
+        const int col = n0 + c4 * 4;
+        if (col >= n) continue;  // n % 4 == 0: a float4 is inside or outside as a whole
+        float4 v = *reinterpret_cast<const float4 *>(&red[i * TN + c4 * 4]);
+#pragma unroll
+        for (int q = 1; q < S::KG; ++q) {
+          const float4 t = *reinterpret_cast<const float4 *>(&red[(q * M + i) * TN + c4 * 4]);
+          v.x += t.x;
+          v.y += t.y;
+          v.z += t.z;
+          v.w += t.w;
+        }
+        if (partial) {
+          *reinterpret_cast<float4 *>(&partial[((long long)blockIdx.z * M + i) * n + col]) = v;
+        } else {
+          gt_finish(v, bias, residual, relu, (long long)i * n + col, col);
+          *reinterpret_cast<float4 *>(&out[(long long)i * n + col]) = v;
+        }
+      }
+      return;
+    }
+    // Cluster mode: this CTA's sums over its k range, k groups joined, to loc[M][TN] behind red.
+    float *loc = red + S::KG * M * TN;
+    for (int e = threadIdx.x; e < M * (TN / 4); e += GT_CONSUMERS * 32) {
+      float4 v = *reinterpret_cast<const float4 *>(&red[e * 4]);
+#pragma unroll
+      for (int q = 1; q < S::KG; ++q) {
+        const float4 t = *reinterpret_cast<const float4 *>(&red[q * M * TN + e * 4]);
+        v.x += t.x;
+        v.y += t.y;
+        v.z += t.z;
+        v.w += t.w;
+      }
+      *reinterpret_cast<float4 *>(&loc[e * 4]) = v;
+    }
+  }
+  __syncwarp();
+  // The CTAs that share a column tile (one per k range) form a cluster. After a barrier over the
+  // whole cluster every CTA reads, for its share of the tile's elements, the sums of all ranks
+  // from their shared memory in rank order, and finishes and stores those elements.
+  cluster_sync_all();
+  if (wid < GT_CONSUMERS && !abort_flag) {
+    const float *loc = reinterpret_cast<const float *>(gt_smem) + S::KG * M * TN;
+    const unsigned loc_addr = smem_u32(loc);
+    const int rank = blockIdx.z;
+    for (int e = threadIdx.x; e * cluster_splits + rank < M * (TN / 4); e += GT_CONSUMERS * 32) {
+      const int u = e * cluster_splits + rank;  // float4 unit of the tile
+      const int i = u / (TN / 4), c4 = u - i * (TN / 4);
+      const int col = n0 + c4 * 4;
+      if (col >= n) continue;
+      float4 v = ld_cluster_f4(cluster_map(loc_addr + u * 16, 0));
+      for (int q = 1; q < cluster_splits; ++q) {
+        const float4 t = ld_cluster_f4(cluster_map(loc_addr + u * 16, (unsigned)q));
+        v.x += t.x;
+        v.y += t.y;
+        v.z += t.z;
+        v.w += t.w;
+      }
+      gt_finish(v, bias, residual, relu, (long long)i * n + col, col);
+      *reinterpret_cast<float4 *>(&out[(long long)i * n + col]) = v;
+    }
+  }
+  cluster_sync_all();  // no CTA leaves while a peer may still read its sums
+}
+
+struct GtPlan {
+  int tn = 0;          // 0: the streaming kernel does not take the shape
+  int splits = 1;
+  int k_per_split = 0;
+  bool cluster = false;  // the k ranges of a tile join through a thread-block cluster (no second kernel)
+};
+
+int g_force_tn = 0, g_force_splits = 0, g_force_scratch = 0;  // measurement aid (litnice_b200_gemv_time)
+
+GtPlan gt_plan(int n, int k) {
+  GtPlan p;
+  if (n % 4 != 0 || k % 4 != 0 || n < 128 || k < 32 || !tc_runtime_available()) return p;
+  // 128-column tiles when they alone give every SM a CTA, or when even eight k ranges per wide
+  // tile would leave SMs idle; else the wider tile (1 KB row pieces).
+  const int wide_tiles = (n + 255) / 256;
+  p.tn = ((n + 127) / 128 >= 148 || n < 256 || wide_tiles * 8 < 148) ? 128 : 256;
+  if (g_force_tn == 128 || (g_force_tn == 256 && n >= 256)) p.tn = g_force_tn;
+  const int rows = p.tn == 128 ? 32 : 16;
+  const int tiles = (n + p.tn - 1) / p.tn;
+  int splits = tiles >= 148 ? 1 : (2 * 148 + tiles - 1) / tiles;
+  const int max_splits = k / (2 * rows) > 0 ? k / (2 * rows) : 1;  // at least two stages per CTA
+  if (splits > max_splits) splits = max_splits;
+  // up to eight ranges join inside a cluster; more only pay on a matrix large enough to hide the
+  // second kernel that then adds them
+  if (splits > 8 && (long long)k * n * 4 < (8ll << 20)) splits = 8;
+  if (g_force_splits > 0) splits = g_force_splits;
+  int per = ((k + splits - 1) / splits + rows - 1) / rows * rows;  // whole stages: only the end of k is ragged
+  p.splits = (k + per - 1) / per;
+  p.k_per_split = per;
+  p.cluster = p.splits >= 2 && p.splits <= 8 && !g_force_scratch;
+  return p;
+}
+
+bool gt_aligned(const void *a, const void *b, const void *c, const void *d) {
+  return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+           reinterpret_cast<uintptr_t>(d)) & 15) == 0;
+}
+
+template <int M, int TN>
+void launch_gt(const CUtensorMap &map, const CUtensorMap &xmap, int k, int n, const GtPlan &p, const float *bias,
+               float *out, float *partial, DevErr *err, const float *residual, int relu, cudaStream_t st) {
+  using S = GtShape<M, TN>;
+  static std::mutex mu;
+  static bool configured[64] = {};
+  int dev = 0;
+  LB_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 64 || !configured[dev]) {
+      LB_CUDA(cudaFuncSetAttribute(gemv_tma_kernel<M, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+      if (dev < 64) configured[dev] = true;
+    }
+  }
+  dim3 grid((n + TN - 1) / TN, 1, p.splits);
+  launch_pdl_cluster(gemv_tma_kernel<M, TN>, grid, dim3((GT_CONSUMERS + 1) * 32), (size_t)S::TOTAL, st, g_pdl_enabled,
+                     p.cluster ? (unsigned)p.splits : 1u, map, xmap, k, n, p.k_per_split, bias, out, partial, err,
+                     residual, relu, p.cluster ? p.splits : 1);
+}
+
+template <int M>
+int launch_gt_m(const float *x, const float *w, int k, int n, const GtPlan &p, const float *bias, float *out,
+                float *scratch, DevErr *err, const float *residual, int relu, cudaStream_t st) {
+  CUtensorMap map, xmap;
+  const unsigned rows = p.tn == 128 ? 32u : 16u;
+  tc_make_map_plain(&map, w, (unsigned long long)k, (unsigned long long)n, rows, (unsigned)p.tn);
+  tc_make_map_plain(&xmap, x, (unsigned long long)M, (unsigned long long)k, (unsigned)M, rows);
+  float *partial = (p.splits > 1 && !p.cluster) ? scratch : nullptr;
+  if (p.tn == 128) launch_gt<M, 128>(map, xmap, k, n, p, bias, out, partial, err, residual, relu, st);
+  else launch_gt<M, 256>(map, xmap, k, n, p, bias, out, partial, err, residual, relu, st);
+  if (partial != nullptr) {
+    const long long total = (long long)M * n;
+    launch_pdl(gemv_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, g_pdl_enabled,
+               (const float *)partial, p.splits, M, n, bias, out, residual, relu);
+    return 2;
+  }
+  return 1;
+}
+
+int pad_m(int m) { return m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8)); }
+
+}  // namespace
+
+size_t gemv_scratch_floats(int m, int n, int k) {
+  const GtPlan p = gt_plan(n, k);
+  // sized for the scratch form even where the cluster form is planned (the measurement aid can force it)
+  const size_t streaming = (p.tn != 0 && p.splits > 1) ? (size_t)p.splits * pad_m(m) * n : 0;
+  const size_t plain = plain_scratch_floats(m, n, k);
+  return streaming > plain ? streaming : plain;
+}
+
+int launch_gemv(const float *x, int m, const float *w, int k, int n, const float *bias,
+                float *out, float *scratch, cudaStream_t st, DevErr *err, const float *residual, int relu) {
+  if (m > 8) throw std::invalid_argument("launch_gemv: m must be <= 8");
+  const GtPlan p = gt_plan(n, k);
+  const bool needs_scratch = p.splits > 1 && !p.cluster;
+  if (p.tn != 0 && gt_aligned(x, w, out, bias) && gt_aligned(residual, x, x, x) &&
+      (!needs_scratch || (scratch != nullptr && gt_aligned(scratch, x, x, x)))) {
+    switch (pad_m(m)) {
+      case 1: return launch_gt_m<1>(x, w, k, n, p, bias, out, scratch, err, residual, relu, st);
+      case 2: return launch_gt_m<2>(x, w, k, n, p, bias, out, scratch, err, residual, relu, st);
+      case 4: return launch_gt_m<4>(x, w, k, n, p, bias, out, scratch, err, residual, relu, st);
+      default: return launch_gt_m<8>(x, w, k, n, p, bias, out, scratch, err, residual, relu, st);
+    }
+  }
+  return launch_gemv_plain(x, m, w, k, n, bias, out, scratch, st, residual, relu);
 }
 
 // ---------------------------------------------------------------------------
@@ -213,7 +557,7 @@ extern "C" int litnice_b200_gemv_noalloc(const float *x, int32_t m, const float 
     std::fprintf(stderr, "litnice_b200_gemv_noalloc: m must be 1, 2, 4 or 8 (got %d)\n", m);
     return LITNICE_B200_EINVAL;
   }
-  const size_t need = gemv_scratch_floats(m, n, k);
+  const size_t need = plain_scratch_floats(m, n, k);
   if (need > NOALLOC_MAX_FLOATS) {
     std::fprintf(stderr,
                  "litnice_b200_gemv_noalloc: m=%d k=%d n=%d needs %zu floats of partial sums, the built-in "
@@ -229,10 +573,150 @@ extern "C" int litnice_b200_gemv_noalloc(const float *x, int32_t m, const float 
   try {
     // Every partial sum the reduction reads is written by the first kernel of
     // the same call, so nothing left over from an earlier call is ever used.
-    launch_gemv(x, m, w, k, n, bias, out, partials, static_cast<cudaStream_t>(stream));
+    launch_gemv_plain(x, m, w, k, n, bias, out, partials, static_cast<cudaStream_t>(stream));
   } catch (const std::exception &ex) {
     std::fprintf(stderr, "litnice_b200_gemv_noalloc: %s\n", ex.what());
     return LITNICE_B200_ECUDA;
   }
   return LITNICE_B200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Diagnostics (not part of the loop): the few-row product on host buffers, and
+// its device time with a cold L2.
+// ---------------------------------------------------------------------------
+
+extern "C" int litnice_b200_gemv_host(const float *x, int32_t m, const float *w, int32_t k, int32_t n,
+                                      const float *bias, const float *residual, int32_t relu, float *out) {
+  using namespace lb;
+  if (x == nullptr || w == nullptr || out == nullptr || m <= 0 || m > 8 || k <= 0 || n <= 0) return LITNICE_B200_EINVAL;
+  std::vector<void *> owned;
+  DevErr *err_host = nullptr;
+  int rc = LITNICE_B200_OK;
+  try {
+    auto dev_alloc = [&](size_t bytes) {
+      void *p = nullptr;
+      if (cudaMalloc(&p, bytes) != cudaSuccess) throw std::bad_alloc();
+      owned.push_back(p);
+      return static_cast<float *>(p);
+    };
+    LB_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&err_host), sizeof(DevErr), cudaHostAllocMapped));
+    err_host->code = DEVERR_NONE;
+    err_host->detail = 0;
+    DevErr *err_dev = nullptr;
+    LB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&err_dev), err_host, 0));
+    const int mp = pad_m(m);
+    float *dx = dev_alloc((size_t)mp * k * 4), *dw = dev_alloc((size_t)k * n * 4), *dout = dev_alloc((size_t)mp * n * 4);
+    float *db = bias ? dev_alloc((size_t)n * 4) : nullptr;
+    float *dr = residual ? dev_alloc((size_t)mp * n * 4) : nullptr;
+    const size_t sf = gemv_scratch_floats(m, n, k);
+    float *scr = sf ? dev_alloc(sf * 4) : nullptr;
+    LB_CUDA(cudaMemset(dx, 0, (size_t)mp * k * 4));
+    LB_CUDA(cudaMemcpy(dx, x, (size_t)m * k * 4, cudaMemcpyHostToDevice));
+    LB_CUDA(cudaMemcpy(dw, w, (size_t)k * n * 4, cudaMemcpyHostToDevice));
+    if (db) LB_CUDA(cudaMemcpy(db, bias, (size_t)n * 4, cudaMemcpyHostToDevice));
+    if (dr) {
+      LB_CUDA(cudaMemset(dr, 0, (size_t)mp * n * 4));
+      LB_CUDA(cudaMemcpy(dr, residual, (size_t)m * n * 4, cudaMemcpyHostToDevice));
+    }
+    launch_gemv(dx, m, dw, k, n, db, dout, scr, nullptr, err_dev, dr, relu);
+    LB_CUDA(cudaDeviceSynchronize());
+    LB_CUDA(cudaMemcpy(out, dout, (size_t)m * n * 4, cudaMemcpyDeviceToHost));
+    if (err_host->code != DEVERR_NONE) rc = LITNICE_B200_EDEVICE;
+  } catch (const std::bad_alloc &) {
+    rc = LITNICE_B200_ENOMEM;
+  } catch (const std::exception &e) {
+    std::fprintf(stderr, "litnice_b200_gemv_host: %s\n", e.what());
+    rc = LITNICE_B200_ECUDA;
+  }
+  for (void *p : owned) cudaFree(p);
+  if (err_host) cudaFreeHost(err_host);
+  return rc;
+}
+
+extern "C" int litnice_b200_gemv_time(int32_t m, int32_t k, int32_t n, int32_t repeats, int32_t cold_l2,
+                                      int32_t force_tn, int32_t force_splits, double *avg_us, int32_t *launches) {
+  using namespace lb;
+  if (m <= 0 || m > 8 || k <= 0 || n <= 0 || repeats <= 0 || avg_us == nullptr) return LITNICE_B200_EINVAL;
+  std::vector<void *> owned;
+  cudaStream_t st = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  int rc = LITNICE_B200_OK;
+  g_force_tn = force_tn;
+  g_force_splits = force_splits < 0 ? -force_splits : force_splits;  // negative: through scratch, not a cluster
+  g_force_scratch = force_splits < 0 ? 1 : 0;
+  try {
+    auto dev_alloc = [&](size_t bytes) {
+      void *p = nullptr;
+      if (cudaMalloc(&p, bytes) != cudaSuccess) throw std::bad_alloc();
+      owned.push_back(p);
+      return static_cast<float *>(p);
+    };
+    LB_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    LB_CUDA(cudaEventCreate(&e0));
+    LB_CUDA(cudaEventCreate(&e1));
+    const int mp = pad_m(m);
+    float *dx = dev_alloc((size_t)mp * k * 4), *dw = dev_alloc((size_t)k * n * 4), *dout = dev_alloc((size_t)mp * n * 4);
+    const size_t sf = gemv_scratch_floats(m, n, k);
+    float *scr = sf ? dev_alloc(sf * 4) : nullptr;
+    const size_t flush_bytes = (size_t)256 << 20;  // twice the 126 MB L2
+    float *flush = cold_l2 == 1 ? dev_alloc(flush_bytes) : nullptr;
+    LB_CUDA(cudaMemsetAsync(dx, 0x3c, (size_t)mp * k * 4, st));  // 0x3c3c3c3c = 0.0115f
+    LB_CUDA(cudaMemsetAsync(dw, 0x3c, (size_t)k * n * 4, st));
+    double total_ms = 0;
+    int count = 0;
+    if (cold_l2 == 2) {
+      // Back-to-back launches over a ring of weight copies that together exceed three times the
+      // L2, so every launch reads its matrix from HBM; one event pair around the whole run.
+      const size_t wbytes = (size_t)k * n * 4;
+      int copies = (int)(((size_t)400 << 20) / wbytes) + 2;
+      std::vector<float *> ring{dw};
+      for (int c = 1; c < copies; ++c) {
+        ring.push_back(dev_alloc(wbytes));
+        LB_CUDA(cudaMemsetAsync(ring.back(), 0x3c, wbytes, st));
+      }
+      for (int r = 0; r < copies; ++r) launch_gemv(dx, m, ring[r % copies], k, n, nullptr, dout, scr, st, nullptr);
+      LB_CUDA(cudaEventRecord(e0, st));
+      int nl = 0;
+      for (int r = 0; r < repeats; ++r) nl = launch_gemv(dx, m, ring[r % copies], k, n, nullptr, dout, scr, st, nullptr);
+      LB_CUDA(cudaEventRecord(e1, st));
+      LB_CUDA(cudaStreamSynchronize(st));
+      if (launches) *launches = nl;
+      float ms = 0.f;
+      LB_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+      total_ms = ms;
+      count = repeats;
+    } else {
+      for (int r = 0; r < repeats + 3; ++r) {
+        if (flush) LB_CUDA(cudaMemsetAsync(flush, r & 0xff, flush_bytes, st));
+        LB_CUDA(cudaEventRecord(e0, st));
+        const int nl = launch_gemv(dx, m, dw, k, n, nullptr, dout, scr, st, nullptr);
+        LB_CUDA(cudaEventRecord(e1, st));
+        LB_CUDA(cudaStreamSynchronize(st));
+        if (launches) *launches = nl;
+        if (r < 3) continue;  // warm-up
+        float ms = 0.f;
+        LB_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        total_ms += ms;
+        ++count;
+      }
+    }
+    *avg_us = 1e3 * total_ms / count;
+  } catch (const std::bad_alloc &) {
+    rc = LITNICE_B200_ENOMEM;
+  } catch (const std::exception &e) {
+    std::fprintf(stderr, "litnice_b200_gemv_time: %s\n", e.what());
+    rc = LITNICE_B200_ECUDA;
+  }
+  g_force_tn = 0;
+  g_force_splits = 0;
+  g_force_scratch = 0;
+  if (st) {
+    cudaStreamSynchronize(st);
+    cudaStreamDestroy(st);
+  }
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  for (void *p : owned) cudaFree(p);
+  return rc;
 }

@@ -200,8 +200,9 @@ struct litnice_b200_session {
 
   // per-class event timing (profile_step only)
   bool profiling = false;
+  bool stamping = false;  // device-clock stamps instead of events: launches overlap as in the loop
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> gemm_ev, attn_ev;
-  double gemm_flops = 0;
+  double gemm_flops = 0, stamped_gemm_flops = 0;
 
   std::string error;
 };
@@ -432,8 +433,10 @@ void projection_f16(litnice_b200_session *s, PairKind pk, long long rows, int k,
   const TcPairF16 &a = pk == PAIR_LN ? s->pair_ln : pk == PAIR_CTX ? s->pair_ctx : s->pair_h;
   const TcPlan plan = tc_plan((int)rows, n, k, tw->has64, tw->has128, tw->has256, TC_F16_SLOT);
   TcEpilogue e = ep;
-  if (s->profiling && s->gemm_timeline && s->gemm_timeline_used < litnice_b200_session::kTimelineSlots)
+  if (s->stamping && s->gemm_timeline && s->gemm_timeline_used < litnice_b200_session::kTimelineSlots) {
     e.timeline = s->gemm_timeline + 32 * s->gemm_timeline_used++;
+    s->stamped_gemm_flops += 2.0 * (double)rows * n * k;
+  }
   launch_gemm_tc_f16(s->pair_map[pk], a.inv_scale, plan.bn == 256 ? tw->f256 : plan.bn == 128 ? tw->f128 : tw->f64,
                      tw->h_inv_scale, (int)rows, n, k, plan, e, s->tc_scratch, s->tc_counters, s->err_dev, s->st);
 }
@@ -487,9 +490,9 @@ void enqueue_body(litnice_b200_session *s, int B, int sl, const LoopState *dstat
         ClassTimer t(s, &s->attn_ev);
         launch_attention_tc(s->qk_map, s->vt_map, nullptr, nullptr, B, sl, d.n_heads, D, s->attn_scratch,
                             s->attn_counters, dstate, s->err_dev, s->st,
-                            (s->profiling && s->attn_timeline &&
+                            (s->stamping && s->attn_timeline &&
                              s->attn_timeline_used < litnice_b200_session::kTimelineSlots)
-                                ? s->attn_timeline + 16 * s->attn_timeline_used++
+                                ? s->attn_timeline + 32 * s->attn_timeline_used++
                                 : nullptr,
                             &s->pair_ctx);
         ++s->launches;
@@ -527,9 +530,9 @@ void enqueue_body(litnice_b200_session *s, int B, int sl, const LoopState *dstat
       ClassTimer t(s, &s->attn_ev);
       launch_attention_tc(s->qk_map, s->vt_map, s->ctx, s->ctx_lo, B, sl, d.n_heads, D, s->attn_scratch,
                           s->attn_counters, dstate, s->err_dev, s->st,
-                          (s->profiling && s->attn_timeline &&
+                          (s->stamping && s->attn_timeline &&
                            s->attn_timeline_used < litnice_b200_session::kTimelineSlots)
-                              ? s->attn_timeline + 16 * s->attn_timeline_used++
+                              ? s->attn_timeline + 32 * s->attn_timeline_used++
                               : nullptr);
       ++s->launches;
     } else {
@@ -565,9 +568,8 @@ void enqueue_head_last(litnice_b200_session *s, int B, int sl, const LoopState *
                         head_tc ? s->xl_lo : nullptr, s->st);
   ++s->launches;
   if (B <= 8) {
-    launch_gemv(s->xl, B, P(s, s->lay.lm_head), d.d_model, d.vocab_size, nullptr, s->logits,
-                s->gemv_scratch, s->st);
-    s->launches += gemv_scratch_floats(B, d.vocab_size, d.d_model) > 0 ? 2 : 1;
+    s->launches += launch_gemv(s->xl, B, P(s, s->lay.lm_head), d.d_model, d.vocab_size, nullptr, s->logits,
+                               s->gemv_scratch, s->st, s->err_dev);
   } else {
     projection(s, A_XL, B, d.d_model, P(s, s->lay.lm_head), head_tc ? &s->tc_head : nullptr, d.vocab_size,
                nullptr, nullptr, 0, s->logits, nullptr);
@@ -697,8 +699,22 @@ void upload_ids(litnice_b200_session *s, const int32_t *ids, int B, int len) {
 
 extern "C" {
 
+static int session_create_impl(const litnice_b200_dims *dims, int32_t max_streams, int32_t device_or_negative,
+                               litnice_b200_session **out);
+
 int litnice_b200_session_create(const litnice_b200_dims *dims, int32_t max_streams,
                                 litnice_b200_session **out) {
+  return session_create_impl(dims, max_streams, -1, out);
+}
+
+int litnice_b200_session_create_on(const litnice_b200_dims *dims, int32_t max_streams, int32_t device,
+                                   litnice_b200_session **out) {
+  if (device < 0) return LITNICE_B200_EINVAL;
+  return session_create_impl(dims, max_streams, device, out);
+}
+
+static int session_create_impl(const litnice_b200_dims *dims, int32_t max_streams, int32_t device_or_negative,
+                               litnice_b200_session **out) {
   if (out == nullptr) return LITNICE_B200_EINVAL;
   *out = nullptr;
   if (dims == nullptr || max_streams <= 0) return LITNICE_B200_EINVAL;
@@ -720,7 +736,8 @@ int litnice_b200_session_create(const litnice_b200_dims *dims, int32_t max_strea
   }
   int dev = 0;
   cudaGetDevice(&dev);
-  if (const char *env = std::getenv("LITNICE_B200_DEVICE")) dev = std::atoi(env);
+  if (device_or_negative >= 0) dev = device_or_negative;
+  else if (const char *env = std::getenv("LITNICE_B200_DEVICE")) dev = std::atoi(env);
   if (dev < 0 || dev >= count) {
     delete s;
     return LITNICE_B200_EINVAL;
@@ -884,15 +901,31 @@ int litnice_b200_load_checkpoint(litnice_b200_session *s, const char *path) {
       hd.alignment_bytes != d.alignment_bytes || hd.data_bytes != s->lay.total ||
       hd.adam_bytes != 2 * s->lay.total)
     return fail(s, LITNICE_B200_EIO, "incompatible checkpoint: model dimensions or arena sizes differ");
-  std::vector<char> buf(s->lay.total);
-  in.read(buf.data(), (std::streamsize)buf.size());
-  if (in.gcount() != (std::streamsize)buf.size())
-    return fail(s, LITNICE_B200_EIO, "could not read parameter arena payload");
-  // checkpoint.cpp:176-205 rejects non-finite parameters
-  const float *f = reinterpret_cast<const float *>(buf.data());
-  for (size_t i = 0; i < buf.size() / 4; ++i)
-    if (!std::isfinite(f[i])) return fail(s, LITNICE_B200_EIO, "parameter arena holds a non-finite value");
-  return litnice_b200_load_params(s, buf.data(), buf.size());
+  in.close();
+  // The file must hold the whole parameter arena behind the header (a short file is refused
+  // before anything is copied), then the arena streams to the device in pieces.
+  {
+    std::ifstream size_probe(path, std::ios::binary | std::ios::ate);
+    if (!size_probe || (uint64_t)size_probe.tellg() < sizeof(Header) + (uint64_t)s->lay.total)
+      return fail(s, LITNICE_B200_EIO, "could not read parameter arena payload");
+  }
+  return guarded(s, [&]() {
+    s->params_loaded = false;
+    try {
+      file_to_device(path, sizeof(Header), s->lay.total, s->params, s->st, true);
+    } catch (const std::domain_error &) {
+      // checkpoint.cpp:176-205 rejects non-finite parameters
+      return fail(s, LITNICE_B200_EIO, "parameter arena holds a non-finite value");
+    } catch (const CudaError &) {
+      throw;
+    } catch (const std::runtime_error &e) {
+      return fail(s, LITNICE_B200_EIO, std::string("could not read parameter arena payload: ") + e.what());
+    }
+    if (s->tc) prepare_tc_weights(s);
+    LB_CUDA(cudaStreamSynchronize(s->st));
+    s->params_loaded = true;
+    return LITNICE_B200_OK;
+  });
 }
 
 int litnice_b200_upload_prompts(litnice_b200_session *s, const int32_t *prompts, int32_t n_streams,
@@ -972,14 +1005,20 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
     }
     if (s->keep_logits) {
       const long long need = (long long)(s->cur_tokens + steps) * B * V;
+      if (s->cur_tokens == 0) s->step_logits_count = 0;
       if (need > s->step_logits_cap) {
-        if (s->step_logits) cudaFree(s->step_logits);
-        s->step_logits = nullptr;
-        if (cudaMalloc(reinterpret_cast<void **>(&s->step_logits), (size_t)need * 4) != cudaSuccess)
-          throw std::bad_alloc();
+        LB_CUDA(cudaStreamSynchronize(s->st));
+        float *n = nullptr;
+        if (cudaMalloc(reinterpret_cast<void **>(&n), (size_t)need * 4) != cudaSuccess) throw std::bad_alloc();
+        if (s->step_logits) {  // a resumed run keeps the logits of the steps already taken
+          const long long have = (long long)s->cur_tokens * B * V;
+          if (have > 0 && s->step_logits_count == have)
+            LB_CUDA(cudaMemcpy(n, s->step_logits, (size_t)have * 4, cudaMemcpyDeviceToDevice));
+          cudaFree(s->step_logits);
+        }
+        s->step_logits = n;
         s->step_logits_cap = need;
       }
-      if (s->cur_tokens == 0) s->step_logits_count = 0;
     }
 
     const long long launches0 = s->launches;
@@ -1115,6 +1154,7 @@ int litnice_b200_forward(litnice_b200_session *s, const int32_t *ids, int32_t n_
     const int B = n_streams, V = s->dims.vocab_size, D = s->dims.d_model;
     const long long R = (long long)B * seq_len;
     s->stats = litnice_b200_stats{};
+    s->cur_streams = 0;  // the ids of an uploaded prompt batch are overwritten: run needs a fresh upload
     ensure_rows(s, R);
     ensure_attention_scratch(s, B, seq_len, seq_len);
     upload_ids(s, ids, B, seq_len);
@@ -1167,6 +1207,7 @@ int litnice_b200_inspect(litnice_b200_session *s, const int32_t *ids, int32_t n_
     PdlScope pdl_scope(s->pdl);
     const int B = n_streams, V = s->dims.vocab_size;
     s->stats = litnice_b200_stats{};
+    s->cur_streams = 0;  // as in forward: the uploaded prompt batch is gone
     ensure_rows(s, (long long)B * seq_len);
     ensure_attention_scratch(s, B, seq_len, seq_len);
     upload_ids(s, ids, B, seq_len);
@@ -1250,11 +1291,13 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
     s->gemm_ev.clear();
     s->attn_ev.clear();
     s->gemm_flops = 0;
-    if (s->tc_attn && s->attn_timeline == nullptr && std::getenv("LITNICE_B200_ATTN_TIMELINE") != nullptr)
+    const bool print_timelines = std::getenv("LITNICE_B200_TC_TIMELINE") != nullptr ||
+                                 std::getenv("LITNICE_B200_ATTN_TIMELINE") != nullptr;
+    if (s->tc_attn && s->attn_timeline == nullptr)
       if (cudaMalloc(reinterpret_cast<void **>(&s->attn_timeline), litnice_b200_session::kTimelineSlots * 256) !=
           cudaSuccess)
         throw std::bad_alloc();
-    if (s->gemm_timeline == nullptr && std::getenv("LITNICE_B200_TC_TIMELINE") != nullptr)
+    if (s->f16 && s->gemm_timeline == nullptr)
       if (cudaMalloc(reinterpret_cast<void **>(&s->gemm_timeline), litnice_b200_session::kTimelineSlots * 256) !=
           cudaSuccess)
         throw std::bad_alloc();
@@ -1262,15 +1305,31 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
       LB_CUDA(cudaMemsetAsync(s->gemm_timeline, 0, litnice_b200_session::kTimelineSlots * 256, s->st));
       for (int i = 0; i < litnice_b200_session::kTimelineSlots; ++i)
         LB_CUDA(cudaMemsetAsync(s->gemm_timeline + 32 * i + 8, 0xff, 8, s->st));
+      for (int i = 0; i < litnice_b200_session::kTimelineSlots; ++i)
+        LB_CUDA(cudaMemsetAsync(s->gemm_timeline + 32 * i + 14, 0xff, 8, s->st));  // earliest return of the wait
       s->gemm_timeline_used = 0;
     }
     if (s->attn_timeline) {
       LB_CUDA(cudaMemsetAsync(s->attn_timeline, 0, litnice_b200_session::kTimelineSlots * 256, s->st));
       for (int i = 0; i < litnice_b200_session::kTimelineSlots; ++i)
-        LB_CUDA(cudaMemsetAsync(s->attn_timeline + 16 * i + 8, 0xff, 8, s->st));  // earliest start: preset to max
+        LB_CUDA(cudaMemsetAsync(s->attn_timeline + 32 * i + 8, 0xff, 8, s->st));  // earliest start: preset to max
+      for (int i = 0; i < litnice_b200_session::kTimelineSlots; ++i)
+        LB_CUDA(cudaMemsetAsync(s->attn_timeline + 32 * i + 16, 0xff, 8, s->st));
       s->attn_timeline_used = 0;
     }
     enqueue_body(s, n_streams, seq_len);  // warm-up, untimed
+    // One step with device-clock stamps only: the launches overlap through programmatic
+    // dependent launch as they do in the token loop (event records between them would
+    // serialise them), and every CTA contributes to its launch's earliest start and latest end.
+    s->stamped_gemm_flops = 0;
+    s->stamping = true;
+    try {
+      enqueue_body(s, n_streams, seq_len);
+    } catch (...) {
+      s->stamping = false;
+      throw;
+    }
+    s->stamping = false;
     s->profiling = true;
     try {
       for (int r = 0; r < repeats; ++r) {
@@ -1303,10 +1362,26 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
     s->stats.gemm_flops = s->gemm_flops;
     s->gemm_ev.clear();
     s->attn_ev.clear();
+    s->stats.gemm_span_ms = s->stats.attn_span_ms = s->stats.step_span_ms = 0;
+    s->stats.gemm_span_launches = s->stats.attn_span_launches = 0;
+    s->stats.gemm_span_flops = s->stamped_gemm_flops;
+    unsigned long long first_start = ~0ull, last_end = 0;
     if (s->gemm_timeline) {
       std::vector<unsigned long long> t(32 * (size_t)s->gemm_timeline_used);
       if (!t.empty()) LB_CUDA(cudaMemcpy(t.data(), s->gemm_timeline, t.size() * 8, cudaMemcpyDeviceToHost));
       for (int i = 0; i < s->gemm_timeline_used; ++i) {
+        const unsigned long long *u = t.data() + 32 * i;
+        // a launch's work runs from the moment its predecessor has completed (the earliest return
+        // of its wait; its CTAs are resident and set up before that) to its last CTA's end
+        const unsigned long long begin = u[14] != ~0ull && u[14] > u[8] ? u[14] : u[8];
+        if (u[9] > begin) {
+          s->stats.gemm_span_ms += 1e-6 * (double)(u[9] - begin);
+          ++s->stats.gemm_span_launches;
+          first_start = begin < first_start ? begin : first_start;
+          last_end = u[9] > last_end ? u[9] : last_end;
+        }
+      }
+      for (int i = 0; print_timelines && i < s->gemm_timeline_used; ++i) {
         const unsigned long long *u = t.data() + 32 * i;
         std::fprintf(stderr,
                      "projection launch %d (ns from CTA start): setup %lld, loads issued %lld, first stage %lld, mma "
@@ -1320,10 +1395,21 @@ int litnice_b200_profile_step(litnice_b200_session *s, int32_t n_streams, int32_
     }
     if (s->attn_timeline) {
       // per profiled launch: stamps of CTA (0,0,0) and the span from the first CTA's start to the last CTA's end
-      std::vector<unsigned long long> t(16 * (size_t)s->attn_timeline_used);
+      std::vector<unsigned long long> t(32 * (size_t)s->attn_timeline_used);
       if (!t.empty()) LB_CUDA(cudaMemcpy(t.data(), s->attn_timeline, t.size() * 8, cudaMemcpyDeviceToHost));
       for (int i = 0; i < s->attn_timeline_used; ++i) {
-        const unsigned long long *u = t.data() + 16 * i;
+        const unsigned long long *u = t.data() + 32 * i;
+        const unsigned long long begin = u[16] != ~0ull && u[16] > u[8] ? u[16] : u[8];
+        if (u[9] > begin) {
+          s->stats.attn_span_ms += 1e-6 * (double)(u[9] - begin);
+          ++s->stats.attn_span_launches;
+          first_start = begin < first_start ? begin : first_start;
+          last_end = u[9] > last_end ? u[9] : last_end;
+        }
+      }
+      if (last_end > first_start) s->stats.step_span_ms = 1e-6 * (double)(last_end - first_start);
+      for (int i = 0; print_timelines && i < s->attn_timeline_used; ++i) {
+        const unsigned long long *u = t.data() + 32 * i;
         std::fprintf(stderr,
                      "attention launch %d (ns from CTA start): setup %lld, Q+K landed %lld, S ready %lld, P stored %lld, "
                      "O ready %lld, partial merged %lld, end %lld; CTA start after first %lld; last CTA start %lld; whole grid %lld; last to end: blockIdx.x %d merge %d; split path: partial stored %lld, fenced %lld, counted %lld, merge loaded %lld\n",

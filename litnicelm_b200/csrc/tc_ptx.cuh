@@ -42,22 +42,30 @@ __device__ __forceinline__ unsigned mbar_try_wait(unsigned bar, unsigned parity)
 // is a real function, not inlined at the several dozen wait sites of a kernel:
 // these kernels run a few warps per SM and every kilobyte of code they do not
 // execute still costs instruction-cache space.
-static __device__ __noinline__ bool mbar_wait_slow(unsigned bar, unsigned parity, volatile int *abort_flag, DevErr *err,
-                                            int where) {
+// err may be null (a caller without an error word): the wait still ends and
+// the abort flag still tells the other roles.
+static __device__ __noinline__ bool mbar_wait_limit(unsigned bar, unsigned parity, volatile int *abort_flag, DevErr *err,
+                                                    int where, unsigned long long limit_ns) {
   const unsigned long long t0 = global_timer();
   unsigned spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0) {
       if (*abort_flag) return false;
-      if (global_timer() - t0 > WAIT_LIMIT_NS) {
+      if (global_timer() - t0 > limit_ns) {
         *abort_flag = 1;
-        err->code = DEVERR_WAIT_TIMEOUT;
-        err->detail = where;
+        if (err != nullptr) {
+          err->code = DEVERR_WAIT_TIMEOUT;
+          err->detail = where;
+        }
         return false;
       }
     }
   }
+}
+static __device__ __forceinline__ bool mbar_wait_slow(unsigned bar, unsigned parity, volatile int *abort_flag,
+                                                      DevErr *err, int where) {
+  return mbar_wait_limit(bar, parity, abort_flag, err, where, WAIT_LIMIT_NS);
 }
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, DevErr *err,
                                           int where) {
@@ -170,6 +178,15 @@ __device__ __forceinline__ void st_cluster_f4(unsigned cluster_addr, float4 v) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(v.x), "f"(v.y), "f"(v.z),
                "f"(v.w)
                : "memory");
+}
+
+__device__ __forceinline__ float4 ld_cluster_f4(unsigned cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
 }
 
 // A operand read from tensor memory (lane = row, one column per k element).

@@ -202,7 +202,8 @@ def write_yaml(path: str, d: ModelDims, *, backend_library: str, checkpoint: str
                dataset_bin: str = "unused.bin", tokenizer_type: str = "character",
                artifacts_dir: str = "", attention: str = "reference", ffn: str = "reference",
                prompt: str = "", max_new: int = 64, temp: float = 0.0, top_k: int = 0,
-               top_p: float = 1.0, seed: int = 12345) -> None:
+               top_p: float = 1.0, seed: int = 12345, corpus: str = "unused.txt",
+               train_seq_len: int = 4, batch_size: int = 2) -> None:
     """A litnicelm YAML holding every key the loader requires
     (config_mapper.cpp:124-189) and none it does not know (:713-716)."""
     text = f"""conf:
@@ -220,7 +221,7 @@ backend:
 tokenizer:
   type: "{tokenizer_type}"
   target_vocab_size: {d.vocab}
-  training_corpus: "unused.txt"
+  training_corpus: "{corpus}"
   inter_file_boundary: "\\n"
   artifacts_dir: "{artifacts_dir}"
   bpe_vocab_file: ""
@@ -230,7 +231,7 @@ tokenizer:
   run_validation: false
 
 tokenization:
-  input_corpus: "unused.txt"
+  input_corpus: "{corpus}"
   output_binary: "{dataset_bin}"
   chunk_size_mb: 16
 
@@ -260,9 +261,9 @@ training:
   num_epochs_dry_run: 1
   save_interval_epochs: 1
   grad_clip: 1.0
-  train_seq_len: 4
-  window_stride: 4
-  batch_size: 2
+  train_seq_len: {train_seq_len}
+  window_stride: {train_seq_len}
+  batch_size: {batch_size}
   target_loss: -1.0
   min_delta: 0.0
   patience_epochs: 0

@@ -116,13 +116,16 @@ class BackendApiV1(C.Structure):
 
 API_ENTRY_NAMES = [name for name, _ in _API_FIELDS[1:]]
 
+# What a host of the native loop binds (the diagnostics of the header's third section are
+# left out on purpose).
 NATIVE_SYMBOLS = [
-    "litnice_b200_session_create", "litnice_b200_session_destroy", "litnice_b200_last_error",
+    "litnice_b200_session_create", "litnice_b200_session_create_on", "litnice_b200_session_destroy",
+    "litnice_b200_last_error",
     "litnice_b200_load_params", "litnice_b200_load_checkpoint", "litnice_b200_generate",
     "litnice_b200_upload_prompts", "litnice_b200_run", "litnice_b200_download_tokens",
     "litnice_b200_keep_step_logits", "litnice_b200_read_step_logits", "litnice_b200_forward",
     "litnice_b200_inspect", "litnice_b200_sample_logits", "litnice_b200_get_stats",
-    "litnice_b200_profile_step",
+    "litnice_b200_gemv_noalloc",
 ]
 
 
@@ -162,6 +165,54 @@ def projection_time(m: int, k: int, n: int, repeats: int = 20, engine: int = 1,
     if rc != 0:
         raise RuntimeError(f"litnice_b200_projection_time failed with status {rc}")
     return us.value
+
+
+def gemv_host(x: np.ndarray, w: np.ndarray, bias: Optional[np.ndarray] = None,
+              residual: Optional[np.ndarray] = None, relu: bool = False,
+              lib: Optional[C.CDLL] = None) -> np.ndarray:
+    """out[m, n] = x[m, k] . W[k, n] (+ bias) (+ residual) (ReLU) for m <= 8 on the few-row
+    kernels of the output head (litnice_b200_gemv_host: host buffers in, host buffer out)."""
+    lib = lib or load_library()
+    f32p = C.POINTER(C.c_float)
+    fn = lib.litnice_b200_gemv_host
+    fn.argtypes = [f32p, C.c_int32, f32p, C.c_int32, C.c_int32, f32p, f32p, C.c_int32, f32p]
+    fn.restype = C.c_int
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    m, k = x.shape
+    n = w.shape[1]
+    out = np.empty((m, n), np.float32)
+    b = None
+    if bias is not None:
+        bias = np.ascontiguousarray(bias, np.float32).ravel()
+        b = bias.ctypes.data_as(f32p)
+    r = None
+    if residual is not None:
+        residual = np.ascontiguousarray(residual, np.float32)
+        r = residual.ctypes.data_as(f32p)
+    rc = fn(x.ctypes.data_as(f32p), m, w.ctypes.data_as(f32p), k, n, b, r, 1 if relu else 0,
+            out.ctypes.data_as(f32p))
+    if rc != 0:
+        raise RuntimeError(f"litnice_b200_gemv_host failed with status {rc}")
+    return out
+
+
+def gemv_time(m: int, k: int, n: int, repeats: int = 50, cold_l2: int = 2, force_tn: int = 0,
+              force_splits: int = 0, lib: Optional[C.CDLL] = None) -> Tuple[float, int]:
+    """(mean device microseconds, kernels per call) of the few-row product. cold_l2 = 2:
+    `repeats` calls back to back between one pair of CUDA events, each on the next of a
+    ring of weight copies larger than three times the L2 (every call reads HBM);
+    1: events around each call, a 256 MB buffer written before it; 0: the same matrix
+    every call (L2-resident when it fits)."""
+    lib = lib or load_library()
+    fn = lib.litnice_b200_gemv_time
+    fn.argtypes = [C.c_int32] * 7 + [C.POINTER(C.c_double), C.POINTER(C.c_int32)]
+    fn.restype = C.c_int
+    us, nl = C.c_double(0), C.c_int32(0)
+    rc = fn(m, k, n, repeats, int(cold_l2), force_tn, force_splits, C.byref(us), C.byref(nl))
+    if rc != 0:
+        raise RuntimeError(f"litnice_b200_gemv_time failed with status {rc}")
+    return us.value, nl.value
 
 
 @dataclass
@@ -276,7 +327,9 @@ class B200Stats(C.Structure):
     _fields_ = [("device_ms", C.c_double), ("kernel_launches", C.c_int64), ("tokens", C.c_int64),
                 ("h2d_bytes", C.c_int64), ("d2h_bytes", C.c_int64), ("gemm_ms", C.c_double),
                 ("gemm_launches", C.c_int64), ("gemm_flops", C.c_double), ("attn_ms", C.c_double),
-                ("attn_launches", C.c_int64)]
+                ("attn_launches", C.c_int64), ("gemm_span_ms", C.c_double), ("gemm_span_launches", C.c_int64),
+                ("gemm_span_flops", C.c_double), ("attn_span_ms", C.c_double), ("attn_span_launches", C.c_int64),
+                ("step_span_ms", C.c_double)]
 
 
 class NativeError(RuntimeError):
@@ -287,7 +340,8 @@ class Session:
     """Native token loop: generate_text of the reference (inference.cpp:265-296)
     for n independent streams in lockstep, entirely on the GPU."""
 
-    def __init__(self, dims: ModelDims, max_streams: int = 1, lib_path: Optional[str] = None):
+    def __init__(self, dims: ModelDims, max_streams: int = 1, lib_path: Optional[str] = None,
+                 device: Optional[int] = None):
         self.lib = load_library(lib_path)
         L = self.lib
         i32p, f32p, u32p = C.POINTER(C.c_int32), C.POINTER(C.c_float), C.POINTER(C.c_uint32)
@@ -316,7 +370,12 @@ class Session:
         cd = B200Dims(dims.n_layers, dims.n_heads, dims.d_model, dims.d_ff, dims.vocab, dims.max_seq,
                       dims.alignment)
         self.h = C.c_void_p()
-        rc = L.litnice_b200_session_create(C.byref(cd), max_streams, C.byref(self.h))
+        if device is None:
+            rc = L.litnice_b200_session_create(C.byref(cd), max_streams, C.byref(self.h))
+        else:
+            L.litnice_b200_session_create_on.argtypes = [C.POINTER(B200Dims), C.c_int32, C.c_int32,
+                                                         C.POINTER(C.c_void_p)]
+            rc = L.litnice_b200_session_create_on(C.byref(cd), max_streams, device, C.byref(self.h))
         if rc != 0:
             msg = L.litnice_b200_last_error(self.h).decode() if self.h else "no session"
             if self.h:

@@ -108,3 +108,38 @@ def test_live_reference_agrees_when_built(oracle, have_ref, attention, ffn):
                                    top_p=0.9, seed=9, attention=attention, ffn=ffn)
     mine, _ = oracle.generate(d, arena, ids, 20, temp=0.9, top_k=0, top_p=0.9, seed=9)
     assert np.array_equal(toks, mine)
+
+
+# ---- fixtures of the benchmark workloads (made by the restatement, confirmed by the
+# reference where one forward is affordable; see tests/golden/make_golden.py) ----
+
+def _workload(name, key):
+    z = np.load(os.path.join(GOLDEN, name))
+    d = formats.CONFIG_DIMS[key]
+    arena = formats.make_param_arena(d, int(z["arena_seed"][0]))
+    if hashlib.sha256(arena.tobytes()).digest() != z["arena_sha256"].tobytes():
+        pytest.skip("numpy's generator stream changed; the seeded arena no longer matches the fixture")
+    return z, d, arena
+
+
+def test_config2_workload_fixture_is_self_consistent_and_pinned(oracle):
+    z, d, arena = _workload("c2_full.npz", "c2")
+    assert int(z["confirmed_by_reference"][0]) == 1
+    toks, logits = z["greedy_tokens"], z["logits_all"]
+    assert toks.shape == (768,) and logits.shape == (1023, d.vocab)
+    # token i is the first maximum of the last row at context 256 + i (inference.cpp:188-198)
+    assert np.array_equal(np.argmax(logits[255:], axis=1), toks)
+    srt = np.sort(logits[255:].astype(np.float64), axis=1)
+    assert np.array_equal((srt[:, -1] - srt[:, -2]).astype(np.float32), z["top2_gap"])
+    # the restatement reproduces the prompt's rows bit for bit
+    got = oracle.forward(d, arena, z["prompt"])
+    assert np.array_equal(got, logits[:256])
+
+
+def test_config3_workload_fixture_first_tokens(oracle):
+    z, d, arena = _workload("c3_streams.npz", "c3")
+    temp, top_k, top_p = (float(z["sampled_params"][0]), int(z["sampled_params"][1]), float(z["sampled_params"][2]))
+    toks, lg = oracle.generate(d, arena, z["prompts"][2], 4, temp=temp, top_k=top_k, top_p=top_p,
+                               seed=int(z["seeds"][2]), want_logits=True)
+    assert np.array_equal(toks, z["sampled_tokens"][2, :4])
+    assert np.array_equal(lg, z["step_logits"][2, :4])
