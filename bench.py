@@ -325,7 +325,7 @@ class Box:
             self.dist.destroy_process_group()
 
 
-def measure_generation(box: Box, workload: str, steps: int, warmup: int, sample_clocks: bool):
+def measure_generation(box: Box, workload: str, steps: int, warmup: int, sample_clocks: bool, kv_cache: bool = False):
     """W warm-up and K timed generations of this rank's streams, device-timed with
     the prompts resident, then K more through litnice_b200_generate with pinned
     host buffers. Returns the figures of the job over all ranks and the session."""
@@ -334,7 +334,16 @@ def measure_generation(box: Box, workload: str, steps: int, warmup: int, sample_
     torch = box.torch
     first, count, scaling = rank_streams(workload, box.world, box.rank)
     d, arena, prompts, seeds, (plen, max_new, temp, top_k, top_p) = make_rank_inputs(workload, first, count)
-    sess = Session(d, count)
+    # kv_cache: the opt-in cached mode (an extension; the reference recomputes the context)
+    old_kv = os.environ.get("LITNICE_B200_KV_CACHE")
+    os.environ["LITNICE_B200_KV_CACHE"] = "1" if kv_cache else "0"
+    try:
+        sess = Session(d, count)
+    finally:
+        if old_kv is None:
+            del os.environ["LITNICE_B200_KV_CACHE"]
+        else:
+            os.environ["LITNICE_B200_KV_CACHE"] = old_kv
     sess.load_params(arena)
     pinned_prompts = torch.from_numpy(prompts.copy()).pin_memory()
     pinned_out = torch.zeros((count, max_new), dtype=torch.int32).pin_memory()
@@ -431,7 +440,8 @@ def hbm_block(peaks):
 def run_b200_arm(args, rank, local_rank, world):
     box = Box(rank, local_rank, world)
     peaks = load_peaks()
-    main = measure_generation(box, args.workload, args.steps, args.warmup, sample_clocks=True)
+    main = measure_generation(box, args.workload, args.steps, args.warmup, sample_clocks=True,
+                              kv_cache=args.kv_cache)
     sess, d = main["sess"], main["dims"]
     plen, max_new = main["plen"], main["max_new"]
     streams_total = WORKLOADS[args.workload][1] * (1 if main["scaling"] == "strong" else world)
@@ -522,6 +532,18 @@ def run_b200_arm(args, rank, local_rank, world):
                 "whole_loop_tflops": wl, "whole_loop_frac": wl / peaks["bf16_tflops"], "clocks": r["clocks"],
                 "parity": r["parity"],
             }
+    if args.workload == "c2" and not args.no_extras:
+        # the same workload in the opt-in cached mode: keys and values of earlier positions kept in
+        # HBM, one new row per step (the regime the few-row products are for); reported beside the
+        # headline, never instead of it, because the reference itself keeps no cache
+        r = measure_generation(box, "c2", 3, 3, sample_clocks=False, kv_cache=True)
+        r["sess"].close()
+        extra["c2_kv_cache"] = {
+            "workload": workload_name("c2", r["streams_this_rank"], r["plen"], r["max_new"]).replace(
+                "whole-context recomputation per token", "keys and values cached (LITNICE_B200_KV_CACHE=1)"),
+            "value": r["value"], "unit": "tokens/s", "ms_per_step": r["dev_ms_per_step"], "steps": 3, "warmup": 3,
+            "e2e": r["e2e"], "gpu_launches": r["launches"], "parity": r["parity"],
+        }
     if rank == 0:
         line = {
             "metric": "generated tokens/s (greedy decode)", "value": main["value"], "unit": "tokens/s",
@@ -530,7 +552,9 @@ def run_b200_arm(args, rank, local_rank, world):
             "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
             "config": {"workload": workload_name(args.workload, main["streams_this_rank"], plen, max_new),
                        "l2": "256 MB buffer written between timed steps (L2 flush)",
-                       "sampling": main["sampling"]},
+                       "sampling": main["sampling"],
+                       "mode": "keys and values cached (extension)" if args.kv_cache else
+                               "whole-context recomputation, as the reference"},
             "e2e": main["e2e"], "gpu_launches": main["launches"],
             "roofline": roofline, "hbm": hbm, "cpu_baseline": cpu, "clocks": main["clocks"],
             "parity": main["parity"], "extra": extra,
@@ -634,6 +658,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kv-cache", action="store_true",
+                    help="run the workload in the opt-in cached mode (an extension; not the headline)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the output-head bandwidth block and the config-3 / config-5 side measurements")
     args = ap.parse_args()

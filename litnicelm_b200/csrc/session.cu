@@ -139,10 +139,10 @@ struct litnice_b200_session {
     int streams = 0;
     SamplerParams sp{};
     unsigned long long generation = 0;
+    long long launches = 0;  // kernels in one replay
   };
   std::vector<StepGraph> graphs;       // indexed by context bucket (tiles of 64)
   unsigned long long generation = 1;   // bumped whenever a buffer a graph points at is replaced
-  long long graph_launches_per_step = 0;
   float *ln_lo = nullptr, *ctx_lo = nullptr, *h_lo = nullptr, *xl_lo = nullptr;
   long long xl_rows = 0;
   std::vector<std::array<TcWeight, 4>> tcw;  // per layer: qkv, out, w1, w2
@@ -189,6 +189,19 @@ struct litnice_b200_session {
   size_t sampler_scratch_bytes_ = 0;
   DevErr *err_host = nullptr, *err_dev = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+
+  // Opt-in cached mode (LITNICE_B200_KV_CACHE=1, an extension: the reference keeps no cache). Keys
+  // and values of earlier positions stay in HBM, [n_layers][kv_streams][kv_cap][d_model] each, and a
+  // step computes one new row per stream (decode.cu). Runs on the fp32 kernels: the whole-context
+  // pass over the prompt that fills the caches on the SIMT path, the steps on the few-row products.
+  bool kv = false;
+  float *kcache = nullptr, *vcache = nullptr;
+  int kv_cap = 0, kv_streams = 0;
+  int kv_len = 0;         // positions of the current streams held in the caches
+  bool kv_store = false;  // the whole-context pass under way also fills the caches
+  float *dx = nullptr, *dy = nullptr, *dln = nullptr, *dqkv = nullptr, *dctx = nullptr, *dh = nullptr;  // step rows
+  float *dec_part = nullptr;  // partial attention sums of the key chunks
+  size_t dec_part_floats = 0;
 
   bool keep_logits = false;
   float *step_logits = nullptr;
@@ -538,6 +551,11 @@ void enqueue_body(litnice_b200_session *s, int B, int sl, const LoopState *dstat
     } else {
       projection(s, A_LN, R, D, P(s, o.qkv_w), tw ? &(*tw)[0] : nullptr, 3 * D, qkv_bias, nullptr, 0, s->qkv,
                  nullptr, fold ? &consume1 : nullptr);
+      if (s->kv_store) {  // cached mode, pass over the prompt: this layer's K and V of every position
+        const size_t layer = (size_t)s->kv_streams * s->kv_cap * D;
+        launch_kv_store(s->qkv, dstate, sl, B, D, s->kv_cap, s->kcache + l * layer, s->vcache + l * layer, s->st);
+        ++s->launches;
+      }
       ClassTimer t(s, &s->attn_ev);
       launch_attention(s->qkv, s->ctx, s->tc ? s->ctx_lo : nullptr, B, sl, d.n_heads, D, s->attn_scratch,
                        s->attn_counters, dstate, s->st);
@@ -573,6 +591,88 @@ void enqueue_head_last(litnice_b200_session *s, int B, int sl, const LoopState *
   } else {
     projection(s, A_XL, B, d.d_model, P(s, s->lay.lm_head), head_tc ? &s->tc_head : nullptr, d.vocab_size,
                nullptr, nullptr, 0, s->logits, nullptr);
+  }
+}
+
+// Cached mode: one projection of the step's rows, out[B, n] = a[B, k] W + bias (+ residual) (ReLU):
+// the few-row kernels up to 8 streams, the fp32 tile kernel beyond.
+void decode_projection(litnice_b200_session *s, const float *a, int B, int k, const float *w, int n, const float *bias,
+                       const float *residual, int relu, float *out) {
+  if (B <= 8) {
+    s->launches += launch_gemv(a, B, w, k, n, bias, out, s->gemv_scratch, s->st, s->err_dev, residual, relu);
+    return;
+  }
+  GemmEpilogue ep;
+  ep.bias = bias;
+  ep.residual = residual;
+  ep.relu = relu;
+  launch_gemm_simt(dense(a, B, k), dense(w, k, n), dense(out, B, n), B, n, k, ep, s->st);
+  ++s->launches;
+}
+
+// Cached mode: the forward pass of the newest row of every stream at context length sl
+// (transformer_layer.cpp:50-92 for one row; attention over the cached positions and the new one),
+// ending with the last-row logits in s->logits.
+void enqueue_decode_step(litnice_b200_session *s, int B, int sl, const LoopState *dstate) {
+  const litnice_b200_dims &d = s->dims;
+  const int D = d.d_model, F = d.d_ff, V = d.vocab_size;
+  const size_t layer = (size_t)s->kv_streams * s->kv_cap * D;
+  launch_embed_last_ln(P(s, s->lay.tok_emb), P(s, s->lay.pos_emb), s->ids, d.max_seq_len, dstate, sl, B, D, V,
+                       P(s, s->lay.layer[0].ln1_g), P(s, s->lay.layer[0].ln1_b), s->dx, s->dln, s->err_dev, s->st);
+  ++s->launches;
+  for (int l = 0; l < d.n_layers; ++l) {
+    const LayerOff &o = s->lay.layer[l];
+    if (l > 0) {
+      launch_layernorm_dense(s->dx, P(s, o.ln1_g), P(s, o.ln1_b), B, D, s->dln, nullptr, nullptr, B, s->st);
+      ++s->launches;
+    }
+    decode_projection(s, s->dln, B, D, P(s, o.qkv_w), 3 * D, P(s, o.qkv_b), nullptr, 0, s->dqkv);
+    s->launches += launch_attn_decode(s->dqkv, s->kcache + l * layer, s->vcache + l * layer, s->kv_cap, D, d.n_heads, B,
+                                      dstate, sl, s->dec_part, s->dctx, s->st);
+    decode_projection(s, s->dctx, B, D, P(s, o.out_w), D, P(s, o.out_b), s->dx, 0, s->dy);
+    launch_layernorm_dense(s->dy, P(s, o.ln2_g), P(s, o.ln2_b), B, D, s->dln, nullptr, nullptr, B, s->st);
+    ++s->launches;
+    decode_projection(s, s->dln, B, D, P(s, o.w1), F, P(s, o.b1), nullptr, 1, s->dh);
+    decode_projection(s, s->dh, B, F, P(s, o.w2), D, P(s, o.b2), s->dy, 0, s->dx);
+  }
+  launch_layernorm_dense(s->dx, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), B, D, s->xl, nullptr, nullptr, B, s->st);
+  ++s->launches;
+  decode_projection(s, s->xl, B, D, P(s, s->lay.lm_head), V, nullptr, nullptr, 0, s->logits);
+}
+
+// Cached mode: caches for n_streams streams of up to cap positions, and the scratch of the
+// attention over key chunks for every context length up to cap.
+void ensure_kv(litnice_b200_session *s, int B, int cap) {
+  const litnice_b200_dims &d = s->dims;
+  if (B > s->kv_streams || cap > s->kv_cap) {
+    LB_CUDA(cudaStreamSynchronize(s->st));
+    for (float **p : {&s->kcache, &s->vcache}) {
+      if (*p) cudaFree(*p);
+      *p = nullptr;
+    }
+    s->kv_streams = s->kv_cap = 0;
+    s->kv_len = 0;
+    const int nb = B > s->max_streams ? B : s->max_streams;
+    const size_t bytes = (size_t)d.n_layers * nb * cap * d.d_model * 4;
+    if (cudaMalloc(reinterpret_cast<void **>(&s->kcache), bytes) != cudaSuccess) throw std::bad_alloc();
+    if (cudaMalloc(reinterpret_cast<void **>(&s->vcache), bytes) != cudaSuccess) throw std::bad_alloc();
+    s->kv_streams = nb;
+    s->kv_cap = cap;
+    ++s->generation;
+  }
+  size_t need = 0;
+  for (int sl = 64; sl <= (cap + 63) / 64 * 64; sl += 64) {
+    const size_t f = attn_decode_plan(B, sl, d.n_heads, d.d_model / d.n_heads).scratch_floats;
+    if (f > need) need = f;
+  }
+  if (need > s->dec_part_floats) {
+    LB_CUDA(cudaStreamSynchronize(s->st));
+    if (s->dec_part) cudaFree(s->dec_part);
+    s->dec_part = nullptr;
+    s->dec_part_floats = 0;
+    if (cudaMalloc(reinterpret_cast<void **>(&s->dec_part), need * 4) != cudaSuccess) throw std::bad_alloc();
+    s->dec_part_floats = need;
+    ++s->generation;
   }
 }
 
@@ -768,8 +868,11 @@ static int session_create_impl(const litnice_b200_dims *dims, int32_t max_stream
     s->use_graphs = !(graph_env && graph_env[0] == '0');
     const char *tail_env = std::getenv("LITNICE_B200_FUSED_TAIL");
     s->fused_tail = !(tail_env && tail_env[0] == '0');
+    const char *kv_env = std::getenv("LITNICE_B200_KV_CACHE");
+    s->kv = kv_env && kv_env[0] == '1';
     const char *tc_env = std::getenv("LITNICE_B200_TC");
-    s->tc = !(tc_env && tc_env[0] == '0') && tc_runtime_available() && d.d_model % 64 == 0 && d.d_ff % 64 == 0;
+    s->tc = !s->kv && !(tc_env && tc_env[0] == '0') && tc_runtime_available() && d.d_model % 64 == 0 &&
+            d.d_ff % 64 == 0;
     // Attention on the tensor cores needs head dimension 64; LITNICE_B200_TC_ATTN=0
     // keeps the fp32 SIMT attention kernel.
     const char *ta_env = std::getenv("LITNICE_B200_TC_ATTN");
@@ -800,7 +903,20 @@ static int session_create_impl(const litnice_b200_dims *dims, int32_t max_stream
     must(cudaMalloc(reinterpret_cast<void **>(&s->probs), lr * d.vocab_size * 4));
     LB_CUDA(cudaMemsetAsync(s->xl, 0, lr * d.d_model * 4, s->st));
     LB_CUDA(cudaMemsetAsync(s->logits, 0, lr * d.vocab_size * 4, s->st));
-    const size_t gs = gemv_scratch_floats(8, d.vocab_size, d.d_model);
+    size_t gs = gemv_scratch_floats(8, d.vocab_size, d.d_model);
+    if (s->kv) {
+      // the step's rows and the few-row products of the layers
+      for (size_t f : {gemv_scratch_floats(8, 3 * d.d_model, d.d_model), gemv_scratch_floats(8, d.d_model, d.d_model),
+                       gemv_scratch_floats(8, d.d_ff, d.d_model), gemv_scratch_floats(8, d.d_model, d.d_ff)})
+        gs = f > gs ? f : gs;
+      const size_t rows = (size_t)(max_streams < 8 ? 8 : max_streams);
+      for (auto &[p, cols] : {std::pair<float **, size_t>{&s->dx, (size_t)d.d_model}, {&s->dy, (size_t)d.d_model},
+                              {&s->dln, (size_t)d.d_model}, {&s->dqkv, (size_t)3 * d.d_model},
+                              {&s->dctx, (size_t)d.d_model}, {&s->dh, (size_t)d.d_ff}}) {
+        must(cudaMalloc(reinterpret_cast<void **>(p), rows * cols * 4));
+        LB_CUDA(cudaMemsetAsync(*p, 0, rows * cols * 4, s->st));
+      }
+    }
     if (gs) must(cudaMalloc(reinterpret_cast<void **>(&s->gemv_scratch), gs * 4));
     must(cudaMalloc(reinterpret_cast<void **>(&s->ids), (size_t)max_streams * d.max_seq_len * 4));
     LB_CUDA(cudaMemsetAsync(s->ids, 0, (size_t)max_streams * d.max_seq_len * 4, s->st));
@@ -824,6 +940,8 @@ void litnice_b200_session_destroy(litnice_b200_session *s) {
     if (p) cudaFree(p);
   for (auto &g : s->graphs)
     if (g.exec) cudaGraphExecDestroy(g.exec);
+  for (float *p : {s->kcache, s->vcache, s->dx, s->dy, s->dln, s->dqkv, s->dctx, s->dh, s->dec_part})
+    if (p) cudaFree(p);
   if (s->xl_lo) cudaFree(s->xl_lo);
   if (s->tc_scratch) cudaFree(s->tc_scratch);
   if (s->attn_timeline) cudaFree(s->attn_timeline);
@@ -951,6 +1069,7 @@ int litnice_b200_upload_prompts(litnice_b200_session *s, const int32_t *prompts,
     s->cur_streams = n_streams;
     s->cur_prompt_len = prompt_len;
     s->cur_tokens = 0;
+    s->kv_len = 0;  // cached mode: the caches hold another batch's positions
     return LITNICE_B200_OK;
   });
 }
@@ -972,8 +1091,19 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
     if (steps < 0) steps = 0;
     const int s_last = s0 + (steps > 0 ? steps - 1 : 0);
     const int s_last_cap = (s_last + 63) / 64 * 64;  // graph replay sizes launches per 64-token bucket
-    ensure_rows(s, (long long)B * s_last_cap);
-    if (steps > 0) ensure_attention_scratch(s, B, s0, s_last_cap);
+    if (s->kv) {
+      // cached mode: whole-context buffers only for the pass over the prompt that fills the caches
+      if (steps > 0) {
+        ensure_kv(s, B, s_last_cap);
+        if (s->kv_len != s0 - 1) {
+          ensure_rows(s, (long long)B * s0);
+          ensure_attention_scratch(s, B, s0, s0);
+        }
+      }
+    } else {
+      ensure_rows(s, (long long)B * s_last_cap);
+      if (steps > 0) ensure_attention_scratch(s, B, s0, s_last_cap);
+    }
     if (s->out_cap < s->cur_tokens + steps || s->out_tokens == nullptr) {
       LB_CUDA(cudaStreamSynchronize(s->st));
       int *n = nullptr;
@@ -1028,9 +1158,21 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
     // the device-side LoopState) and replayed for every step in the bucket, so
     // the host issues one launch per token instead of ~50.
     const bool graphs = s->use_graphs && !s->keep_logits;
-    const bool fused_tail = greedy && !s->keep_logits && s->fused_tail && head_greedy_supports(B, s->dims.d_model, V);
-    auto enqueue_step = [&](int sl_cap, const LoopState *dstate, int step) {
-      enqueue_body(s, B, sl_cap, dstate);
+    const bool fused_tail =
+        greedy && !s->keep_logits && s->fused_tail && !s->kv && head_greedy_supports(B, s->dims.d_model, V);
+    auto enqueue_step = [&](int sl_cap, const LoopState *dstate, int step, bool decode) {
+      if (decode) {
+        enqueue_decode_step(s, B, sl_cap, dstate);
+      } else {
+        s->kv_store = s->kv;
+        try {
+          enqueue_body(s, B, sl_cap, dstate);
+        } catch (...) {
+          s->kv_store = false;
+          throw;
+        }
+        s->kv_store = false;
+      }
       if (fused_tail) {
         launch_head_greedy(s->x, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), P(s, s->lay.lm_head), s->dims.d_model, V, B,
                            sl_cap, dstate, s->state, reinterpret_cast<unsigned *>(s->state + 1), s->ids,
@@ -1038,7 +1180,7 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
         ++s->launches;
         return;
       }
-      enqueue_head_last(s, B, sl_cap, dstate);
+      if (!decode) enqueue_head_last(s, B, sl_cap, dstate);
       if (s->keep_logits) {
         LB_CUDA(cudaMemcpyAsync(s->step_logits + (long long)(s->cur_tokens + step) * B * V, s->logits,
                                 (size_t)B * V * 4, cudaMemcpyDeviceToDevice, s->st));
@@ -1051,8 +1193,12 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
     LB_CUDA(cudaEventRecord(s->ev0, s->st));
     for (int step = 0; step < steps; ++step) {
       const int sl = s0 + step;
-      if (!graphs) {
-        enqueue_step(sl, nullptr, step);
+      // cached mode: a step on one new row per stream when the caches hold every earlier
+      // position, else a whole-context pass that also fills them (the first step of a batch)
+      const bool decode = s->kv && s->kv_len == sl - 1;
+      if (s->kv) s->kv_len = sl;
+      if (!graphs || (s->kv && !decode)) {
+        enqueue_step(sl, nullptr, step, decode);
         continue;
       }
       const int bucket = (sl + 63) / 64;
@@ -1069,7 +1215,7 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
         cudaGraph_t graph = nullptr;
         LB_CUDA(cudaStreamBeginCapture(s->st, cudaStreamCaptureModeRelaxed));
         try {
-          enqueue_step(bucket * 64, s->state, step);
+          enqueue_step(bucket * 64, s->state, step, decode);
         } catch (...) {
           cudaStreamEndCapture(s->st, &graph);
           if (graph) cudaGraphDestroy(graph);
@@ -1082,11 +1228,11 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
         g.streams = B;
         g.sp = sp;
         g.generation = s->generation;
-        s->graph_launches_per_step = s->launches - before;
+        g.launches = s->launches - before;
         s->launches = before;  // capturing enqueued nothing
       }
       LB_CUDA(cudaGraphLaunch(g.exec, s->st));
-      s->launches += s->graph_launches_per_step;
+      s->launches += g.launches;
     }
     LB_CUDA(cudaEventRecord(s->ev1, s->st));
     LB_CUDA(cudaStreamSynchronize(s->st));
