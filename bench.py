@@ -8,7 +8,13 @@ generation of the workload: for the default workload `c2` a 256-token Zipf
 prompt followed by 768 greedy tokens at batch 1 on the 6-layer / 512-wide /
 vocab-96 model, every token recomputing its whole context as the reference
 does (no KV cache). With N GPUs each rank decodes its own independent stream
-(weak scaling, no collective on the data path); rank 0 prints one JSON line.
+(weak scaling, no collective on the data path); `--workload c5` is one job of
+512 streams cut into contiguous blocks over the GPUs (strong scaling). Rank 0
+prints one JSON line. Beside the headline the default line carries: `parity`
+(the run's tokens against the committed oracle fixture of the same inputs),
+`hbm` (the output-head product of configs 4/5 against the HBM roofline), and
+`extra` (config 3: 64 lockstep streams with the fused sampler; config 5 cut
+over the GPUs; config 2 in the opt-in cached mode).
 
 `--impl reference` times the reference's own CPU backend (oracle/_ref, built
 from the reference sources) on a bounded sample of the same workload.
@@ -215,7 +221,8 @@ def run_reference_arm(args, rank, world):
         "ms_per_step": 1e3 * wall / max(1, args.steps), "higher_is_better": True, "scaling": scaling,
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(args.workload, per_gpu, plen, max_new), "l2": "not applicable (CPU)",
-                   "sampling": {"temp": temp, "top_k": top_k, "top_p": top_p}},
+                   "sampling": {"temp": temp, "top_k": top_k, "top_p": top_p},
+                   "mode": "whole-context recomputation, as the reference"},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": conc, "kind": "reference", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
