@@ -35,6 +35,26 @@ struct Backend {
   void *scratch = nullptr;  // partial sums and row statistics of the training entries
   size_t scratch_bytes = 0;
 
+  // Deferred operators. The host issues one table call per operator and per attention head
+  // (self_attention_fused_inplace.cpp:82-94: three calls per head; transformer_layer.cpp:79-86 and
+  // the FFN variants: a product, then its bias). Calls that can be merged with their neighbours are
+  // recorded instead of launched and issued together at the next call that is anything else:
+  // a projection with the bias (and ReLU) that follows it becomes one launch, and the score product,
+  // causal softmax and context product of all heads of a layer become three launches instead of
+  // three per head. Nothing is reordered against other calls and every buffer the host's sequence
+  // writes is written with the same values, so the host cannot tell the difference
+  // (LITNICE_B200_ABI_QUEUE=0 issues every call at once).
+  struct Pending {
+    enum Kind { PROJECTION, BIAS, BIAS_RELU, SCORES, SOFTMAX, CONTEXT } kind;
+    BackendTensorView a, b, c;  // copies: the host's views are only valid during its call
+    float scale = 0.f;
+  };
+  std::vector<Pending> queue;
+  bool queue_on = true;
+  float *queue_scratch = nullptr;  // scores of all heads when the host gives every head the same buffer
+  size_t queue_scratch_floats = 0;
+  long long fused_projections = 0, grouped_heads = 0;
+
   // Read-ahead for row-by-row read-back. The host reads logits one row per
   // copy_device2host call (host_tensor_stage.hpp:101-125: s calls of V floats per
   // token). When two small copies in a row walk forward through one allocation
@@ -62,15 +82,26 @@ constexpr uint64_t SHADOW_MAX = 64ull << 20;     // largest window (pinned buffe
 
 // Every table entry except the read-only ones comes through here: whatever it
 // does may write device memory, which invalidates the read-back mirror.
+void flush_queue(Backend *b);
+
 Backend *self(void *h) {
   if (h == nullptr) throw std::invalid_argument("litnice_b200: null backend handle");
   Backend *b = static_cast<Backend *>(h);
   ++b->epoch;
+  if (!b->queue.empty()) flush_queue(b);
   return b;
 }
-Backend *self_reader(void *h) {  // entries that only read
+Backend *self_reader(void *h) {  // entries that only read (they see every earlier call's effect)
   if (h == nullptr) throw std::invalid_argument("litnice_b200: null backend handle");
-  return static_cast<Backend *>(h);
+  Backend *b = static_cast<Backend *>(h);
+  if (!b->queue.empty()) flush_queue(b);
+  return b;
+}
+Backend *self_recording(void *h) {  // entries that may record instead of launching, and pure bookkeeping
+  if (h == nullptr) throw std::invalid_argument("litnice_b200: null backend handle");
+  Backend *b = static_cast<Backend *>(h);
+  ++b->epoch;
+  return b;
 }
 
 void bind(Backend *b) { LB_CUDA(cudaSetDevice(b->device)); }
@@ -125,6 +156,7 @@ void *api_create(uint32_t device_kind) {
   try {
     b->device = dev;
     if (const char *env = std::getenv("LITNICE_B200_READ_AHEAD")) b->read_ahead = env[0] != '0';
+    if (const char *env = std::getenv("LITNICE_B200_ABI_QUEUE")) b->queue_on = env[0] != '0';
     bind(b);
     cudaDeviceProp prop{};
     LB_CUDA(cudaGetDeviceProperties(&prop, dev));
@@ -147,6 +179,7 @@ void api_destroy(void *h) {
   if (h == nullptr) return;
   Backend *b = static_cast<Backend *>(h);
   cudaSetDevice(b->device);
+  b->queue.clear();  // nothing can observe recorded work once the instance is gone
   if (b->st) {
     cudaStreamSynchronize(b->st);
     cudaStreamDestroy(b->st);
@@ -154,6 +187,7 @@ void api_destroy(void *h) {
   if (b->err_host) cudaFreeHost(b->err_host);
   if (b->shadow) cudaFreeHost(b->shadow);
   if (b->scratch) cudaFree(b->scratch);
+  if (b->queue_scratch) cudaFree(b->queue_scratch);
   delete b;
 }
 
@@ -362,15 +396,37 @@ void api_add_inplace(void *h, LitniceView a, LitniceView bb) {
   api_add(h, a, bb, a);
 }
 
+bool same_view(const BackendTensorView &p, const BackendTensorView &q) {
+  if (p.data != q.data || p.rank != q.rank || p.dtype != q.dtype || p.device != q.device) return false;
+  for (uint32_t i = 0; i < p.rank; ++i)
+    if (p.dims[i] != q.dims[i] || p.strides_bytes[i] != q.strides_bytes[i]) return false;
+  return true;
+}
+
 void bias_op(void *h, EwOp op, LitniceView x, LitniceView bias, LitniceView out, const char *who) {
-  Backend *b = self(h);
+  Backend *b = self_recording(h);
   require_gpu_f32(x, who);
   require_gpu_f32(bias, who);
   require_gpu_f32(out, who);
+  {
+    RowView rx = make_row_view(x, who), ro = make_row_view(out, who);
+    if (view_numel(bias) != rx.cols || ro.cols != rx.cols || ro.rows != rx.rows)
+      throw std::runtime_error(std::string(who) + ": semantic shape mismatch");
+  }
+  // In place on the result of the projection recorded just before: joins it as its epilogue.
+  if (b->queue.size() == 1 && b->queue[0].kind == Backend::Pending::PROJECTION && (op == EW_ADD_BIAS || op == EW_ADD_BIAS_RELU) && same_view(*x, *out) && same_view(b->queue[0].c, *x) &&
+      bias->strides_bytes[bias->rank - 1] == 4 && (reinterpret_cast<uintptr_t>(bias->data) & 3) == 0) {
+    Backend::Pending p;
+    p.kind = op == EW_ADD_BIAS ? Backend::Pending::BIAS : Backend::Pending::BIAS_RELU;
+    p.a = *bias;
+    p.c = *out;
+    b->queue.push_back(p);
+    flush_queue(b);  // a projection with its epilogue is complete
+    return;
+  }
+  if (!b->queue.empty()) flush_queue(b);
   bind(b);
   RowView rx = make_row_view(x, who), ro = make_row_view(out, who);
-  if (view_numel(bias) != rx.cols || ro.cols != rx.cols || ro.rows != rx.rows)
-    throw std::runtime_error(std::string(who) + ": semantic shape mismatch");
   RowView rb{};
   rb.data = static_cast<char *>(bias->data);
   rb.np = 0;
@@ -494,17 +550,36 @@ void api_softmax_rows(void *h, LitniceView x, LitniceView out) {
 }
 
 // device_backend.cpp:1554-1592
-void api_causal_softmax(void *h, LitniceView scores, float scale, LitniceView out) {
-  Backend *b = self(h);
-  require_gpu_f32(scores, "litnice_b200::scaled_causal_softmax_rows(scores)");
-  require_gpu_f32(out, "litnice_b200::scaled_causal_softmax_rows(out)");
+void run_causal_softmax(Backend *b, const BackendTensorView *scores, float scale, const BackendTensorView *out) {
   bind(b);
   RowView rx = make_row_view(scores, "scaled_causal_softmax_rows(scores)"),
           ro = make_row_view(out, "scaled_causal_softmax_rows(out)");
-  if (rx.rows != ro.rows || rx.cols != ro.cols)
-    throw std::runtime_error("litnice_b200::scaled_causal_softmax_rows: shape mismatch");
   launch_softmax_rows(rx, ro, 1, scale, b->st);
   ++b->launches;
+}
+
+void api_causal_softmax(void *h, LitniceView scores, float scale, LitniceView out) {
+  Backend *b = self_recording(h);
+  require_gpu_f32(scores, "litnice_b200::scaled_causal_softmax_rows(scores)");
+  require_gpu_f32(out, "litnice_b200::scaled_causal_softmax_rows(out)");
+  {
+    RowView rx = make_row_view(scores, "scaled_causal_softmax_rows(scores)"),
+            ro = make_row_view(out, "scaled_causal_softmax_rows(out)");
+    if (rx.rows != ro.rows || rx.cols != ro.cols)
+      throw std::runtime_error("litnice_b200::scaled_causal_softmax_rows: shape mismatch");
+  }
+  // the softmax of the score product recorded just before: part of a head's three calls
+  if (!b->queue.empty() && b->queue.back().kind == Backend::Pending::SCORES && same_view(b->queue.back().c, *scores)) {
+    Backend::Pending p;
+    p.kind = Backend::Pending::SOFTMAX;
+    p.a = *scores;
+    p.c = *out;
+    p.scale = scale;
+    b->queue.push_back(p);
+    return;
+  }
+  if (!b->queue.empty()) flush_queue(b);
+  run_causal_softmax(b, scores, scale, out);
 }
 
 // ---- matrix products -------------------------------------------------------------
@@ -521,13 +596,18 @@ MatView shared_matrix(LitniceView t, const char *who) {  // rank-2 operand used 
   return v;
 }
 
-void run_gemm(Backend *b, const MatView &a, const MatView &bm, const MatView &c, const char *who) {
+void check_gemm(const MatView &a, const MatView &bm, const MatView &c, const char *who) {
   if (a.cols != bm.rows || c.rows != a.rows || c.cols != bm.cols)
     throw std::runtime_error(std::string(who) + ": inner or output dimension mismatch");
   if (a.batch != c.batch || (bm.batch != 1 && bm.batch != c.batch))
     throw std::runtime_error(std::string(who) + ": batch mismatch");
+}
+
+void run_gemm(Backend *b, const MatView &a, const MatView &bm, const MatView &c, const char *who,
+              const GemmEpilogue &ep = GemmEpilogue{}) {
+  check_gemm(a, bm, c, who);
   bind(b);
-  launch_gemm_simt(a, bm, c, c.rows, c.cols, a.cols, GemmEpilogue{}, b->st);
+  launch_gemm_simt(a, bm, c, c.rows, c.cols, a.cols, ep, b->st);
   ++b->launches;
 }
 
@@ -543,32 +623,255 @@ void api_gemm(void *h, LitniceView a, LitniceView bb, LitniceView out) {
 
 // device_backend.cpp:1112-1131
 void api_gemm_ranked_matrix_rhs(void *h, LitniceView a, LitniceView bb, LitniceView out) {
-  Backend *b = self(h);
+  Backend *b = self_recording(h);
+  if (!b->queue.empty()) flush_queue(b);
   require_gpu_f32(a, "litnice_b200::gemm_ranked_matrix_rhs(a)");
   require_gpu_f32(bb, "litnice_b200::gemm_ranked_matrix_rhs(b)");
   require_gpu_f32(out, "litnice_b200::gemm_ranked_matrix_rhs(out)");
-  run_gemm(b, make_mat_view(a, "gemm_ranked_matrix_rhs(a)"), shared_matrix(bb, "gemm_ranked_matrix_rhs(b)"),
-           make_mat_view(out, "gemm_ranked_matrix_rhs(out)"), "litnice_b200::gemm_ranked_matrix_rhs");
+  const MatView av = make_mat_view(a, "gemm_ranked_matrix_rhs(a)"), bv = shared_matrix(bb, "gemm_ranked_matrix_rhs(b)"),
+                ov = make_mat_view(out, "gemm_ranked_matrix_rhs(out)");
+  if (b->queue_on) {  // recorded: the bias call that usually follows becomes its epilogue
+    check_gemm(av, bv, ov, "litnice_b200::gemm_ranked_matrix_rhs");
+    Backend::Pending p;
+    p.kind = Backend::Pending::PROJECTION;
+    p.a = *a;
+    p.b = *bb;
+    p.c = *out;
+    b->queue.push_back(p);
+    return;
+  }
+  run_gemm(b, av, bv, ov, "litnice_b200::gemm_ranked_matrix_rhs");
 }
 
 // device_backend.cpp:1175-1193
 void api_gemm_batched(void *h, LitniceView a, LitniceView bb, LitniceView out) {
-  Backend *b = self(h);
+  Backend *b = self_recording(h);
   require_gpu_f32(a, "litnice_b200::gemm_batched(a)");
   require_gpu_f32(bb, "litnice_b200::gemm_batched(b)");
   require_gpu_f32(out, "litnice_b200::gemm_batched(out)");
-  run_gemm(b, make_mat_view(a, "gemm_batched(a)"), make_mat_view(bb, "gemm_batched(b)"),
-           make_mat_view(out, "gemm_batched(out)"), "litnice_b200::gemm_batched");
+  const MatView av = make_mat_view(a, "gemm_batched(a)"), bv = make_mat_view(bb, "gemm_batched(b)"),
+                ov = make_mat_view(out, "gemm_batched(out)");
+  // the context product of the softmax recorded just before: completes a head's three calls
+  if (!b->queue.empty() && b->queue.back().kind == Backend::Pending::SOFTMAX && same_view(b->queue.back().c, *a)) {
+    check_gemm(av, bv, ov, "litnice_b200::gemm_batched");
+    Backend::Pending p;
+    p.kind = Backend::Pending::CONTEXT;
+    p.a = *a;
+    p.b = *bb;
+    p.c = *out;
+    b->queue.push_back(p);
+    return;
+  }
+  if (!b->queue.empty()) flush_queue(b);
+  run_gemm(b, av, bv, ov, "litnice_b200::gemm_batched");
 }
 
 // device_backend.cpp:1216-1235: out[r,c] = sum_k a[r,k] * b[c,k]
 void api_gemm_batched_rhs_t(void *h, LitniceView a, LitniceView bb, LitniceView out) {
-  Backend *b = self(h);
+  Backend *b = self_recording(h);
   require_gpu_f32(a, "litnice_b200::gemm_batched_rhs_t(a)");
   require_gpu_f32(bb, "litnice_b200::gemm_batched_rhs_t(b)");
   require_gpu_f32(out, "litnice_b200::gemm_batched_rhs_t(out)");
-  run_gemm(b, make_mat_view(a, "gemm_batched_rhs_t(a)"), transposed(make_mat_view(bb, "gemm_batched_rhs_t(b)")),
-           make_mat_view(out, "gemm_batched_rhs_t(out)"), "litnice_b200::gemm_batched_rhs_t");
+  const MatView av = make_mat_view(a, "gemm_batched_rhs_t(a)"),
+                bv = transposed(make_mat_view(bb, "gemm_batched_rhs_t(b)")),
+                ov = make_mat_view(out, "gemm_batched_rhs_t(out)");
+  // a score product opens a head's three calls; it may follow the completed calls of earlier heads
+  const bool heads_pending = !b->queue.empty() && b->queue.back().kind == Backend::Pending::CONTEXT;
+  if (!b->queue.empty() && !heads_pending) flush_queue(b);
+  if (b->queue_on) {
+    check_gemm(av, bv, ov, "litnice_b200::gemm_batched_rhs_t");
+    Backend::Pending p;
+    p.kind = Backend::Pending::SCORES;
+    p.a = *a;
+    p.b = *bb;
+    p.c = *out;
+    b->queue.push_back(p);
+    return;
+  }
+  run_gemm(b, av, bv, ov, "litnice_b200::gemm_batched_rhs_t");
+}
+
+// ---- the deferred operators, issued ---------------------------------------------------------
+
+MatView with_heads(MatView v, long long n, long long delta) {  // one more (outermost) batch axis
+  for (int i = v.nb; i > 0; --i) {
+    v.bd[i] = v.bd[i - 1];
+    v.bs[i] = v.bs[i - 1];
+  }
+  v.bd[0] = n;
+  v.bs[0] = delta;
+  ++v.nb;
+  v.batch *= n;
+  return v;
+}
+RowView with_heads(RowView v, long long n, long long delta) {
+  for (int i = v.np; i > 0; --i) {
+    v.pd[i] = v.pd[i - 1];
+    v.ps[i] = v.ps[i - 1];
+  }
+  v.pd[0] = n;
+  v.ps[0] = delta;
+  ++v.np;
+  v.rows *= n;
+  return v;
+}
+
+bool same_shape(const BackendTensorView &p, const BackendTensorView &q) {
+  if (p.rank != q.rank) return false;
+  for (uint32_t i = 0; i < p.rank; ++i)
+    if (p.dims[i] != q.dims[i] || p.strides_bytes[i] != q.strides_bytes[i]) return false;
+  return true;
+}
+
+void issue_one(Backend *b, const Backend::Pending &p) {
+  switch (p.kind) {
+    case Backend::Pending::PROJECTION:
+      run_gemm(b, make_mat_view(&p.a, "gemm_ranked_matrix_rhs(a)"), shared_matrix(&p.b, "gemm_ranked_matrix_rhs(b)"),
+               make_mat_view(&p.c, "gemm_ranked_matrix_rhs(out)"), "litnice_b200::gemm_ranked_matrix_rhs");
+      break;
+    case Backend::Pending::SCORES:
+      run_gemm(b, make_mat_view(&p.a, "gemm_batched_rhs_t(a)"), transposed(make_mat_view(&p.b, "gemm_batched_rhs_t(b)")),
+               make_mat_view(&p.c, "gemm_batched_rhs_t(out)"), "litnice_b200::gemm_batched_rhs_t");
+      break;
+    case Backend::Pending::SOFTMAX:
+      run_causal_softmax(b, &p.a, p.scale, &p.c);
+      break;
+    case Backend::Pending::CONTEXT:
+      run_gemm(b, make_mat_view(&p.a, "gemm_batched(a)"), make_mat_view(&p.b, "gemm_batched(b)"),
+               make_mat_view(&p.c, "gemm_batched(out)"), "litnice_b200::gemm_batched");
+      break;
+    default:
+      throw std::logic_error("litnice_b200: a recorded bias has no projection");
+  }
+}
+
+// The three calls of heads [0, n) starting at queue index `at` as three launches over all heads, when
+// every head's views have the same shape and their addresses advance by one constant per operand.
+bool issue_heads_grouped(Backend *b, size_t at, long long n) {
+  const Backend::Pending *q = b->queue.data() + at;
+  auto delta = [&](int op, int which) -> long long {  // address step from head 0 to head 1
+    auto pick = [&](const Backend::Pending &p) { return which == 0 ? p.a.data : which == 1 ? p.b.data : p.c.data; };
+    return (long long)(static_cast<char *>(pick(q[3 + op])) - static_cast<char *>(pick(q[op])));
+  };
+  const long long dq = delta(0, 0), dk = delta(0, 1), ds = delta(0, 2), dw = delta(1, 2), dv = delta(2, 1),
+                  dc = delta(2, 2);
+  for (long long h = 0; h < n; ++h)
+    for (int op = 0; op < 3; ++op) {
+      const Backend::Pending &p = q[3 * h + op], &p0 = q[op];
+      if (!same_shape(p.a, p0.a) || !same_shape(p.c, p0.c) || (op != 1 && !same_shape(p.b, p0.b))) return false;
+      if (op == 1 && p.scale != p0.scale) return false;
+      auto at_step = [&](void *ptr, void *base, long long d) {
+        return static_cast<char *>(ptr) == static_cast<char *>(base) + h * d;
+      };
+      if (op == 0 && !(at_step(p.a.data, p0.a.data, dq) && at_step(p.b.data, p0.b.data, dk) &&
+                       at_step(p.c.data, p0.c.data, ds)))
+        return false;
+      if (op == 1 && !at_step(p.c.data, p0.c.data, dw)) return false;
+      if (op == 2 && !(at_step(p.b.data, p0.b.data, dv) && at_step(p.c.data, p0.c.data, dc))) return false;
+    }
+  if (dw == 0 || dc == 0) return false;  // heads must not share their outputs
+  MatView qa = make_mat_view(&q[0].a, "gemm_batched_rhs_t(a)"),
+          kb = transposed(make_mat_view(&q[0].b, "gemm_batched_rhs_t(b)")),
+          sc = make_mat_view(&q[0].c, "gemm_batched_rhs_t(out)");
+  RowView sx = make_row_view(&q[1].a, "scaled_causal_softmax_rows(scores)"),
+          so = make_row_view(&q[1].c, "scaled_causal_softmax_rows(out)");
+  MatView wa = make_mat_view(&q[2].a, "gemm_batched(a)"), vb = make_mat_view(&q[2].b, "gemm_batched(b)"),
+          co = make_mat_view(&q[2].c, "gemm_batched(out)");
+  if (qa.nb > 2 || sx.np > 3) return false;
+  bind(b);
+  const bool shared_scores = ds == 0;  // every head's scores land in one buffer of the host
+  MatView sc_all = with_heads(sc, n, ds);
+  RowView sx_all = with_heads(sx, n, ds);
+  if (shared_scores) {
+    // Scores of all heads side by side in scratch; the host's buffer receives the last head's, which is
+    // what it holds after the host's own sequence.
+    if (sc.batch != 1) return false;
+    const size_t per_head = (size_t)sc.rows * sc.cols;
+    if (per_head * n > b->queue_scratch_floats) {
+      LB_CUDA(cudaStreamSynchronize(b->st));
+      if (b->queue_scratch) cudaFree(b->queue_scratch);
+      b->queue_scratch = nullptr;
+      b->queue_scratch_floats = 0;
+      if (cudaMalloc(reinterpret_cast<void **>(&b->queue_scratch), per_head * n * 4) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+      }
+      b->queue_scratch_floats = per_head * n;
+    }
+    MatView dense_sc{};
+    dense_sc.data = reinterpret_cast<char *>(b->queue_scratch);
+    dense_sc.nb = 0;
+    dense_sc.batch = 1;
+    dense_sc.rows = sc.rows;
+    dense_sc.cols = sc.cols;
+    dense_sc.rs = sc.cols * 4;
+    dense_sc.cs = 4;
+    sc_all = with_heads(dense_sc, n, (long long)per_head * 4);
+    RowView dense_sx{};
+    dense_sx.data = reinterpret_cast<char *>(b->queue_scratch);
+    dense_sx.np = 1;
+    dense_sx.pd[0] = sc.rows;
+    dense_sx.ps[0] = sc.cols * 4;
+    dense_sx.rows = sc.rows;
+    dense_sx.cols = sc.cols;
+    dense_sx.cs = 4;
+    sx_all = with_heads(dense_sx, n, (long long)per_head * 4);
+  }
+  launch_gemm_simt(with_heads(qa, n, dq), with_heads(kb, n, dk), sc_all, sc.rows, sc.cols, qa.cols, GemmEpilogue{},
+                   b->st);
+  launch_softmax_rows(sx_all, with_heads(so, n, dw), 1, q[1].scale, b->st);
+  launch_gemm_simt(with_heads(wa, n, dw), with_heads(vb, n, dv), with_heads(co, n, dc), co.rows, co.cols, wa.cols,
+                   GemmEpilogue{}, b->st);
+  b->launches += 3;
+  if (shared_scores) {
+    RowView last{};
+    last.data = reinterpret_cast<char *>(b->queue_scratch + (size_t)(n - 1) * sc.rows * sc.cols);
+    last.np = 1;
+    last.pd[0] = sc.rows;
+    last.ps[0] = sc.cols * 4;
+    last.rows = sc.rows;
+    last.cols = sc.cols;
+    last.cs = 4;
+    launch_rowwise(EW_COPY, last, nullptr, 0, 0.f, sx, b->st);
+    ++b->launches;
+  }
+  b->grouped_heads += n;
+  return true;
+}
+
+void flush_queue(Backend *b) {
+  std::vector<Backend::Pending> q;
+  q.swap(b->queue);  // whatever happens below, nothing stays recorded
+  if (q.empty()) return;
+  if (q[0].kind == Backend::Pending::PROJECTION) {
+    if (q.size() == 2) {  // a projection and its bias (+ ReLU) in one launch
+      GemmEpilogue ep;
+      ep.bias = static_cast<const float *>(q[1].a.data);
+      ep.relu = q[1].kind == Backend::Pending::BIAS_RELU ? 1 : 0;
+      run_gemm(b, make_mat_view(&q[0].a, "gemm_ranked_matrix_rhs(a)"),
+               shared_matrix(&q[0].b, "gemm_ranked_matrix_rhs(b)"), make_mat_view(&q[0].c, "gemm_ranked_matrix_rhs(out)"),
+               "litnice_b200::gemm_ranked_matrix_rhs", ep);
+      ++b->fused_projections;
+    } else {
+      issue_one(b, q[0]);
+    }
+    return;
+  }
+  const long long heads = (long long)(q.size() / 3);  // complete (scores, softmax, context) triples
+  size_t done = 0;
+  if (heads >= 2) {
+    b->queue.swap(q);  // issue_heads_grouped reads the recorded calls through the instance
+    bool grouped = false;
+    try {
+      grouped = issue_heads_grouped(b, 0, heads);
+    } catch (...) {
+      b->queue.clear();
+      throw;
+    }
+    q.swap(b->queue);
+    if (grouped) done = (size_t)heads * 3;
+  }
+  for (size_t i = done; i < q.size(); ++i) issue_one(b, q[i]);
 }
 
 // ---- exec-context lanes ------------------------------------------------------------
@@ -578,31 +881,31 @@ void api_gemm_batched_rhs_t(void *h, LitniceView a, LitniceView bb, LitniceView 
 // only the nesting is validated.
 
 uint32_t api_supports_ctx(void *h) {
-  self(h);
+  self_recording(h);
   return 1u;
 }
 void api_start_iter(void *h) {
-  Backend *b = self(h);
+  Backend *b = self_recording(h);
   if (b->ctx_iteration) throw std::runtime_error("litnice_b200: exec context iteration already started");
   b->ctx_iteration = 1;
 }
 void api_finish_iter(void *h) {
-  Backend *b = self(h);
+  Backend *b = self_recording(h);
   if (!b->ctx_iteration || b->ctx_group) throw std::runtime_error("litnice_b200: exec context iteration not open");
   b->ctx_iteration = 0;
 }
 void api_start_group(void *h) {
-  Backend *b = self(h);
+  Backend *b = self_recording(h);
   if (!b->ctx_iteration || b->ctx_group) throw std::runtime_error("litnice_b200: exec context group misuse");
   b->ctx_group = 1;
 }
 void api_finish_group(void *h) {
-  Backend *b = self(h);
+  Backend *b = self_recording(h);
   if (!b->ctx_group) throw std::runtime_error("litnice_b200: exec context group not open");
   b->ctx_group = 0;
 }
 void require_group(void *h, const char *who) {
-  if (!self(h)->ctx_group) throw std::runtime_error(std::string(who) + ": no exec context group is open");
+  if (!self_recording(h)->ctx_group) throw std::runtime_error(std::string(who) + ": no exec context group is open");
 }
 void api_gemm_batched_ctx(void *h, LitniceView a, LitniceView bb, LitniceView out) {
   require_group(h, "litnice_b200::gemm_batched_exec_context");

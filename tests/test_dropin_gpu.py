@@ -79,6 +79,24 @@ def test_unmodified_litnicelm_cli_infer_on_plugin(ref, tmp_path):
     assert outs["cpu"] == outs["b200"]
 
 
+@pytest.mark.parametrize("attention", ATTENTION)
+@pytest.mark.parametrize("ffn", FFN)
+def test_deferred_operator_queue_changes_nothing(ref, attention, ffn):
+    """The plugin records the host's per-head attention calls and projection + bias pairs and issues
+    them merged (three launches for all heads, one per projection). With the queue off every call is
+    issued at once. Both must leave bit-identical logits: merging changes launch counts, not values."""
+    d = formats.ModelDims(2, 4, 64, 128, 40, 48)
+    arena = formats.make_param_arena(d, 77, bias_std=0.02, ln_std=0.1)
+    ids = formats.zipf_prompt(d.vocab, 37, 5)
+    merged, _ = ref.ref_run(d, arena, ids, backend_library=LIB_PATH, attention=attention, ffn=ffn)
+    plain, _ = ref.ref_run(d, arena, ids, backend_library=LIB_PATH, attention=attention, ffn=ffn,
+                           threads_env={"LITNICE_B200_ABI_QUEUE": "0"})
+    assert np.array_equal(merged, plain)
+    want, _ = ref.ref_run(d, arena, ids)        # the reference CPU plugin
+    scale = np.abs(want).max(axis=-1, keepdims=True)
+    assert float((np.abs(merged - want) / scale).max()) < 1e-3
+
+
 def test_reference_token_loop_on_plugin_config2_shape(ref):
     """The reference's own loop (whole-context forward, one copy_device2host per
     logits row, host-side argmax) at the config-2 shape on the plugin: same
@@ -88,11 +106,13 @@ def test_reference_token_loop_on_plugin_config2_shape(ref):
     arena = formats.make_param_arena(d, 1002)
     prompt = formats.zipf_prompt(d.vocab, 200, 4002)
     runs = {}
-    for tag, env in (("read-ahead", {}), ("row copies", {"LITNICE_B200_READ_AHEAD": "0"})):
+    for tag, env in (("read-ahead", {}), ("row copies", {"LITNICE_B200_READ_AHEAD": "0"}),
+                     ("read-ahead, every call issued at once", {"LITNICE_B200_ABI_QUEUE": "0"})):
         toks, _, secs, _ = ref.ref_run(d, arena, prompt, mode="generate", max_new=24, backend_library=LIB_PATH,
                                        attention="fused_inplace", ffn="inplace_fused_bias_relu", threads_env=env)
         runs[tag] = (toks, float(np.median(secs[2:])))
     assert np.array_equal(runs["read-ahead"][0], runs["row copies"][0])
+    assert np.array_equal(runs["read-ahead"][0], runs["read-ahead, every call issued at once"][0])
     assert len(runs["read-ahead"][0]) == 24
     for tag, (_, t) in runs.items():
         print(f"reference host loop on the plugin, context ~212, {tag}: {1e3 * t:.2f} ms per token")
