@@ -459,7 +459,8 @@ def run_b200_arm(args, rank, local_rank, world):
         prof = sess.profile_step(main["streams_this_rank"], s_mid, 3)
         isolated = prof.gemm_flops / (prof.gemm_ms * 1e-3) / 1e12 if prof.gemm_ms > 0 else 0.0
         in_loop = prof.gemm_span_flops / (prof.gemm_span_ms * 1e-3) / 1e12 if prof.gemm_span_ms > 0 else None
-        whole = whole_loop_flops(d, streams_total, plen, max_new) / (main["dev_ms_per_step"] * 1e-3) / 1e12
+        # per GPU: this rank's streams over this rank's time (every rank does the same amount of work)
+        whole = whole_loop_flops(d, main["streams_this_rank"], plen, max_new) / (main["dev_ms_per_step"] * 1e-3) / 1e12
         achieved = in_loop if in_loop is not None else isolated
         roofline = {
             "bound": "tensor",
@@ -471,8 +472,9 @@ def run_b200_arm(args, rank, local_rank, world):
             "ceiling_frac_3_products": 1.0 / 3.0,
             "executed_mma_frac": 3.0 * achieved / peaks["bf16_tflops"],
             "how": (f"in the loop: algorithmic 2*M*N*K flops of the {prof.gemm_span_launches} projection launches of "
-                    f"one step at context {s_mid} / the sum of their device-clock spans (earliest CTA start to "
-                    f"latest CTA end, {prof.gemm_span_ms:.3f} ms; launches overlap as in the token loop; "
+                    f"one step at context {s_mid} / the sum of their device-clock spans (from the completion of a "
+                    f"launch's predecessor to the end of its last CTA, {prof.gemm_span_ms:.3f} ms; no event between "
+                    f"the launches, which overlap as in the token loop; "
                     f"attention {prof.attn_span_launches} launches {prof.attn_span_ms:.3f} ms; whole step "
                     f"{prof.step_span_ms:.3f} ms)") if in_loop is not None else
                    "CUDA events around each launch (the device-clock spans need the tensor-core path)",
@@ -480,8 +482,8 @@ def run_b200_arm(args, rank, local_rank, world):
                          "how": f"{prof.gemm_launches} launches, CUDA events around each, {prof.gemm_ms:.3f} ms"},
             "whole_loop": {"achieved": whole, "frac": whole / peaks["bf16_tflops"],
                            "frac_of_sustained": whole / peaks["bf16_tflops_sustained"],
-                           "how": "all algorithmic flops of a generation (projections on every row, causal-useful "
-                                  "attention, head on the last rows) / ms_per_step"},
+                           "how": "all algorithmic flops of one GPU's generation (projections on every row, "
+                                  "causal-useful attention, head on the last rows) / ms_per_step"},
             "traffic": NCU_DRAM_BYTES_PER_GEMM_LAUNCH.get(args.workload),
             "traffic_source": ("profiles/gemm_tc_c2_context640_and_c5shape.md (ncu dram__bytes_read + write, mean "
                                "per projection launch at context 640)")
@@ -529,7 +531,8 @@ def run_b200_arm(args, rank, local_rank, world):
             r = measure_generation(box, name, 1, 1, sample_clocks=True)
             r["sess"].close()
             total = WORKLOADS[name][1] * (1 if r["scaling"] == "strong" else world)
-            wl = whole_loop_flops(r["dims"], total, r["plen"], r["max_new"]) / (r["dev_ms_per_step"] * 1e-3) / 1e12
+            wl = whole_loop_flops(r["dims"], r["streams_this_rank"], r["plen"], r["max_new"]) / \
+                (r["dev_ms_per_step"] * 1e-3) / 1e12   # per GPU
             extra["c5_split" if name == "c5" else name] = {
                 "workload": workload_name(name, r["streams_this_rank"], r["plen"], r["max_new"]),
                 "value": r["value"], "unit": "tokens/s", "scaling": r["scaling"],
