@@ -314,9 +314,13 @@ int litnice_b200_projection_time(int32_t engine, const float *a, int32_t m, int3
  * (ReLU when relu != 0), m <= 8, on host buffers: the M <= 8 case of
  * gemm_ranked_matrix_rhs (device_backend.cpp:1112-1131) as the output head uses it
  * on the last rows (output_head.cpp:58-70), followed by add_bias_rowwise / add /
- * relu (:840-908, 752-813, 978-1001). Allocates and frees its own device buffers. */
+ * relu (:840-908, 752-813, 978-1001). With ln_gamma and ln_beta ([k], both or
+ * neither) the rows of x pass through layernorm_forward (:1247-1279) first, inside
+ * the same kernel; only shapes the streaming kernel takes (EINVAL otherwise).
+ * Allocates and frees its own device buffers. */
 int litnice_b200_gemv_host(const float *x, int32_t m, const float *w, int32_t k, int32_t n,
-                           const float *bias, const float *residual, int32_t relu, float *out);
+                           const float *bias, const float *residual, int32_t relu, const float *ln_gamma,
+                           const float *ln_beta, float *out);
 
 /* Device time of that product. cold_l2 = 2: `repeats` calls back to back between one
  * pair of CUDA events, each on the next of a ring of weight copies larger than three

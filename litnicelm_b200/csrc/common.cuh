@@ -250,9 +250,13 @@ void launch_layernorm_dense(const float *x, const float *gamma, const float *bet
 size_t gemv_scratch_floats(int m, int n, int k);
 // residual ([m, n] dense, added after the bias) and relu finish the product as the layer wiring of
 // the reference does (add_bias_rowwise, add, relu).
+// ln_gamma / ln_beta ([k], only for shapes gemv_fuses_layernorm accepts): the rows of x pass through
+// LayerNorm (layernorm_forward of the reference) on their way into the product.
+bool gemv_fuses_layernorm(int n, int k);
 int launch_gemv(const float *x, int m, const float *w, int k, int n, const float *bias,
                 float *out, float *scratch, cudaStream_t st, DevErr *err = nullptr,
-                const float *residual = nullptr, int relu = 0);
+                const float *residual = nullptr, int relu = 0, const float *ln_gamma = nullptr,
+                const float *ln_beta = nullptr);
 
 // attention.cu: ctx[r, h*dh + :] for rows r = b*s + t of qkv [rows, 3*d].
 // ctx_lo != nullptr: ctx receives the TF32 high part and ctx_lo the low part.
@@ -284,9 +288,10 @@ void launch_embed_last_ln(const float *tok_emb, const float *pos_emb, const int 
                           const float *beta, float *x, float *ln, DevErr *err, cudaStream_t st);
 void launch_kv_store(const float *qkv, const LoopState *state, int s_host, int n_streams, int d, int cap, float *kc,
                      float *vc, cudaStream_t st);
-// Returns the number of kernels launched (2 when the keys are cut into chunks).
+// counters: one zero-resting int per (stream, head), needed when the keys are cut into chunks.
+// Returns the number of kernels launched.
 int launch_attn_decode(const float *qkv, float *kc, float *vc, int cap, int d_model, int n_heads, int n_streams,
-                       const LoopState *state, int s_host, float *part, float *ctx, cudaStream_t st);
+                       const LoopState *state, int s_host, float *part, int *counters, float *ctx, cudaStream_t st);
 
 // sampler.cu
 struct SamplerParams {

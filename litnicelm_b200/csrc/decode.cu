@@ -51,6 +51,7 @@ __global__ void embed_last_ln_kernel(const float *__restrict__ tok_emb, const fl
     xp[c] = v;
     sum += (double)v;
   }
+  if (ln == nullptr) return;  // the consumer normalises the row itself
   const double mean = warp_sum_d(sum) / (double)d;
   double var = 0.0;
   for (int c = lane; c < d; c += 32) {  // each lane re-reads the elements it wrote itself
@@ -89,12 +90,12 @@ __global__ void kv_store_kernel(const float *__restrict__ qkv, const LoopState *
 // (scaled_causal_softmax_rows, device_backend.cpp:1554-1592, restricted to one row) and
 // o = sum e_j v_j. The CTA whose chunk holds the newest position first appends that position's K
 // and V (this step's QKV row) to the caches. With one chunk the normalised context row is
-// written directly; otherwise (o, max, sum) go to `part` and attn_merge_kernel joins the chunks.
+// written directly; otherwise (o, max, sum) go to `part` and the chunk that finishes last joins them.
 template <int DH>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(const float *__restrict__ qkv, float *__restrict__ kc, float *__restrict__ vc, int cap,
                    int d_model, const LoopState *state, int s_host, int keys_per_chunk, float scale,
-                   float *__restrict__ part, float *__restrict__ ctx) {
+                   float *__restrict__ part, float *__restrict__ ctx, int *__restrict__ counters) {
   constexpr int LPK = DH / 8;      // lanes that share one key: 8 floats of the head each
   constexpr int KPI = 128 / LPK;   // keys per trip of the CTA
   constexpr int PARTS = 128 / DH;  // threads per output column in the second product
@@ -102,6 +103,7 @@ attn_decode_kernel(const float *__restrict__ qkv, float *__restrict__ kc, float 
   __shared__ float red_f[4];
   __shared__ double red_d[4];
   __shared__ float o_part[128];
+  __shared__ int is_last;
   pdl_launch_dependents();
   pdl_wait();
   const int s = state ? state->s : s_host;  // context length including the newest token
@@ -109,14 +111,14 @@ attn_decode_kernel(const float *__restrict__ qkv, float *__restrict__ kc, float 
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z, chunks = gridDim.x;
   const int c0 = c * keys_per_chunk, c1 = min(s, c0 + keys_per_chunk);
   float *out = part ? part + (((long long)b * gridDim.y + h) * chunks + c) * (DH + 2) : nullptr;
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   if (c0 >= s) {  // a launch sized for a longer context: nothing in this chunk
-    if (out != nullptr && threadIdx.x == 0) {
+    if (out == nullptr) return;
+    if (tid == 0) {
       out[DH] = -INFINITY;
       out[DH + 1] = 0.f;
     }
-    return;
-  }
-  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  } else {
   const float *row = qkv + (long long)b * 3 * d_model;
   if (p >= c0 && p < c1 && tid < DH / 4) {
     const float4 k4 = *reinterpret_cast<const float4 *>(row + d_model + h * DH + tid * 4);
@@ -187,28 +189,35 @@ attn_decode_kernel(const float *__restrict__ qkv, float *__restrict__ kc, float 
       }
     }
   }
-}
-
-// Joins the chunks of one (stream, head) in chunk order: the common maximum, every chunk's sums
-// rescaled to it, the context row normalised by the total.
-template <int DH>
-__global__ void attn_merge_kernel(const float *__restrict__ part, int chunks, int d_model, float *__restrict__ ctx) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  const float *p = part + ((long long)b * gridDim.x + h) * chunks * (DH + 2);
-  float m = -INFINITY;
-  for (int c = 0; c < chunks; ++c) m = fmaxf(m, p[c * (DH + 2) + DH]);
-  double l = 0.0;
-  float o = 0.f;
-  for (int c = 0; c < chunks; ++c) {
-    const float mc = p[c * (DH + 2) + DH];
-    if (mc == -INFINITY) continue;  // an empty chunk of a launch sized for a longer context
-    const float w = expf(mc - m);
-    l += (double)p[c * (DH + 2) + DH + 1] * (double)w;
-    o = fmaf(p[c * (DH + 2) + d], w, o);
+  }  // chunk with keys
+  if (out == nullptr) return;
+  // The chunk that finishes last joins all chunks of its (stream, head) in chunk order: the common
+  // maximum, every chunk's sums rescaled to it, the context row normalised by the total. The
+  // counter rests at zero between launches.
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    is_last = atomicAdd(&counters[b * gridDim.y + h], 1) == chunks - 1;
   }
-  ctx[(long long)b * d_model + h * DH + d] = o * (float)(1.0 / l);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (tid < DH) {
+    const float *pp = part + ((long long)b * gridDim.y + h) * chunks * (DH + 2);
+    float mm = -INFINITY;
+    for (int q = 0; q < chunks; ++q) mm = fmaxf(mm, __ldcg(&pp[q * (DH + 2) + DH]));
+    double ll = 0.0;
+    float oo = 0.f;
+    for (int q = 0; q < chunks; ++q) {
+      const float mc = __ldcg(&pp[q * (DH + 2) + DH]);
+      if (mc == -INFINITY) continue;  // an empty chunk of a launch sized for a longer context
+      const float w = expf(mc - mm);
+      ll += (double)__ldcg(&pp[q * (DH + 2) + DH + 1]) * (double)w;
+      oo = fmaf(__ldcg(&pp[q * (DH + 2) + tid]), w, oo);
+    }
+    ctx[(long long)b * d_model + h * DH + tid] = oo * (float)(1.0 / ll);
+    if (tid == 0) counters[b * gridDim.y + h] = 0;
+  }
 }
 
 }  // namespace
@@ -248,30 +257,28 @@ DecodeAttnPlan attn_decode_plan(int n_streams, int s, int n_heads, int dh) {
 template <int DH>
 static void launch_attn_decode_dh(const float *qkv, float *kc, float *vc, int cap, int d_model, int n_heads,
                                   int n_streams, const LoopState *state, int s_host, const DecodeAttnPlan &plan,
-                                  float *part, float *ctx, cudaStream_t st) {
+                                  float *part, int *counters, float *ctx, cudaStream_t st) {
   const float scale = 1.0f / sqrtf((float)DH);
   dim3 grid((unsigned)plan.chunks, (unsigned)n_heads, (unsigned)n_streams);
   float *pp = plan.chunks > 1 ? part : nullptr;
   launch_pdl(attn_decode_kernel<DH>, grid, dim3(128), (size_t)plan.keys_per_chunk * sizeof(float), st, g_pdl_enabled,
-             qkv, kc, vc, cap, d_model, state, s_host, plan.keys_per_chunk, scale, pp, ctx);
-  if (plan.chunks > 1)
-    launch_pdl(attn_merge_kernel<DH>, dim3((unsigned)n_heads, (unsigned)n_streams), dim3(DH), 0, st, g_pdl_enabled,
-               (const float *)part, plan.chunks, d_model, ctx);
+             qkv, kc, vc, cap, d_model, state, s_host, plan.keys_per_chunk, scale, pp, ctx, counters);
 }
 
 int launch_attn_decode(const float *qkv, float *kc, float *vc, int cap, int d_model, int n_heads, int n_streams,
-                       const LoopState *state, int s_host, float *part, float *ctx, cudaStream_t st) {
+                       const LoopState *state, int s_host, float *part, int *counters, float *ctx, cudaStream_t st) {
   const int dh = d_model / n_heads;
   const DecodeAttnPlan plan = attn_decode_plan(n_streams, s_host, n_heads, dh);
-  if (plan.chunks > 1 && part == nullptr) throw std::invalid_argument("litnice_b200: decode attention needs scratch");
+  if (plan.chunks > 1 && (part == nullptr || counters == nullptr))
+    throw std::invalid_argument("litnice_b200: decode attention needs scratch");
   switch (dh) {
-    case 16: launch_attn_decode_dh<16>(qkv, kc, vc, cap, d_model, n_heads, n_streams, state, s_host, plan, part, ctx, st); break;
-    case 32: launch_attn_decode_dh<32>(qkv, kc, vc, cap, d_model, n_heads, n_streams, state, s_host, plan, part, ctx, st); break;
-    case 64: launch_attn_decode_dh<64>(qkv, kc, vc, cap, d_model, n_heads, n_streams, state, s_host, plan, part, ctx, st); break;
-    case 128: launch_attn_decode_dh<128>(qkv, kc, vc, cap, d_model, n_heads, n_streams, state, s_host, plan, part, ctx, st); break;
+    case 16: launch_attn_decode_dh<16>(qkv, kc, vc, cap, d_model, n_heads, n_streams, state, s_host, plan, part, counters, ctx, st); break;
+    case 32: launch_attn_decode_dh<32>(qkv, kc, vc, cap, d_model, n_heads, n_streams, state, s_host, plan, part, counters, ctx, st); break;
+    case 64: launch_attn_decode_dh<64>(qkv, kc, vc, cap, d_model, n_heads, n_streams, state, s_host, plan, part, counters, ctx, st); break;
+    case 128: launch_attn_decode_dh<128>(qkv, kc, vc, cap, d_model, n_heads, n_streams, state, s_host, plan, part, counters, ctx, st); break;
     default: throw std::invalid_argument("litnice_b200: decode attention supports head dimensions 16, 32, 64, 128");
   }
-  return plan.chunks > 1 ? 2 : 1;
+  return 1;
 }
 
 }  // namespace lb

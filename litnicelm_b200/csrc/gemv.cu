@@ -235,11 +235,13 @@ __global__ void __launch_bounds__((GT_CONSUMERS + 1) * 32)
 gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap, int k, int n,
                 int k_per_split, const float *__restrict__ bias, float *__restrict__ out,
                 float *__restrict__ partial, DevErr *err, const float *__restrict__ residual, int relu,
-                int cluster_splits) {
+                int cluster_splits, const float *__restrict__ x_rows, const float *__restrict__ ln_gamma,
+                const float *__restrict__ ln_beta) {
   using S = GtShape<M, TN>;
   extern __shared__ __align__(1024) unsigned char gt_smem[];
   __shared__ __align__(8) unsigned long long bar_full[GT_STAGES], bar_empty[GT_STAGES];
   __shared__ int abort_flag;
+  __shared__ float2 ln_stat[M];  // (mean, 1/std) of each row of x when a LayerNorm is applied on the way in
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int n0 = blockIdx.x * TN;
@@ -287,6 +289,36 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
   } else {
     // Consumers: warp -> (column group, 4 rows of every stage); lane -> 4 columns.
     const int colg = wid % S::COLG, kg = wid / S::COLG;
+    if (ln_gamma != nullptr) {
+      // LayerNorm folded into the product's input (layernorm_forward followed by
+      // gemm_ranked_matrix_rhs, transformer_layer.cpp:58-60,84): warp i forms the statistics of
+      // row i over the whole of k exactly as the stand-alone kernel does (double sums in the same
+      // order, device_backend.cpp:1247-1279), and every value is normalised as it leaves its stage.
+      pdl_wait();  // x is the predecessor's output and is read here directly
+      if (wid < M) {
+        const float4 *xp = reinterpret_cast<const float4 *>(x_rows + (long long)wid * k);
+        const int n4 = k >> 2;
+        double sum = 0.0;
+        for (int c = lane; c < n4; c += 32) {
+          const float4 v = xp[c];
+          sum += (double)v.x + (double)v.y + (double)v.z + (double)v.w;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const double mean = sum / (double)k;
+        double var = 0.0;
+        for (int c = lane; c < n4; c += 32) {
+          const float4 v = xp[c];
+          const double a = v.x - mean, b = v.y - mean, cc = v.z - mean, e = v.w - mean;
+          var += a * a + b * b + cc * cc + e * e;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+        var /= (double)k;
+        if (lane == 0) ln_stat[wid] = make_float2((float)mean, 1.0f / sqrtf((float)var + 1e-5f));
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(GT_CONSUMERS * 32) : "memory");
+    }
     float acc[M][4];
 #pragma unroll
     for (int i = 0; i < M; ++i)
@@ -304,10 +336,23 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
 #pragma unroll
         for (int r = 0; r < 4; ++r)
           wv[r] = *reinterpret_cast<const float4 *>(wt + ((kg * 4 + r) * TN + colg * 128 + lane * 4) * 4);
+        float4 g4 = make_float4(1.f, 1.f, 1.f, 1.f), b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ln_gamma != nullptr) {
+          const int kk = kb + it * S::ROWS + kg * 4;
+          g4 = __ldg(reinterpret_cast<const float4 *>(ln_gamma + kk));
+          b4 = __ldg(reinterpret_cast<const float4 *>(ln_beta + kk));
+        }
 #pragma unroll
         for (int i = 0; i < M; ++i) {
           const float4 xv = *reinterpret_cast<const float4 *>(xs + i * S::ROWS + kg * 4);
-          const float xr[4] = {xv.x, xv.y, xv.z, xv.w};
+          float xr[4] = {xv.x, xv.y, xv.z, xv.w};
+          if (ln_gamma != nullptr) {
+            const float2 ms = ln_stat[i];
+            xr[0] = __fadd_rn(__fmul_rn((xr[0] - ms.x) * ms.y, g4.x), b4.x);
+            xr[1] = __fadd_rn(__fmul_rn((xr[1] - ms.x) * ms.y, g4.y), b4.y);
+            xr[2] = __fadd_rn(__fmul_rn((xr[2] - ms.x) * ms.y, g4.z), b4.z);
+            xr[3] = __fadd_rn(__fmul_rn((xr[3] - ms.x) * ms.y, g4.w), b4.w);
+          }
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
             acc[i][0] = fmaf(xr[r], wv[r].x, acc[i][0]);
@@ -437,7 +482,8 @@ bool gt_aligned(const void *a, const void *b, const void *c, const void *d) {
 
 template <int M, int TN>
 void launch_gt(const CUtensorMap &map, const CUtensorMap &xmap, int k, int n, const GtPlan &p, const float *bias,
-               float *out, float *partial, DevErr *err, const float *residual, int relu, cudaStream_t st) {
+               float *out, float *partial, DevErr *err, const float *residual, int relu, const float *x,
+               const float *ln_gamma, const float *ln_beta, cudaStream_t st) {
   using S = GtShape<M, TN>;
   static std::mutex mu;
   static bool configured[64] = {};
@@ -453,19 +499,20 @@ void launch_gt(const CUtensorMap &map, const CUtensorMap &xmap, int k, int n, co
   dim3 grid((n + TN - 1) / TN, 1, p.splits);
   launch_pdl_cluster(gemv_tma_kernel<M, TN>, grid, dim3((GT_CONSUMERS + 1) * 32), (size_t)S::TOTAL, st, g_pdl_enabled,
                      p.cluster ? (unsigned)p.splits : 1u, map, xmap, k, n, p.k_per_split, bias, out, partial, err,
-                     residual, relu, p.cluster ? p.splits : 1);
+                     residual, relu, p.cluster ? p.splits : 1, x, ln_gamma, ln_beta);
 }
 
 template <int M>
 int launch_gt_m(const float *x, const float *w, int k, int n, const GtPlan &p, const float *bias, float *out,
-                float *scratch, DevErr *err, const float *residual, int relu, cudaStream_t st) {
+                float *scratch, DevErr *err, const float *residual, int relu, const float *ln_gamma,
+                const float *ln_beta, cudaStream_t st) {
   CUtensorMap map, xmap;
   const unsigned rows = p.tn == 128 ? 32u : 16u;
   tc_make_map_plain(&map, w, (unsigned long long)k, (unsigned long long)n, rows, (unsigned)p.tn);
   tc_make_map_plain(&xmap, x, (unsigned long long)M, (unsigned long long)k, (unsigned)M, rows);
   float *partial = (p.splits > 1 && !p.cluster) ? scratch : nullptr;
-  if (p.tn == 128) launch_gt<M, 128>(map, xmap, k, n, p, bias, out, partial, err, residual, relu, st);
-  else launch_gt<M, 256>(map, xmap, k, n, p, bias, out, partial, err, residual, relu, st);
+  if (p.tn == 128) launch_gt<M, 128>(map, xmap, k, n, p, bias, out, partial, err, residual, relu, x, ln_gamma, ln_beta, st);
+  else launch_gt<M, 256>(map, xmap, k, n, p, bias, out, partial, err, residual, relu, x, ln_gamma, ln_beta, st);
   if (partial != nullptr) {
     const long long total = (long long)M * n;
     launch_pdl(gemv_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, g_pdl_enabled,
@@ -487,20 +534,25 @@ size_t gemv_scratch_floats(int m, int n, int k) {
   return streaming > plain ? streaming : plain;
 }
 
+bool gemv_fuses_layernorm(int n, int k) { return gt_plan(n, k).tn != 0; }
+
 int launch_gemv(const float *x, int m, const float *w, int k, int n, const float *bias,
-                float *out, float *scratch, cudaStream_t st, DevErr *err, const float *residual, int relu) {
+                float *out, float *scratch, cudaStream_t st, DevErr *err, const float *residual, int relu,
+                const float *ln_gamma, const float *ln_beta) {
   if (m > 8) throw std::invalid_argument("launch_gemv: m must be <= 8");
   const GtPlan p = gt_plan(n, k);
   const bool needs_scratch = p.splits > 1 && !p.cluster;
-  if (p.tn != 0 && gt_aligned(x, w, out, bias) && gt_aligned(residual, x, x, x) &&
+  if (p.tn != 0 && gt_aligned(x, w, out, bias) && gt_aligned(residual, ln_gamma, ln_beta, x) &&
       (!needs_scratch || (scratch != nullptr && gt_aligned(scratch, x, x, x)))) {
     switch (pad_m(m)) {
-      case 1: return launch_gt_m<1>(x, w, k, n, p, bias, out, scratch, err, residual, relu, st);
-      case 2: return launch_gt_m<2>(x, w, k, n, p, bias, out, scratch, err, residual, relu, st);
-      case 4: return launch_gt_m<4>(x, w, k, n, p, bias, out, scratch, err, residual, relu, st);
-      default: return launch_gt_m<8>(x, w, k, n, p, bias, out, scratch, err, residual, relu, st);
+      case 1: return launch_gt_m<1>(x, w, k, n, p, bias, out, scratch, err, residual, relu, ln_gamma, ln_beta, st);
+      case 2: return launch_gt_m<2>(x, w, k, n, p, bias, out, scratch, err, residual, relu, ln_gamma, ln_beta, st);
+      case 4: return launch_gt_m<4>(x, w, k, n, p, bias, out, scratch, err, residual, relu, ln_gamma, ln_beta, st);
+      default: return launch_gt_m<8>(x, w, k, n, p, bias, out, scratch, err, residual, relu, ln_gamma, ln_beta, st);
     }
   }
+  if (ln_gamma != nullptr)
+    throw std::invalid_argument("launch_gemv: a LayerNorm on the way in needs a shape the streaming kernel takes");
   return launch_gemv_plain(x, m, w, k, n, bias, out, scratch, st, residual, relu);
 }
 
@@ -587,7 +639,8 @@ extern "C" int litnice_b200_gemv_noalloc(const float *x, int32_t m, const float 
 // ---------------------------------------------------------------------------
 
 extern "C" int litnice_b200_gemv_host(const float *x, int32_t m, const float *w, int32_t k, int32_t n,
-                                      const float *bias, const float *residual, int32_t relu, float *out) {
+                                      const float *bias, const float *residual, int32_t relu, const float *ln_gamma,
+                                      const float *ln_beta, float *out) {
   using namespace lb;
   if (x == nullptr || w == nullptr || out == nullptr || m <= 0 || m > 8 || k <= 0 || n <= 0) return LITNICE_B200_EINVAL;
   std::vector<void *> owned;
@@ -619,7 +672,19 @@ extern "C" int litnice_b200_gemv_host(const float *x, int32_t m, const float *w,
       LB_CUDA(cudaMemset(dr, 0, (size_t)mp * n * 4));
       LB_CUDA(cudaMemcpy(dr, residual, (size_t)m * n * 4, cudaMemcpyHostToDevice));
     }
-    launch_gemv(dx, m, dw, k, n, db, dout, scr, nullptr, err_dev, dr, relu);
+    float *dg = nullptr, *dbeta = nullptr;
+    if (ln_gamma != nullptr && ln_beta != nullptr) {
+      if (!gemv_fuses_layernorm(n, k)) {
+        for (void *p : owned) cudaFree(p);
+        cudaFreeHost(err_host);
+        return LITNICE_B200_EINVAL;
+      }
+      dg = dev_alloc((size_t)k * 4);
+      dbeta = dev_alloc((size_t)k * 4);
+      LB_CUDA(cudaMemcpy(dg, ln_gamma, (size_t)k * 4, cudaMemcpyHostToDevice));
+      LB_CUDA(cudaMemcpy(dbeta, ln_beta, (size_t)k * 4, cudaMemcpyHostToDevice));
+    }
+    launch_gemv(dx, m, dw, k, n, db, dout, scr, nullptr, err_dev, dr, relu, dg, dbeta);
     LB_CUDA(cudaDeviceSynchronize());
     LB_CUDA(cudaMemcpy(out, dout, (size_t)m * n * 4, cudaMemcpyDeviceToHost));
     if (err_host->code != DEVERR_NONE) rc = LITNICE_B200_EDEVICE;

@@ -195,6 +195,7 @@ struct litnice_b200_session {
   // step computes one new row per stream (decode.cu). Runs on the fp32 kernels: the whole-context
   // pass over the prompt that fills the caches on the SIMT path, the steps on the few-row products.
   bool kv = false;
+  bool kv_fuse = true;  // LayerNorms inside the products, one-launch greedy tail (LITNICE_B200_KV_FUSE=0: kernels of their own)
   float *kcache = nullptr, *vcache = nullptr;
   int kv_cap = 0, kv_streams = 0;
   int kv_len = 0;         // positions of the current streams held in the caches
@@ -202,6 +203,7 @@ struct litnice_b200_session {
   float *dx = nullptr, *dy = nullptr, *dln = nullptr, *dqkv = nullptr, *dctx = nullptr, *dh = nullptr;  // step rows
   float *dec_part = nullptr;  // partial attention sums of the key chunks
   size_t dec_part_floats = 0;
+  int *dec_counters = nullptr;  // per (stream, head): chunks finished; rests at zero
 
   bool keep_logits = false;
   float *step_logits = nullptr;
@@ -594,12 +596,22 @@ void enqueue_head_last(litnice_b200_session *s, int B, int sl, const LoopState *
   }
 }
 
-// Cached mode: one projection of the step's rows, out[B, n] = a[B, k] W + bias (+ residual) (ReLU):
-// the few-row kernels up to 8 streams, the fp32 tile kernel beyond.
+// Cached mode: one projection of the step's rows, out[B, n] = LN?(a)[B, k] W + bias (+ residual) (ReLU):
+// the few-row kernels up to 8 streams (with the LayerNorm in front of the product applied inside the
+// kernel where its shape allows), the fp32 tile kernel beyond. ln_g / ln_b: that LayerNorm, or null;
+// ln_out: where its rows go when it has to run as a kernel of its own.
 void decode_projection(litnice_b200_session *s, const float *a, int B, int k, const float *w, int n, const float *bias,
-                       const float *residual, int relu, float *out) {
+                       const float *residual, int relu, float *out, const float *ln_g = nullptr,
+                       const float *ln_b = nullptr, float *ln_out = nullptr) {
+  const bool fuse_ln = ln_g != nullptr && B <= 8 && s->kv_fuse && gemv_fuses_layernorm(n, k);
+  if (ln_g != nullptr && !fuse_ln) {
+    launch_layernorm_dense(a, ln_g, ln_b, B, k, ln_out, nullptr, nullptr, B, s->st);
+    ++s->launches;
+    a = ln_out;
+  }
   if (B <= 8) {
-    s->launches += launch_gemv(a, B, w, k, n, bias, out, s->gemv_scratch, s->st, s->err_dev, residual, relu);
+    s->launches += launch_gemv(a, B, w, k, n, bias, out, s->gemv_scratch, s->st, s->err_dev, residual, relu,
+                               fuse_ln ? ln_g : nullptr, fuse_ln ? ln_b : nullptr);
     return;
   }
   GemmEpilogue ep;
@@ -611,33 +623,36 @@ void decode_projection(litnice_b200_session *s, const float *a, int B, int k, co
 }
 
 // Cached mode: the forward pass of the newest row of every stream at context length sl
-// (transformer_layer.cpp:50-92 for one row; attention over the cached positions and the new one),
-// ending with the last-row logits in s->logits.
-void enqueue_decode_step(litnice_b200_session *s, int B, int sl, const LoopState *dstate) {
+// (transformer_layer.cpp:50-92 for one row; attention over the cached positions and the new one).
+// with_head: ends with the last-row logits in s->logits; otherwise the final hidden rows stay in
+// s->dx for a tail kernel that applies the final norm and the head itself.
+void enqueue_decode_step(litnice_b200_session *s, int B, int sl, const LoopState *dstate, bool with_head) {
   const litnice_b200_dims &d = s->dims;
   const int D = d.d_model, F = d.d_ff, V = d.vocab_size;
   const size_t layer = (size_t)s->kv_streams * s->kv_cap * D;
+  // the newest row's embedding; its first LayerNorm only when the QKV product cannot apply it itself
+  const bool ln_in_qkv = B <= 8 && s->kv_fuse && gemv_fuses_layernorm(3 * D, D);
   launch_embed_last_ln(P(s, s->lay.tok_emb), P(s, s->lay.pos_emb), s->ids, d.max_seq_len, dstate, sl, B, D, V,
-                       P(s, s->lay.layer[0].ln1_g), P(s, s->lay.layer[0].ln1_b), s->dx, s->dln, s->err_dev, s->st);
+                       P(s, s->lay.layer[0].ln1_g), P(s, s->lay.layer[0].ln1_b), s->dx, ln_in_qkv ? nullptr : s->dln,
+                       s->err_dev, s->st);
   ++s->launches;
   for (int l = 0; l < d.n_layers; ++l) {
     const LayerOff &o = s->lay.layer[l];
-    if (l > 0) {
-      launch_layernorm_dense(s->dx, P(s, o.ln1_g), P(s, o.ln1_b), B, D, s->dln, nullptr, nullptr, B, s->st);
-      ++s->launches;
-    }
-    decode_projection(s, s->dln, B, D, P(s, o.qkv_w), 3 * D, P(s, o.qkv_b), nullptr, 0, s->dqkv);
+    if (l == 0 && !ln_in_qkv)
+      decode_projection(s, s->dln, B, D, P(s, o.qkv_w), 3 * D, P(s, o.qkv_b), nullptr, 0, s->dqkv);
+    else
+      decode_projection(s, s->dx, B, D, P(s, o.qkv_w), 3 * D, P(s, o.qkv_b), nullptr, 0, s->dqkv, P(s, o.ln1_g),
+                        P(s, o.ln1_b), s->dln);
     s->launches += launch_attn_decode(s->dqkv, s->kcache + l * layer, s->vcache + l * layer, s->kv_cap, D, d.n_heads, B,
-                                      dstate, sl, s->dec_part, s->dctx, s->st);
+                                      dstate, sl, s->dec_part, s->dec_counters, s->dctx, s->st);
     decode_projection(s, s->dctx, B, D, P(s, o.out_w), D, P(s, o.out_b), s->dx, 0, s->dy);
-    launch_layernorm_dense(s->dy, P(s, o.ln2_g), P(s, o.ln2_b), B, D, s->dln, nullptr, nullptr, B, s->st);
-    ++s->launches;
-    decode_projection(s, s->dln, B, D, P(s, o.w1), F, P(s, o.b1), nullptr, 1, s->dh);
+    decode_projection(s, s->dy, B, D, P(s, o.w1), F, P(s, o.b1), nullptr, 1, s->dh, P(s, o.ln2_g), P(s, o.ln2_b),
+                      s->dln);
     decode_projection(s, s->dh, B, F, P(s, o.w2), D, P(s, o.b2), s->dy, 0, s->dx);
   }
-  launch_layernorm_dense(s->dx, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), B, D, s->xl, nullptr, nullptr, B, s->st);
-  ++s->launches;
-  decode_projection(s, s->xl, B, D, P(s, s->lay.lm_head), V, nullptr, nullptr, 0, s->logits);
+  if (!with_head) return;
+  decode_projection(s, s->dx, B, D, P(s, s->lay.lm_head), V, nullptr, nullptr, 0, s->logits, P(s, s->lay.lnf_g),
+                    P(s, s->lay.lnf_b), s->xl);
 }
 
 // Cached mode: caches for n_streams streams of up to cap positions, and the scratch of the
@@ -664,6 +679,11 @@ void ensure_kv(litnice_b200_session *s, int B, int cap) {
   for (int sl = 64; sl <= (cap + 63) / 64 * 64; sl += 64) {
     const size_t f = attn_decode_plan(B, sl, d.n_heads, d.d_model / d.n_heads).scratch_floats;
     if (f > need) need = f;
+  }
+  if (s->dec_counters == nullptr) {
+    const size_t n = (size_t)s->max_streams * d.n_heads;
+    if (cudaMalloc(reinterpret_cast<void **>(&s->dec_counters), n * 4) != cudaSuccess) throw std::bad_alloc();
+    LB_CUDA(cudaMemsetAsync(s->dec_counters, 0, n * 4, s->st));
   }
   if (need > s->dec_part_floats) {
     LB_CUDA(cudaStreamSynchronize(s->st));
@@ -870,6 +890,8 @@ static int session_create_impl(const litnice_b200_dims *dims, int32_t max_stream
     s->fused_tail = !(tail_env && tail_env[0] == '0');
     const char *kv_env = std::getenv("LITNICE_B200_KV_CACHE");
     s->kv = kv_env && kv_env[0] == '1';
+    const char *kvf_env = std::getenv("LITNICE_B200_KV_FUSE");
+    s->kv_fuse = !(kvf_env && kvf_env[0] == '0');
     const char *tc_env = std::getenv("LITNICE_B200_TC");
     s->tc = !s->kv && !(tc_env && tc_env[0] == '0') && tc_runtime_available() && d.d_model % 64 == 0 &&
             d.d_ff % 64 == 0;
@@ -942,6 +964,7 @@ void litnice_b200_session_destroy(litnice_b200_session *s) {
     if (g.exec) cudaGraphExecDestroy(g.exec);
   for (float *p : {s->kcache, s->vcache, s->dx, s->dy, s->dln, s->dqkv, s->dctx, s->dh, s->dec_part})
     if (p) cudaFree(p);
+  if (s->dec_counters) cudaFree(s->dec_counters);
   if (s->xl_lo) cudaFree(s->xl_lo);
   if (s->tc_scratch) cudaFree(s->tc_scratch);
   if (s->attn_timeline) cudaFree(s->attn_timeline);
@@ -1160,9 +1183,19 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
     const bool graphs = s->use_graphs && !s->keep_logits;
     const bool fused_tail =
         greedy && !s->keep_logits && s->fused_tail && !s->kv && head_greedy_supports(B, s->dims.d_model, V);
+    // cached mode, greedy, few streams, small vocabulary: the step ends in the one-launch tail too
+    const bool decode_tail = s->kv && s->kv_fuse && greedy && !s->keep_logits && s->fused_tail &&
+                             head_greedy_supports(B, s->dims.d_model, V);
     auto enqueue_step = [&](int sl_cap, const LoopState *dstate, int step, bool decode) {
       if (decode) {
-        enqueue_decode_step(s, B, sl_cap, dstate);
+        enqueue_decode_step(s, B, sl_cap, dstate, !decode_tail);
+        if (decode_tail) {  // the step's rows are the last rows: one row per stream
+          launch_head_greedy(s->dx, P(s, s->lay.lnf_g), P(s, s->lay.lnf_b), P(s, s->lay.lm_head), s->dims.d_model, V, B,
+                             1, nullptr, s->state, reinterpret_cast<unsigned *>(s->state + 1), s->ids,
+                             s->dims.max_seq_len, s->out_tokens, s->out_cap, s->logits, s->st);
+          ++s->launches;
+          return;
+        }
       } else {
         s->kv_store = s->kv;
         try {

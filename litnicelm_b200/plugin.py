@@ -169,13 +169,14 @@ def projection_time(m: int, k: int, n: int, repeats: int = 20, engine: int = 1,
 
 def gemv_host(x: np.ndarray, w: np.ndarray, bias: Optional[np.ndarray] = None,
               residual: Optional[np.ndarray] = None, relu: bool = False,
+              ln: Optional[Tuple[np.ndarray, np.ndarray]] = None,
               lib: Optional[C.CDLL] = None) -> np.ndarray:
     """out[m, n] = x[m, k] . W[k, n] (+ bias) (+ residual) (ReLU) for m <= 8 on the few-row
     kernels of the output head (litnice_b200_gemv_host: host buffers in, host buffer out)."""
     lib = lib or load_library()
     f32p = C.POINTER(C.c_float)
     fn = lib.litnice_b200_gemv_host
-    fn.argtypes = [f32p, C.c_int32, f32p, C.c_int32, C.c_int32, f32p, f32p, C.c_int32, f32p]
+    fn.argtypes = [f32p, C.c_int32, f32p, C.c_int32, C.c_int32, f32p, f32p, C.c_int32, f32p, f32p, f32p]
     fn.restype = C.c_int
     x = np.ascontiguousarray(x, np.float32)
     w = np.ascontiguousarray(w, np.float32)
@@ -190,7 +191,12 @@ def gemv_host(x: np.ndarray, w: np.ndarray, bias: Optional[np.ndarray] = None,
     if residual is not None:
         residual = np.ascontiguousarray(residual, np.float32)
         r = residual.ctypes.data_as(f32p)
-    rc = fn(x.ctypes.data_as(f32p), m, w.ctypes.data_as(f32p), k, n, b, r, 1 if relu else 0,
+    g = be = None
+    if ln is not None:   # (gamma, beta): the rows of x pass through LayerNorm inside the kernel
+        gamma = np.ascontiguousarray(ln[0], np.float32).ravel()
+        beta = np.ascontiguousarray(ln[1], np.float32).ravel()
+        g, be = gamma.ctypes.data_as(f32p), beta.ctypes.data_as(f32p)
+    rc = fn(x.ctypes.data_as(f32p), m, w.ctypes.data_as(f32p), k, n, b, r, 1 if relu else 0, g, be,
             out.ctypes.data_as(f32p))
     if rc != 0:
         raise RuntimeError(f"litnice_b200_gemv_host failed with status {rc}")

@@ -77,3 +77,24 @@ def test_a_wait_that_nothing_completes_gives_up_and_reports():
     assert fn(5000, C.byref(code), C.byref(detail), C.byref(waited)) == -1   # limits above 1 ms are refused
     x = np.ones((1, 64), np.float32)
     assert np.array_equal(gemv_host(x, np.ones((64, 8), np.float32)), np.full((1, 8), 64.0, np.float32))
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 512, 1536), (1, 512, 2048), (8, 1024, 32000), (3, 1000, 512), (1, 1024, 4096)])
+def test_layernorm_on_the_way_in_matches_oracle(oracle, m, k, n):
+    """layernorm_forward followed by gemm_ranked_matrix_rhs + add_bias_rowwise + relu
+    (transformer_layer.cpp:58-60,84 and the FFN) as one kernel: the statistics keep the
+    reference's widths, so the normalised rows equal the stand-alone LayerNorm's and the
+    product differs from the oracle's only by its summation order."""
+    rng = np.random.default_rng(k + n)
+    x = (rng.standard_normal((m, k)) * 2 + 0.5).astype(np.float32)
+    w = (rng.standard_normal((k, n), dtype=np.float32) * 0.02).astype(np.float32)
+    b = rng.standard_normal(n, dtype=np.float32)
+    gamma = (1 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    beta = (0.1 * rng.standard_normal(k)).astype(np.float32)
+    xn = oracle.layernorm(x, gamma, beta)
+    want = np.maximum(oracle.gemm(xn, w) + b[None, :], 0)
+    got = gemv_host(x, w, b, relu=True, ln=(gamma, beta))
+    tol = 2e-5 * np.sqrt(k) * float(np.abs(xn).max()) * float(np.abs(w).max())
+    assert float(np.abs(got - want).max()) <= tol
+    # and bit-identical to the same kernel fed the oracle's normalised rows
+    assert np.array_equal(got, gemv_host(xn, w, b, relu=True))
