@@ -293,6 +293,33 @@ void launch_kv_store(const float *qkv, const LoopState *state, int s_host, int n
 int launch_attn_decode(const float *qkv, float *kc, float *vc, int cap, int d_model, int n_heads, int n_streams,
                        const LoopState *state, int s_host, float *part, int *counters, float *ctx, cudaStream_t st);
 
+// decode_persistent.cu: cached mode, greedy, up to 8 streams: `steps` tokens in one resident kernel
+// (cooperative launch, one CTA per SM, grid-wide barriers between the operators).
+struct DecodePersistentArgs {
+  const char *params;                 // parameter arena (device)
+  const unsigned long long *offsets;  // device: [n_layers][12] byte offsets in LayerOff order, then
+                                      // tok_emb, pos_emb, lnf_g, lnf_b, lm_head
+  int n_layers, n_heads, d_model, d_ff, vocab, max_seq, n_streams;
+  float *kcache, *vcache;
+  int cap;
+  unsigned long long layer_stride;    // floats between the layers of a cache
+  int *ids;
+  int ids_ld;
+  int *out_tokens;
+  int out_ld;
+  LoopState *state;
+  float *logits;     // [n_streams, vocab] last step's logits
+  float *scratch;    // decode_persistent_scratch_floats(...)
+  unsigned *barrier; // two words
+  int s0, step0, steps;  // context length of the first step (including its new token), tokens made so far
+  int sm_count;
+  DevErr *err;
+  unsigned long long *timeline;  // measurement aid (64 device words) or null
+};
+bool decode_persistent_supports(int n_streams, int n_heads, int d_model, int d_ff, int vocab);
+size_t decode_persistent_scratch_floats(int n_streams, int n_heads, int d_model, int d_ff, int vocab, int sm_count);
+void launch_decode_persistent(const DecodePersistentArgs &a, cudaStream_t st);
+
 // sampler.cu
 struct SamplerParams {
   float temp;

@@ -204,6 +204,14 @@ struct litnice_b200_session {
   float *dec_part = nullptr;  // partial attention sums of the key chunks
   size_t dec_part_floats = 0;
   int *dec_counters = nullptr;  // per (stream, head): chunks finished; rests at zero
+  // greedy runs of up to 8 streams: all steps after the first in one resident kernel
+  // (decode_persistent.cu; LITNICE_B200_KV_PERSIST=0 keeps one graph replay per token)
+  bool kv_persist = true;
+  int sm_count = 0;
+  unsigned long long *pk_offsets = nullptr;  // device table of parameter offsets
+  float *pk_scratch = nullptr;
+  size_t pk_scratch_floats = 0;
+  unsigned *pk_barrier = nullptr;
 
   bool keep_logits = false;
   float *step_logits = nullptr;
@@ -680,6 +688,17 @@ void ensure_kv(litnice_b200_session *s, int B, int cap) {
     const size_t f = attn_decode_plan(B, sl, d.n_heads, d.d_model / d.n_heads).scratch_floats;
     if (f > need) need = f;
   }
+  if (s->kv_persist && B <= 8 && decode_persistent_supports(B, d.n_heads, d.d_model, d.d_ff, d.vocab_size)) {
+    const size_t need_pk = decode_persistent_scratch_floats(B, d.n_heads, d.d_model, d.d_ff, d.vocab_size, s->sm_count);
+    if (need_pk > s->pk_scratch_floats) {
+      LB_CUDA(cudaStreamSynchronize(s->st));
+      if (s->pk_scratch) cudaFree(s->pk_scratch);
+      s->pk_scratch = nullptr;
+      s->pk_scratch_floats = 0;
+      if (cudaMalloc(reinterpret_cast<void **>(&s->pk_scratch), need_pk * 4) != cudaSuccess) throw std::bad_alloc();
+      s->pk_scratch_floats = need_pk;
+    }
+  }
   if (s->dec_counters == nullptr) {
     const size_t n = (size_t)s->max_streams * d.n_heads;
     if (cudaMalloc(reinterpret_cast<void **>(&s->dec_counters), n * 4) != cudaSuccess) throw std::bad_alloc();
@@ -892,6 +911,20 @@ static int session_create_impl(const litnice_b200_dims *dims, int32_t max_stream
     s->kv = kv_env && kv_env[0] == '1';
     const char *kvf_env = std::getenv("LITNICE_B200_KV_FUSE");
     s->kv_fuse = !(kvf_env && kvf_env[0] == '0');
+    const char *kvp_env = std::getenv("LITNICE_B200_KV_PERSIST");
+    s->kv_persist = !(kvp_env && kvp_env[0] == '0') && prop.cooperativeLaunch != 0;
+    s->sm_count = prop.multiProcessorCount;
+    if (s->kv) {
+      std::vector<unsigned long long> offs;
+      for (const LayerOff &o : s->lay.layer)
+        for (size_t v : {o.ln1_g, o.ln1_b, o.qkv_w, o.qkv_b, o.out_w, o.out_b, o.ln2_g, o.ln2_b, o.w1, o.b1, o.w2, o.b2})
+          offs.push_back((unsigned long long)v);
+      for (size_t v : {s->lay.tok_emb, s->lay.pos_emb, s->lay.lnf_g, s->lay.lnf_b, s->lay.lm_head})
+        offs.push_back((unsigned long long)v);
+      must(cudaMalloc(reinterpret_cast<void **>(&s->pk_offsets), offs.size() * 8));
+      LB_CUDA(cudaMemcpy(s->pk_offsets, offs.data(), offs.size() * 8, cudaMemcpyHostToDevice));
+      must(cudaMalloc(reinterpret_cast<void **>(&s->pk_barrier), 16));
+    }
     const char *tc_env = std::getenv("LITNICE_B200_TC");
     s->tc = !s->kv && !(tc_env && tc_env[0] == '0') && tc_runtime_available() && d.d_model % 64 == 0 &&
             d.d_ff % 64 == 0;
@@ -965,6 +998,9 @@ void litnice_b200_session_destroy(litnice_b200_session *s) {
   for (float *p : {s->kcache, s->vcache, s->dx, s->dy, s->dln, s->dqkv, s->dctx, s->dh, s->dec_part})
     if (p) cudaFree(p);
   if (s->dec_counters) cudaFree(s->dec_counters);
+  if (s->pk_offsets) cudaFree(s->pk_offsets);
+  if (s->pk_scratch) cudaFree(s->pk_scratch);
+  if (s->pk_barrier) cudaFree(s->pk_barrier);
   if (s->xl_lo) cudaFree(s->xl_lo);
   if (s->tc_scratch) cudaFree(s->tc_scratch);
   if (s->attn_timeline) cudaFree(s->attn_timeline);
@@ -1229,6 +1265,56 @@ int litnice_b200_run(litnice_b200_session *s, int32_t max_new, const litnice_b20
       // cached mode: a step on one new row per stream when the caches hold every earlier
       // position, else a whole-context pass that also fills them (the first step of a batch)
       const bool decode = s->kv && s->kv_len == sl - 1;
+      if (decode && s->kv_persist && greedy && !s->keep_logits && B <= 8 && s->pk_scratch != nullptr &&
+          decode_persistent_supports(B, s->dims.n_heads, s->dims.d_model, s->dims.d_ff, V)) {
+        // every remaining step in one resident kernel
+        DecodePersistentArgs a{};
+        a.params = s->params;
+        a.offsets = s->pk_offsets;
+        a.n_layers = s->dims.n_layers;
+        a.n_heads = s->dims.n_heads;
+        a.d_model = s->dims.d_model;
+        a.d_ff = s->dims.d_ff;
+        a.vocab = V;
+        a.max_seq = s->dims.max_seq_len;
+        a.n_streams = B;
+        a.kcache = s->kcache;
+        a.vcache = s->vcache;
+        a.cap = s->kv_cap;
+        a.layer_stride = (unsigned long long)s->kv_streams * s->kv_cap * s->dims.d_model;
+        a.ids = s->ids;
+        a.ids_ld = s->dims.max_seq_len;
+        a.out_tokens = s->out_tokens;
+        a.out_ld = s->out_cap;
+        a.state = s->state;
+        a.logits = s->logits;
+        a.scratch = s->pk_scratch;
+        a.barrier = s->pk_barrier;
+        a.s0 = sl;
+        a.step0 = s->cur_tokens + step;
+        a.steps = steps - step;
+        a.sm_count = s->sm_count;
+        a.err = s->err_dev;
+        unsigned long long *tl = nullptr;
+        if (std::getenv("LITNICE_B200_PK_TIMELINE") != nullptr && steps - step > 11) {
+          if (cudaMalloc(reinterpret_cast<void **>(&tl), 64 * 8) != cudaSuccess) throw std::bad_alloc();
+          LB_CUDA(cudaMemsetAsync(tl, 0, 64 * 8, s->st));
+        }
+        a.timeline = tl;
+        launch_decode_persistent(a, s->st);
+        if (tl != nullptr) {  // measurement aid: the phases of one token of CTA 0, ns from the token's start
+          unsigned long long h[64];
+          LB_CUDA(cudaMemcpyAsync(h, tl, sizeof(h), cudaMemcpyDeviceToHost, s->st));
+          LB_CUDA(cudaStreamSynchronize(s->st));
+          cudaFree(tl);
+          std::fprintf(stderr, "resident decode kernel, token 11 of CTA 0 (ns):");
+          for (int i = 1; i < 64 && h[i] != 0; ++i) std::fprintf(stderr, " %lld", (long long)(h[i] - h[0]));
+          std::fprintf(stderr, "\n");
+        }
+        ++s->launches;
+        s->kv_len = s0 + steps - 1;
+        break;
+      }
       if (s->kv) s->kv_len = sl;
       if (!graphs || (s->kv && !decode)) {
         enqueue_step(sl, nullptr, step, decode);
