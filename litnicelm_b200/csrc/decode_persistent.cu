@@ -34,6 +34,7 @@ namespace {
 constexpr int PK_THREADS = 256;
 constexpr int PK_WARPS = PK_THREADS / 32;
 constexpr int PK_BATCH = 8;  // weight loads a thread has in flight
+constexpr int PK_MAX_CHUNKS = 24;  // key chunks per (stream, head): the out-projection joins them from registers
 
 struct PkGemv {   // one product of the step: how it is cut
   int k, n, tn, tiles, ranges, k_per;   // k_per: rows per range (multiple of the rows one CTA trip covers)
@@ -106,59 +107,68 @@ __device__ __forceinline__ double pk_warp_sum(double v) {
 }
 
 // LayerNorm of B rows held in shared memory (device_backend.cpp:1247-1279: mean and biased
-// variance in double, inv_std = 1/sqrt(float(var) + 1e-5f)) by the whole CTA: every thread sums
-// its elements of every row, warps join by shuffles, the eight warp sums in warp order.
+// variance in double, inv_std = 1/sqrt(float(var) + 1e-5f)) by the whole CTA. Sum and sum of squares
+// are taken in one pass, in double (var = E[x^2] - mean^2 loses nothing that survives the rounding of
+// the variance to float at these magnitudes); warps join by shuffles, the eight warp sums in warp
+// order. gamma / beta come from registers the caller filled before the barrier (element c = tid + i*256).
+constexpr int PK_LN_REGS = 8;  // rows up to 2048 wide
 template <int MB>
-__device__ void pk_layernorm(const float *src, float *dst, int d, const float *gamma, const float *beta,
-                             double *s_red /* [PK_WARPS][MB] */) {
+__device__ void pk_layernorm(const float *src, float *dst, int d, const float *g_reg, const float *b_reg,
+                             double *s_red /* [PK_WARPS][2 * MB] */) {
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  double sum[MB];
+  double sum[MB], sq[MB];
 #pragma unroll
-  for (int b = 0; b < MB; ++b) sum[b] = 0.0;
-  for (int c = threadIdx.x; c < d; c += PK_THREADS)
-#pragma unroll
-    for (int b = 0; b < MB; ++b) sum[b] += (double)src[b * d + c];
-#pragma unroll
-  for (int b = 0; b < MB; ++b) {
-    sum[b] = pk_warp_sum(sum[b]);
-    if (lane == 0) s_red[w * MB + b] = sum[b];
-  }
-  __syncthreads();
-  double mean[MB], var[MB];
-#pragma unroll
-  for (int b = 0; b < MB; ++b) {
-    double t = s_red[b];
-    for (int q = 1; q < PK_WARPS; ++q) t += s_red[q * MB + b];
-    mean[b] = t / (double)d;
-    var[b] = 0.0;
-  }
+  for (int b = 0; b < MB; ++b) sum[b] = sq[b] = 0.0;
   for (int c = threadIdx.x; c < d; c += PK_THREADS)
 #pragma unroll
     for (int b = 0; b < MB; ++b) {
-      const double dd = (double)src[b * d + c] - mean[b];
-      var[b] += dd * dd;
+      const double v = (double)src[b * d + c];
+      sum[b] += v;
+      sq[b] += v * v;
     }
-  __syncthreads();  // everyone has read the first sums
 #pragma unroll
   for (int b = 0; b < MB; ++b) {
-    var[b] = pk_warp_sum(var[b]);
-    if (lane == 0) s_red[w * MB + b] = var[b];
+    sum[b] = pk_warp_sum(sum[b]);
+    sq[b] = pk_warp_sum(sq[b]);
+    if (lane == 0) {
+      s_red[w * 2 * MB + 2 * b] = sum[b];
+      s_red[w * 2 * MB + 2 * b + 1] = sq[b];
+    }
   }
   __syncthreads();
   float inv_std[MB], fmean[MB];
 #pragma unroll
   for (int b = 0; b < MB; ++b) {
-    double t = s_red[b];
-    for (int q = 1; q < PK_WARPS; ++q) t += s_red[q * MB + b];
-    inv_std[b] = 1.0f / sqrtf((float)(t / (double)d) + 1e-5f);
-    fmean[b] = (float)mean[b];
+    double t = s_red[2 * b], q = s_red[2 * b + 1];
+    for (int k = 1; k < PK_WARPS; ++k) {
+      t += s_red[k * 2 * MB + 2 * b];
+      q += s_red[k * 2 * MB + 2 * b + 1];
+    }
+    const double mean = t / (double)d;
+    double var = q / (double)d - mean * mean;
+    if (var < 0.0) var = 0.0;
+    inv_std[b] = 1.0f / sqrtf((float)var + 1e-5f);
+    fmean[b] = (float)mean;
   }
-  for (int c = threadIdx.x; c < d; c += PK_THREADS) {
-    const float g = __ldg(gamma + c), be = __ldg(beta + c);
 #pragma unroll
-    for (int b = 0; b < MB; ++b) dst[b * d + c] = __fadd_rn(__fmul_rn((src[b * d + c] - fmean[b]) * inv_std[b], g), be);
+  for (int i = 0; i < PK_LN_REGS; ++i) {
+    const int c = threadIdx.x + i * PK_THREADS;
+    if (c < d) {
+#pragma unroll
+      for (int b = 0; b < MB; ++b)
+        dst[b * d + c] = __fadd_rn(__fmul_rn((src[b * d + c] - fmean[b]) * inv_std[b], g_reg[i]), b_reg[i]);
+    }
   }
   __syncthreads();
+}
+// gamma and beta of the LayerNorm a CTA will apply after the next barrier, requested ahead of it
+__device__ __forceinline__ void pk_ln_prefetch(float *g_reg, float *b_reg, const float *gamma, const float *beta, int d) {
+#pragma unroll
+  for (int i = 0; i < PK_LN_REGS; ++i) {
+    const int c = threadIdx.x + i * PK_THREADS;
+    g_reg[i] = c < d ? __ldg(gamma + c) : 0.f;
+    b_reg[i] = c < d ? __ldg(beta + c) : 0.f;
+  }
 }
 
 // dst[b, c] (shared, row pitch `pitch`) = sum over ranges of part[r][b][col0 + c] (+ bias) (+ residual) (ReLU).
@@ -303,7 +313,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(PkPara
   __shared__ int s_tok[MB];
   __shared__ float red_f[PK_WARPS];
   __shared__ double red_d[PK_WARPS];
-  __shared__ double ln_red[PK_WARPS * MB];
+  __shared__ double ln_red[PK_WARPS * 2 * MB];
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int cta = blockIdx.x, G = gridDim.x;
   const int D = P.d, F = P.f, V = P.vocab, H = P.n_heads, B = P.n_streams;
@@ -330,6 +340,8 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(PkPara
   if (tid == 0) s_abort = 0;
   __syncthreads();
   run.prefetch(P.g_qkv, pk_unit(P.g_qkv, cta), off(0, QKVW));
+  float ln_g[PK_LN_REGS], ln_b[PK_LN_REGS];
+  pk_ln_prefetch(ln_g, ln_b, off(0, LN1G), off(0, LN1B), D);
 
   int stamp_i = 0;
   for (int t = 0; t < P.steps; ++t) {
@@ -366,7 +378,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(PkPara
         // x of this layer = W2 partial sums of the previous layer + b2 + y
         pk_gather<MB>(xrow, D, P.part_w2, P.g_w2.ranges, D, 0, D, off(l - 1, B2), yrow, D, 0);
       }
-      pk_layernorm<MB>(xrow, inrow, D, off(l, LN1G), off(l, LN1B), ln_red);
+      pk_layernorm<MB>(xrow, inrow, D, ln_g, ln_b, ln_red);
       PK_STAMP();  // gathered + normalised
       // (the first unit's weights were requested before the barrier that ended the previous phase)
       for (int u0 = cta; u0 == cta || u0 < P.g_qkv.tiles * P.g_qkv.ranges; u0 += G) {
@@ -379,7 +391,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(PkPara
       PK_STAMP();  // barrier
       // ---- attention over the cached keys and the newest one ----
       {
-        const int chunks = min(P.attn_chunks_max, max(1, G / (B * H)));
+        const int chunks = min(min(P.attn_chunks_max, PK_MAX_CHUNKS), max(1, G / (B * H)));
         const int keys_per_chunk = ((s + chunks - 1) / chunks + 7) / 8 * 8;
         float *kc = P.kcache + (unsigned long long)l * P.layer_stride, *vc = P.vcache + (unsigned long long)l * P.layer_stride;
         for (int u = cta; u < B * H * chunks; u += G) {
@@ -392,6 +404,30 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(PkPara
               out[DH + 1] = 0.f;
             }
             continue;
+          }
+          // Keys and values of earlier positions do not depend on this token: the first trip of keys
+          // (four per thread group) and the first sixteen values per thread are requested before the
+          // partial sums of q are gathered, so that all three reads are in flight together.
+          constexpr int LPK = DH / 8, KPI = PK_THREADS / LPK, KU = 4, PARTS = PK_THREADS / DH, VU = 16;
+          const int sub = tid % LPK, dcol = tid % DH, pt = tid / DH;
+          const int nk = c1 - c0;
+          float4 k0[KU], k1[KU];
+#pragma unroll
+          for (int uu = 0; uu < KU; ++uu) {
+            const int j = c0 + uu * KPI + tid / LPK;
+            if (j < c1 && j != p) {
+              const float *kp = kc + ((long long)b * P.cap + j) * D + h * DH + sub * 8;
+              k0[uu] = __ldcg(reinterpret_cast<const float4 *>(kp));
+              k1[uu] = __ldcg(reinterpret_cast<const float4 *>(kp + 4));
+            } else {
+              k0[uu] = k1[uu] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+          float vv[VU];
+#pragma unroll
+          for (int jj = 0; jj < VU; ++jj) {
+            const int i = pt + jj * PARTS, j = c0 + i;
+            vv[jj] = (i < nk && j != p) ? __ldcg(vc + ((long long)b * P.cap + j) * D + h * DH + dcol) : 0.f;
           }
           // q of this head, and the newest position's k and v when this chunk holds it: QKV partial sums + bias
           float *qs = inrow;              // [DH] q, then [DH] k, [DH] v
@@ -418,38 +454,43 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(PkPara
             if (which == 2) vc[((long long)b * P.cap + p) * D + h * DH + cc] = v;
           }
           __syncthreads();
-          constexpr int LPK = DH / 8, KPI = PK_THREADS / LPK;
-          const int sub = tid % LPK;
           const float4 q0 = *reinterpret_cast<const float4 *>(qs + sub * 8), q1 = *reinterpret_cast<const float4 *>(qs + sub * 8 + 4);
           const float scale = 1.0f / sqrtf((float)DH);
-          for (int base = c0; base < c1; base += KPI) {
-            const int j = base + tid / LPK;
-            float dot = 0.f;
-            if (j < c1) {
-              float4 k0, k1;
-              if (j == p) {
-                k0 = *reinterpret_cast<const float4 *>(qs + DH + sub * 8);
-                k1 = *reinterpret_cast<const float4 *>(qs + DH + sub * 8 + 4);
-              } else {
-                const float *kp = kc + ((long long)b * P.cap + j) * D + h * DH + sub * 8;
-                k0 = __ldcg(reinterpret_cast<const float4 *>(kp));
-                k1 = __ldcg(reinterpret_cast<const float4 *>(kp + 4));
+          for (int base = c0; base < c1; base += KPI * KU) {
+            if (base > c0) {  // further trips of a long chunk
+#pragma unroll
+              for (int uu = 0; uu < KU; ++uu) {
+                const int j = base + uu * KPI + tid / LPK;
+                if (j < c1 && j != p) {
+                  const float *kp = kc + ((long long)b * P.cap + j) * D + h * DH + sub * 8;
+                  k0[uu] = __ldcg(reinterpret_cast<const float4 *>(kp));
+                  k1[uu] = __ldcg(reinterpret_cast<const float4 *>(kp + 4));
+                } else {
+                  k0[uu] = k1[uu] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
               }
-              dot = q0.x * k0.x;
-              dot = fmaf(q0.y, k0.y, dot);
-              dot = fmaf(q0.z, k0.z, dot);
-              dot = fmaf(q0.w, k0.w, dot);
-              dot = fmaf(q1.x, k1.x, dot);
-              dot = fmaf(q1.y, k1.y, dot);
-              dot = fmaf(q1.z, k1.z, dot);
-              dot = fmaf(q1.w, k1.w, dot);
             }
 #pragma unroll
-            for (int o = LPK >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            if (j < c1 && sub == 0) sc[j - c0] = dot * scale;
+            for (int uu = 0; uu < KU; ++uu) {
+              const int j = base + uu * KPI + tid / LPK;
+              if (j == p) {  // the newest position's key is this step's own
+                k0[uu] = *reinterpret_cast<const float4 *>(qs + DH + sub * 8);
+                k1[uu] = *reinterpret_cast<const float4 *>(qs + DH + sub * 8 + 4);
+              }
+              float dot = q0.x * k0[uu].x;
+              dot = fmaf(q0.y, k0[uu].y, dot);
+              dot = fmaf(q0.z, k0[uu].z, dot);
+              dot = fmaf(q0.w, k0[uu].w, dot);
+              dot = fmaf(q1.x, k1[uu].x, dot);
+              dot = fmaf(q1.y, k1[uu].y, dot);
+              dot = fmaf(q1.z, k1[uu].z, dot);
+              dot = fmaf(q1.w, k1[uu].w, dot);
+#pragma unroll
+              for (int o = LPK >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+              if (j < c1 && sub == 0) sc[j - c0] = dot * scale;
+            }
           }
           __syncthreads();
-          const int nk = c1 - c0;
           float m = -INFINITY;
           for (int i = tid; i < nk; i += PK_THREADS) m = fmaxf(m, sc[i]);
 #pragma unroll
@@ -471,22 +512,25 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(PkPara
           lsum = red_d[0];
 #pragma unroll
           for (int q = 1; q < PK_WARPS; ++q) lsum += red_d[q];
-          constexpr int PARTS = PK_THREADS / DH;
-          const int dcol = tid % DH, pt = tid / DH;
           float o = 0.f;
-          for (int i0 = pt; i0 < nk; i0 += 8 * PARTS) {
-            float vv[8];
+#pragma unroll
+          for (int jj = 0; jj < VU; ++jj) {  // the values requested at the start of the unit
+            const int i = pt + jj * PARTS;
+            if (i < nk) o = fmaf(sc[i], c0 + i == p ? qs[2 * DH + dcol] : vv[jj], o);
+          }
+          for (int i0 = pt + VU * PARTS; i0 < nk; i0 += 8 * PARTS) {  // the rest of a long chunk
+            float vw[8];
 #pragma unroll
             for (int jj = 0; jj < 8; ++jj) {
               const int i = i0 + jj * PARTS, j = c0 + i;
-              vv[jj] = i >= nk ? 0.f
+              vw[jj] = i >= nk ? 0.f
                        : j == p ? qs[2 * DH + dcol]
                                 : __ldcg(vc + ((long long)b * P.cap + j) * D + h * DH + dcol);
             }
 #pragma unroll
             for (int jj = 0; jj < 8; ++jj) {
               const int i = i0 + jj * PARTS;
-              if (i < nk) o = fmaf(sc[i], vv[jj], o);
+              if (i < nk) o = fmaf(sc[i], vw[jj], o);
             }
           }
           float *opart = reinterpret_cast<float *>(red);
@@ -515,52 +559,39 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(PkPara
           const PkUnit u = pk_unit(P.g_wo, u0);
           if (u0 != cta) run.prefetch(P.g_wo, u, off(l, OUTW));
           if (u.valid) {
-            // Join the attention chunks of the heads this range of k covers: first every chunk's weight
-            // exp(max_chunk - max) / sum per (stream, head), then the weighted sum of the chunks' outputs.
+            // Join the attention chunks of the heads this range of k covers. Every thread reads, for
+            // its element, each chunk's maximum, sum and output in one batch of independent loads and
+            // forms the common maximum, the weights exp(max_chunk - max) and the total itself, in chunk
+            // order (threads of one head repeat the same few operations; one round trip instead of three).
             const int nrows = u.ke - u.kb;
-            const int h_lo = u.kb / DH, h_hi = (u.ke - 1) / DH, nh = h_hi - h_lo + 1;
-            float *wts = sc;  // [MB][nh][chunks]
-            for (int e = wid; e < B * nh; e += PK_WARPS) {  // one warp per (stream, head)
-              const int b = e / nh, h = h_lo + (e - b * nh);
-              const float *pp = P.part_attn + ((long long)b * H + h) * P.attn_chunks_max * (DH + 2);
-              float mm = -INFINITY;
-              for (int q = lane; q < chunks; q += 32) mm = fmaxf(mm, __ldcg(pp + q * (DH + 2) + DH));
-#pragma unroll
-              for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
-              double ll = 0.0;
-              for (int q0 = 0; q0 < chunks; q0 += 32) {  // the sum in chunk order: lanes hold terms, lane 0 adds them
-                const int q = q0 + lane;
-                float wq = 0.f, lq = 0.f;
-                if (q < chunks) {
-                  const float mc = __ldcg(pp + q * (DH + 2) + DH);
-                  wq = mc == -INFINITY ? 0.f : expf(mc - mm);
-                  lq = __ldcg(pp + q * (DH + 2) + DH + 1);
-                  wts[(e * chunks) + q] = wq;
-                }
-                for (int j = 0; j < 32 && q0 + j < chunks; ++j)
-                  ll += (double)__shfl_sync(0xffffffffu, lq, j) * (double)__shfl_sync(0xffffffffu, wq, j);
-              }
-              const float inv = (float)(1.0 / ll);
-              if (lane == 0) wts[MB * nh * chunks + e] = inv;  // the weights stay unnormalised; the sum's inverse beside them
-            }
-            __syncthreads();
             for (int e = tid; e < MB * nrows; e += PK_THREADS) {
               const int b = e / nrows, r = e - b * nrows, col = u.kb + r;
               float v = 0.f;
               if (b < B) {
-                const int h = col / DH, dd = col - h * DH, hw = b * nh + (h - h_lo);
-                const float *pp = P.part_attn + ((long long)b * H + h) * P.attn_chunks_max * (DH + 2) + dd;
-                const float *wq = wts + hw * chunks;
-                float oo = 0.f;
-                for (int q0 = 0; q0 < chunks; q0 += 8) {
-                  float tt[8];
+                const int h = col / DH, dd = col - h * DH;
+                const float *pp = P.part_attn + ((long long)b * H + h) * P.attn_chunks_max * (DH + 2);
+                float mq[PK_MAX_CHUNKS], lq[PK_MAX_CHUNKS], oq[PK_MAX_CHUNKS];
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) tt[j] = (q0 + j < chunks && wq[q0 + j] != 0.f) ? __ldcg(pp + (q0 + j) * (DH + 2)) : 0.f;
-#pragma unroll
-                  for (int j = 0; j < 8; ++j)
-                    if (q0 + j < chunks) oo = fmaf(tt[j], wq[q0 + j], oo);
+                for (int q = 0; q < PK_MAX_CHUNKS; ++q) {
+                  const bool live = q < chunks;
+                  mq[q] = live ? __ldcg(pp + q * (DH + 2) + DH) : -INFINITY;
+                  lq[q] = live ? __ldcg(pp + q * (DH + 2) + DH + 1) : 0.f;
+                  oq[q] = live ? __ldcg(pp + q * (DH + 2) + dd) : 0.f;
                 }
-                v = oo * wts[MB * nh * chunks + hw];
+                float mm = -INFINITY;
+#pragma unroll
+                for (int q = 0; q < PK_MAX_CHUNKS; ++q) mm = fmaxf(mm, mq[q]);
+                double ll = 0.0;
+                float oo = 0.f;
+#pragma unroll
+                for (int q = 0; q < PK_MAX_CHUNKS; ++q) {
+                  if (mq[q] != -INFINITY) {  // not an empty chunk
+                    const float w = expf(mq[q] - mm);
+                    ll += (double)lq[q] * (double)w;
+                    oo = fmaf(oq[q], w, oo);
+                  }
+                }
+                v = oo * (float)(1.0 / ll);
               }
               inrow[b * in_pitch + r] = v;
             }
@@ -572,13 +603,14 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(PkPara
       {
         const PkUnit uw = pk_unit(P.g_w1, cta);
         run.prefetch(P.g_w1, uw, off(l, W1));
+        pk_ln_prefetch(ln_g, ln_b, off(l, LN2G), off(l, LN2B), D);
       }
       PK_STAMP();  // out-projection units done
       if (!pk_grid_sync(P.barrier, target, G, P.err, &s_abort)) return;
       PK_STAMP();  // barrier
       // ---- h = relu(LN2(y) W1 + b1), y = out-projection partial sums + bo + x ----
       pk_gather<MB>(yrow, D, P.part_wo, P.g_wo.ranges, D, 0, D, off(l, OUTB), xrow, D, 0);
-      pk_layernorm<MB>(yrow, inrow, D, off(l, LN2G), off(l, LN2B), ln_red);
+      pk_layernorm<MB>(yrow, inrow, D, ln_g, ln_b, ln_red);
       PK_STAMP();  // gathered + normalised
       for (int u0 = cta; u0 == cta || u0 < P.g_w1.tiles * P.g_w1.ranges; u0 += G) {
         const PkUnit u = pk_unit(P.g_w1, u0);
@@ -605,6 +637,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(PkPara
         const PkGemv &gn = last ? P.g_head : P.g_qkv;
         const PkUnit uw = pk_unit(gn, cta);
         run.prefetch(gn, uw, last ? lm_head : off(l + 1, QKVW));
+        pk_ln_prefetch(ln_g, ln_b, last ? lnf_g : off(l + 1, LN1G), last ? lnf_b : off(l + 1, LN1B), D);
       }
       PK_STAMP();  // W2 units done
       if (!pk_grid_sync(P.barrier, target, G, P.err, &s_abort)) return;
@@ -612,7 +645,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(PkPara
     }
     // ---- head: logits = LN_f(x) W_head, x = last W2 partial sums + b2 + y ----
     pk_gather<MB>(xrow, D, P.part_w2, P.g_w2.ranges, D, 0, D, off(P.n_layers - 1, B2), yrow, D, 0);
-    pk_layernorm<MB>(xrow, inrow, D, lnf_g, lnf_b, ln_red);
+    pk_layernorm<MB>(xrow, inrow, D, ln_g, ln_b, ln_red);
     for (int u0 = cta; u0 == cta || u0 < P.g_head.tiles * P.g_head.ranges; u0 += G) {
       const PkUnit u = pk_unit(P.g_head, u0);
       if (u0 != cta) run.prefetch(P.g_head, u, lm_head);
@@ -621,6 +654,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(PkPara
     if (t + 1 < P.steps) {
       const PkUnit uw = pk_unit(P.g_qkv, cta);
       run.prefetch(P.g_qkv, uw, off(0, QKVW));
+      pk_ln_prefetch(ln_g, ln_b, off(0, LN1G), off(0, LN1B), D);
     }
     if (!pk_grid_sync(P.barrier, target, G, P.err, &s_abort)) return;
     // ---- selection: every CTA adds the head's partial sums and finds the first maximum itself
@@ -731,7 +765,7 @@ bool decode_persistent_supports(int n_streams, int n_heads, int d_model, int d_f
   if (n_streams < 1 || n_streams > 8 || d_model % n_heads != 0) return false;
   const int dh = d_model / n_heads;
   if (dh != 32 && dh != 64) return false;
-  return d_model % 4 == 0 && d_ff % 4 == 0 && vocab % 4 == 0 && d_model >= 32;
+  return d_model % 4 == 0 && d_ff % 4 == 0 && vocab % 4 == 0 && d_model >= 32 && d_model <= 2048;
 }
 
 size_t decode_persistent_scratch_floats(int n_streams, int n_heads, int d_model, int d_ff, int vocab, int sm_count) {

@@ -355,10 +355,16 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
           }
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
-            acc[i][0] = fmaf(xr[r], wv[r].x, acc[i][0]);
-            acc[i][1] = fmaf(xr[r], wv[r].y, acc[i][1]);
-            acc[i][2] = fmaf(xr[r], wv[r].z, acc[i][2]);
-            acc[i][3] = fmaf(xr[r], wv[r].w, acc[i][3]);
+            // two fused multiply-adds per instruction (sm_100 packed fp32): each lane of the pair is
+            // the same fmaf as before, so results do not change; at 8 rows the kernel is close to
+            // issue-bound on SMs that hold two CTAs
+            const float2 xx = make_float2(xr[r], xr[r]);
+            const float2 lo = __ffma2_rn(xx, make_float2(wv[r].x, wv[r].y), make_float2(acc[i][0], acc[i][1]));
+            const float2 hi = __ffma2_rn(xx, make_float2(wv[r].z, wv[r].w), make_float2(acc[i][2], acc[i][3]));
+            acc[i][0] = lo.x;
+            acc[i][1] = lo.y;
+            acc[i][2] = hi.x;
+            acc[i][3] = hi.y;
           }
         }
       }
