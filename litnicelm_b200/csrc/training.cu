@@ -75,9 +75,15 @@ __global__ void sum_squares_kernel(const float *__restrict__ x, long long n, dou
 
 __global__ void ordered_sum_kernel(const double *__restrict__ partial, int count, double scale, double *out_f64,
                                    float *out_f32) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  // One warp: lanes fetch 32 consecutive terms at a time (one round trip instead of 32), lane 0
+  // adds them in index order, which keeps the sum identical to a sequential loop.
   double acc = 0.0;
-  for (int i = 0; i < count; ++i) acc += partial[i];
+  for (int i0 = 0; i0 < count; i0 += 32) {
+    const int i = i0 + (int)threadIdx.x;
+    const double mine = i < count ? partial[i] : 0.0;
+    for (int j = 0; j < 32 && i0 + j < count; ++j) acc += __shfl_sync(0xffffffffu, mine, j);
+  }
+  if (threadIdx.x != 0) return;
   acc *= scale;
   if (out_f64) *out_f64 = acc;
   if (out_f32) *out_f32 = (float)acc;
