@@ -652,12 +652,32 @@ def run_prefill_arm(args, rank, local_rank, world):
                                  "head on the last rows) / device time of the step"},
             "cpu_baseline": None, "clocks": clock_info,
             "probability_row_sums": [float(probs[0].sum()), float(probs[-1].sum())],
+            "parity": check_prefill_against_fixture(probs),
         }
         print(json.dumps(line), flush=True)
     sess.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def check_prefill_against_fixture(probs: np.ndarray) -> dict:
+    """Rank 0's sequences 0 and 31 of the prefill batch against the oracle's last-row logits of the
+    same inputs (tests/golden/c4_prefill.npz): most likely token and largest probability error."""
+    path = os.path.join(ROOT, "tests", "golden", "c4_prefill.npz")
+    if not os.path.exists(path):
+        return {"fixture": None}
+    z = np.load(path)
+    out = {"fixture": "tests/golden/c4_prefill.npz", "sequences": z["sequences"].tolist(), "argmax_equal": 0,
+           "max_abs_probability_error": 0.0}
+    for i, seq in enumerate(z["sequences"].tolist()):
+        row = z["last_logits"][i].astype(np.float64)
+        want = np.exp(row - row.max())
+        want /= want.sum()
+        out["argmax_equal"] += int(int(np.argmax(probs[seq])) == int(np.argmax(want)))
+        out["max_abs_probability_error"] = max(out["max_abs_probability_error"],
+                                               float(np.abs(probs[seq] - want).max()))
+    return out
 
 
 def main():

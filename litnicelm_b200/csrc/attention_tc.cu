@@ -154,6 +154,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __grid_
 
   if (warp == 0) {
     // ---- TMA producer: Q once, then K and V^T of each key tile as their buffers free up ----
+    if (lane == 0) {
+      tma_prefetch_map(&map_qk_hi);
+      tma_prefetch_map(&map_qk_lo);
+      tma_prefetch_map(&map_vt_hi);
+      tma_prefetch_map(&map_vt_lo);
+    }
     pdl_wait();
     if (lane == 0) {
       if (timeline != nullptr) atomicMin(timeline + 16, global_timer());  // the predecessor has completed

@@ -74,7 +74,15 @@ constexpr int TC_CHUNK = LB_TC_CHUNK;  // k-blocks (of 32) per TMEM accumulation
 // pairs: a k-block is 64 elements (still one 128-byte row per tile row), the
 // instructions are kind::f16 with K = 16, and the drain multiplies each chain by
 // a_inv_scale[row][k-block] * b_inv_scale.
-template <int BN, int STAGES, bool F16>
+//
+// WIDE (fp16 pairs, tiles up to 128 columns): the B_lo tile lies directly behind the
+// B_hi tile in a stage, so one instruction of 2*BN columns multiplies a_hi by
+// [b_hi | b_lo]: columns 0..BN-1 of the chain's buffer take a_hi*b_hi and columns
+// BN..2BN-1 the two small products (a_hi*b_lo from the wide instruction, a_lo*b_hi from
+// one of BN columns added there). Two instructions per k-step instead of three, the A_hi
+// tile read once instead of twice: (32 + BN) + (32 + BN/2) clocks against 3*(32 + BN/2).
+// The drain adds both halves of the buffer into the same registers.
+template <int BN, int STAGES, bool F16, bool WIDE>
 __global__ void __launch_bounds__(tc_threads(BN), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
@@ -88,7 +96,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   unsigned char *base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const unsigned bar_base = base + L::BAR_OFFSET;
   // barriers: full[S], empty[S], tmem_full[NBUF], tmem_empty[NBUF]
-  constexpr int NBUF = 512 / BN;
+  static_assert(!WIDE || (F16 && BN <= 128), "the wide instruction needs fp16 pairs and 2*BN <= 256 columns");
+  constexpr int ACCW = WIDE ? 2 * BN : BN;  // tensor-memory columns of one accumulation chain
+  constexpr int NBUF = 512 / ACCW;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
@@ -175,6 +185,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     // stages are requested before waiting for the predecessor to finish.
     const int pre = min(STAGES, kblocks);
     if (lane == 0) {
+      tma_prefetch_map(&map_a_hi);
+      tma_prefetch_map(&map_a_lo);
       for (int kb = 0; kb < pre; ++kb) {
         const unsigned stage = base + (unsigned)kb * L::STAGE_BYTES;
         const int kx = (kb0 + kb) * KBE;
@@ -234,7 +246,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     int committed = -1;  // last chunk whose completion was committed to a tmem_full barrier
     for (int c = 0; c < nchunks && ok; ++c) {
       const int buf = c % NBUF;
-      const unsigned tmem_d = tmem_base + (unsigned)(buf * BN);
+      const unsigned tmem_d = tmem_base + (unsigned)(buf * ACCW);
       // the epilogue must have drained this buffer's previous chunk
       ok = mbar_wait(tmem_empty_bar(buf), ((unsigned)(c / NBUF) & 1u) ^ 1u, abort_flag, err, 4);
       __syncwarp();
@@ -254,7 +266,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
         const unsigned long long a_lo = umma_desc_k128(stage + L::A_BYTES);
         const unsigned long long b_hi = umma_desc_k128(stage + 2 * L::A_BYTES);
         const unsigned long long b_lo = umma_desc_k128(stage + 2 * L::A_BYTES + L::B_BYTES);
-        if (lane == 0) {
+        if (WIDE) {
+          if (lane == 0) {
+            const unsigned idesc2 = umma_idesc_f16(2 * BN);
+#pragma unroll
+            for (int ks = 0; ks < TC_BK / 8; ++ks) {  // a_hi * [b_hi | b_lo]; the first one zeroes both halves
+              const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);
+              tc_mma_f16(tmem_d, a_hi + adv, b_hi + adv, idesc2, (kb == c * TC_CHUNK && ks == 0) ? 0u : 1u);
+            }
+#pragma unroll
+            for (int ks = 0; ks < TC_BK / 8; ++ks) {  // a_lo * b_hi joins the small products
+              const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);
+              tc_mma_f16(tmem_d + (unsigned)BN, a_lo + adv, b_hi + adv, idesc, 1u);
+            }
+            tc_commit(empty_bar(s));
+          }
+        } else if (lane == 0) {
 #pragma unroll
           for (int ks = 0; ks < TC_BK / 8; ++ks) {
             const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);  // 8 fp32 = 32 bytes along k
@@ -311,15 +338,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
       if (F16 && c + 1 < nchunks) chain_scale = a_inv_row[c + 1] * b_inv;  // in flight during this chain's adds
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-      for (int c0 = 0; c0 < CW; c0 += 32) {
-        unsigned r[32];
-        __syncwarp();
-        tc_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN + col0 + c0), r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      for (int half = 0; half < (WIDE ? 2 : 1); ++half) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          acc[c0 + j] = F16 ? __fmaf_rn(__uint_as_float(r[j]), sc, acc[c0 + j])
-                            : __fadd_rn(acc[c0 + j], __uint_as_float(r[j]));
+        for (int c0 = 0; c0 < CW; c0 += 32) {
+          unsigned r[32];
+          __syncwarp();
+          tc_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(buf * ACCW + half * BN + col0 + c0), r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            acc[c0 + j] = F16 ? __fmaf_rn(__uint_as_float(r[j]), sc, acc[c0 + j])
+                              : __fadd_rn(acc[c0 + j], __uint_as_float(r[j]));
+        }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -491,7 +521,7 @@ bool tc_clusters_enabled() {
   return on;
 }
 
-template <int BN, int STAGES, bool F16>
+template <int BN, int STAGES, bool F16, bool WIDE = false>
 void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const TcEpilogue &ep, int splits,
                 float *part, int *counters, DevErr *err, cudaStream_t st, const float *a_inv_scale = nullptr,
                 const float *b_inv_scale = nullptr) {
@@ -505,7 +535,7 @@ void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const
   {
     std::lock_guard<std::mutex> lock(cfg_mu);
     if (dev >= 64 || !configured[dev]) {
-      LB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      LB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, F16, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    L::TOTAL));
       if (dev < 64) configured[dev] = true;
     }
@@ -533,7 +563,7 @@ void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const
       cfg.attrs = attr;
       cfg.numAttrs = 1;
       int nc = 0;
-      if (cudaOccupancyMaxActiveClusters(&nc, gemm_tc_kernel<BN, STAGES, F16>, &cfg) != cudaSuccess || nc <= 0) {
+      if (cudaOccupancyMaxActiveClusters(&nc, gemm_tc_kernel<BN, STAGES, F16, WIDE>, &cfg) != cudaSuccess || nc <= 0) {
         (void)cudaGetLastError();
         nc = -1;
       }
@@ -541,7 +571,7 @@ void launch_cfg(const TcMatrix &a, const TcMatrix &b, int m, int n, int k, const
     }
     if ((long long)grid.x * grid.y > max_clusters[cluster_splits]) cluster_splits = 1;
   }
-  launch_pdl_cluster(gemm_tc_kernel<BN, STAGES, F16>, grid, dim3(tc_threads(BN)), (size_t)L::TOTAL, st, g_pdl_enabled,
+  launch_pdl_cluster(gemm_tc_kernel<BN, STAGES, F16, WIDE>, grid, dim3(tc_threads(BN)), (size_t)L::TOTAL, st, g_pdl_enabled,
                      (unsigned)cluster_splits, a.hi, a.lo, b.hi, b.lo, ep, m, n, k, splits, part, counters, err,
                      a_inv_scale, b_inv_scale, cluster_splits);
 }
@@ -623,9 +653,9 @@ const int *tc_cluster_capacity() {
       cfg.attrs = attr;
       cfg.numAttrs = 1;
       int nc = 0;
-      if (cudaFuncSetAttribute(gemm_tc_kernel<128, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) !=
+      if (cudaFuncSetAttribute(gemm_tc_kernel<128, 3, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) !=
               cudaSuccess ||
-          cudaOccupancyMaxActiveClusters(&nc, gemm_tc_kernel<128, 3, true>, &cfg) != cudaSuccess || nc <= 0) {
+          cudaOccupancyMaxActiveClusters(&nc, gemm_tc_kernel<128, 3, true, false>, &cfg) != cudaSuccess || nc <= 0) {
         (void)cudaGetLastError();
         nc = -1;
       }
@@ -708,10 +738,21 @@ void launch_gemm_tc_f16(const TcMatrix &a, const float *a_inv_scale, const TcMat
     throw std::invalid_argument("litnice_b200: fp16-pair tensor-core GEMM needs the operands' scales");
   if (plan.splits > 1 && (scratch == nullptr || counters == nullptr))
     throw std::invalid_argument("litnice_b200: split-k tensor-core GEMM needs scratch");
+  // LITNICE_B200_TC_WIDE: 0 = three instructions per k-step everywhere, 1 (default) = the wide
+  // instruction for 64-column tiles, 2 = for 128-column tiles too (measured slower there: the wide
+  // chain leaves only two tensor-memory buffers, and the drain does not keep up with the k loop).
+  static const int wide = [] {
+    const char *e = std::getenv("LITNICE_B200_TC_WIDE");
+    return (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
+  }();
   if (bn == 256)
     launch_cfg<256, 2, true>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st, a_inv_scale, b_inv_scale);
+  else if (bn == 128 && wide >= 2)
+    launch_cfg<128, 3, true, true>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st, a_inv_scale, b_inv_scale);
   else if (bn == 128)
     launch_cfg<128, 3, true>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st, a_inv_scale, b_inv_scale);
+  else if (wide >= 1)
+    launch_cfg<64, 4, true, true>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st, a_inv_scale, b_inv_scale);
   else
     launch_cfg<64, 4, true>(a, b, m, n, k, ep, plan.splits, scratch, counters, err, st, a_inv_scale, b_inv_scale);
 }

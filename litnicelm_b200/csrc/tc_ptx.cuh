@@ -85,6 +85,11 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *map
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// Brings a tensor map into the descriptor cache ahead of its first use (the maps of operands
+// an earlier kernel writes are first used right after the wait for that kernel).
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap *map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 // Untiled bulk copy global -> this CTA's shared memory, completion counted in bytes on an
 // mbarrier. Both addresses 16-byte aligned, the size a multiple of 16 bytes.
 __device__ __forceinline__ void bulk_load(unsigned dst, const void *src, unsigned bytes, unsigned bar) {

@@ -160,6 +160,26 @@ def c3_streams():
     print("c3_streams", np.stack(toks)[:, :8])
 
 
+def c4_prefill(confirm_with_reference: bool = False):
+    """Config 4 (arena seed 1004, the bench's prefill batch): sequences 0 and 31
+    of rank 0 (prompt seeds 2000*4+i), all 2048 tokens: the last row's logits,
+    i.e. the next-token distribution the prefill step returns."""
+    d = formats.CONFIG_DIMS["c5"]
+    arena = formats.make_param_arena(d, 1004)
+    which = np.array([0, 31], dtype=np.int32)
+    prompts = np.stack([formats.zipf_prompt(d.vocab, d.max_seq, 2000 * 4 + int(i)) for i in which])
+    rows = np.stack([ob.forward(d, arena, p, only_last=True) for p in prompts])
+    confirmed = 0
+    if confirm_with_reference and ob.have_ref():      # about an hour of the reference's single thread
+        ref_logits, _ = ob.ref_run(d, arena, prompts[0], attention="fused_inplace", ffn="inplace_fused_bias_relu")
+        assert np.array_equal(ref_logits[-1], rows[0]), "restatement differs from the reference at s=2048"
+        confirmed = 1
+    np.savez_compressed(os.path.join(HERE, "c4_prefill.npz"), sequences=which, prompts=prompts,
+                        last_logits=rows, top2_gap=_top2_gap(rows), arena_sha256=_sha(arena),
+                        arena_seed=np.array([1004]), confirmed_by_reference=np.array([confirmed]))
+    print("c4_prefill", rows.argmax(axis=1), "gaps", _top2_gap(rows), "confirmed", confirmed)
+
+
 if __name__ == "__main__":
     what = sys.argv[1:] or ["small"]
     for w in what:
@@ -169,5 +189,6 @@ if __name__ == "__main__":
             c3_streams()
             c5_dims()
             c2_full()
+            c4_prefill()
         else:
-            {"c2_full": c2_full, "c5_dims": c5_dims, "c3_streams": c3_streams}[w]()
+            {"c2_full": c2_full, "c5_dims": c5_dims, "c3_streams": c3_streams, "c4_prefill": c4_prefill}[w]()

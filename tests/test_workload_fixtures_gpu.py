@@ -1,6 +1,6 @@
 """The benchmark workloads themselves against the oracle, through the C ABI.
 
-tests/golden/c2_full.npz, c5_dims.npz and c3_streams.npz hold what the
+tests/golden/c2_full.npz, c5_dims.npz, c3_streams.npz and c4_prefill.npz hold what the
 reference computes on the exact inputs bench.py uses (same seeded weights, same
 prompts, same sampler seeds): the token sequences of generate_text
 (inference.cpp:265-296) and the logits behind them. The native loop must
@@ -112,6 +112,29 @@ def test_config5_model_logits_and_greedy_tokens():
     assert e64 < LOGIT_RTOL and e256 < LOGIT_RTOL
     assert int(np.argmax(last64)) == int(np.argmax(z["last_logits_s64"]))
     agreed_prefix(fast, z["greedy_tokens"], z["top2_gap"])
+
+
+def test_config4_prefill_distribution_at_full_context():
+    """Two of the bench's 32 prefill sequences at all 2048 tokens, run as a batch of two
+    (the many-row tile plans): logits of the last rows, the probabilities `inspect`
+    returns (inspect_distribution, inference.cpp:298-360) and their most likely token."""
+    z, d, arena = load("c4_prefill.npz", "c5")
+    want = z["last_logits"]
+    with Session(d, 2) as s:
+        s.load_params(arena)
+        got = s.forward(z["prompts"])
+        probs = s.inspect(z["prompts"])
+    err = rel_err(got, want)
+    print(f"config 4, sequences {z['sequences'].tolist()} at s={z['prompts'].shape[1]}: logits {err:.2e}, "
+          f"oracle top-2 gaps {z['top2_gap'].tolist()}")
+    assert err < LOGIT_RTOL
+    for i in range(2):
+        row = want[i].astype(np.float64)
+        p = np.exp(row - row.max())
+        p /= p.sum()
+        np.testing.assert_allclose(probs[i], p, rtol=2e-3, atol=1e-7)
+        if z["top2_gap"][i] >= NEAR_TIE:
+            assert int(np.argmax(got[i])) == int(np.argmax(want[i])) == int(np.argmax(probs[i]))
 
 
 def test_config3_sampled_streams_with_the_bench_seeds():
