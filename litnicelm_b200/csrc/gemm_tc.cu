@@ -398,10 +398,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   }
   const bool go = *store_flag != 0;
   if (stamp && warp == 2 && lane == 0) ep.timeline[11] = global_timer();
-  if (go && ep.vt_hi != nullptr)
+  if (go && ep.has_vt())
     tc_store_vt<BN, tc_threads(BN)>(ep, m, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits, rows_each, row_begin,
                                     row_end);
-  if (go && !(ep.vt_hi != nullptr && n0 >= ep.vt_col0))  // a tile of V columns only has left already
+  if (go && !(ep.has_vt() && n0 >= ep.vt_col0))  // a tile of V columns only has left already
     tc_store_rows<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits, rows_each,
                                       row_begin, row_end, first);
   if (stamp && warp == 2 && lane == 0) ep.timeline[12] = global_timer();

@@ -53,6 +53,15 @@ struct TcEpilogue {
   float *vt_lo = nullptr;
   int vt_col0 = 0, vt_rows = 0, vt_pitch = 0, vt_s = 0, vt_streams = 0;
   const LoopState *state = nullptr;
+  // The same outputs as fp16 pairs under fixed scales, for the fp16-pair attention kernel: every
+  // 64-column block of the result (one head of Q, K or V) is multiplied by col_scale[column / 64],
+  // a power of two chosen when the weights were loaded so that no value can leave fp16's range;
+  // columns below vt_col0 go row-major to qk16_hi/lo [M, N], the V columns transposed to
+  // vt16_hi/lo (laid out as vt_hi/vt_lo).
+  __half *qk16_hi = nullptr, *qk16_lo = nullptr;
+  __half *vt16_hi = nullptr, *vt16_lo = nullptr;
+  const float *col_scale = nullptr;  // [N / 64]
+  __host__ __device__ bool has_vt() const { return vt_hi != nullptr || vt16_hi != nullptr; }
   // LayerNorm folded into the product. With W' = diag(gamma) W the reference's
   // LN(x) W + b (layernorm_forward then gemm_ranked_matrix_rhs + add_bias_rowwise)
   // equals inv_std * (x W' - mean * u) + v, u[n] = sum_k W'[k,n],
@@ -179,6 +188,19 @@ void launch_attention_tc(const TcMatrix &qk, const TcMatrix &vt, float *ctx_hi, 
                          int n_heads, int d_model, float *scratch, int *counters, const LoopState *state,
                          DevErr *err, cudaStream_t st, unsigned long long *timeline = nullptr,
                          const TcPairF16 *ctx_f16 = nullptr);
+// attention_tc16.cu: the same on fp16 pairs under fixed per-head scales. qk: fp16 maps (box 128
+// rows x 64) over the [rows, 3*d_model] pair the QKV projection stores (TcEpilogue::qk16_*); vt:
+// fp16 maps (box 64 rows x 64) over its transposed V pair; head_inv_scale [3 * n_heads]: the
+// inverse scales of the heads of Q, K and V (launch_head_scales). Plan, scratch, counters, state
+// and timeline as launch_attention_tc; the context leaves as the fp16 pair ctx_f16.
+void launch_attention_tc16(const TcMatrix &qk, const TcMatrix &vt, const float *head_inv_scale, int n_streams, int s,
+                           int n_heads, int d_model, float *scratch, int *counters, const LoopState *state,
+                           DevErr *err, cudaStream_t st, unsigned long long *timeline, const TcPairF16 &ctx_f16);
+// scale / inv_scale [n / 64]: per 64 columns of LN(x) W + bias (W [k, n] row-major, the LayerNorm's
+// gamma and beta [k]) the power of two that brings the largest value those columns can take for
+// any input row into [2^14, 2^15), and its inverse.
+void launch_head_scales(const float *w, int k, int n, const float *gamma, const float *beta, const float *bias,
+                        float *scale, float *inv_scale, cudaStream_t st);
 
 // x -> (hi, lo) elementwise.
 void launch_split_tf32(const float *x, float *hi, float *lo, long long count, cudaStream_t st);

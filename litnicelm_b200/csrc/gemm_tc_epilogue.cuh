@@ -59,7 +59,8 @@ __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n
   constexpr int G = TC_STORE_G;
   const int c4 = tid % PER_ROW, r0 = tid / PER_ROW;
   const int col = n0 + c4 * 4;
-  const bool col_active = !(ep.vt_hi != nullptr && col >= ep.vt_col0);  // V columns leave transposed, elsewhere
+  const bool col_active = !(ep.has_vt() && col >= ep.vt_col0);  // V columns leave transposed, elsewhere
+  const float cs16 = ep.qk16_hi != nullptr ? __ldg(ep.col_scale + col / 64) : 1.f;
   const bool fold = ep.ln_u != nullptr;
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
   const float4 uu = first.uu, bb = first.bb;
@@ -123,6 +124,12 @@ __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n
         split_tf32(v[g].w, hh.w, ll.w);
         *reinterpret_cast<float4 *>(ep.c_hi + off) = hh;
         *reinterpret_cast<float4 *>(ep.c_lo + off) = ll;
+      }
+      if (ep.qk16_hi) {  // fp16 pair under the head's fixed scale
+        uint2 hi, lo;
+        f16_pair4(v[g], cs16, hi, lo);
+        *reinterpret_cast<uint2 *>(ep.qk16_hi + off) = hi;
+        *reinterpret_cast<uint2 *>(ep.qk16_lo + off) = lo;
       }
       if (ep.stats_out != nullptr)  // final values, over the thread's own rank-0 partial
         *reinterpret_cast<float4 *>(stage + (rg - row_begin) * LDS + c4 * 4) = v[g];
@@ -309,6 +316,18 @@ __device__ __forceinline__ void tc_store_vt(const TcEpilogue &ep, int m, int m0,
     if (!act) continue;
     const float vals[4] = {t.x, t.y, t.z, t.w}, us[4] = {u4.x, u4.y, u4.z, u4.w}, bs[4] = {b4.x, b4.y, b4.z, b4.w};
     const long long at0 = ((long long)v_stream * ep.vt_rows + (col - ep.vt_col0)) * ep.vt_pitch + v_tok;
+    if (ep.vt16_hi != nullptr) {  // fp16 pair under the head's fixed scale (the four columns share a head)
+      const float cs = __ldg(ep.col_scale + col / 64);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float val = fold ? __fmul_rn(st.y, __fmaf_rn(-st.x, us[e], vals[e])) : vals[e];
+        const float a = (val + bs[e]) * cs;
+        const __half hh = __float2half_rn(a);
+        ep.vt16_hi[at0 + (long long)e * ep.vt_pitch] = hh;
+        ep.vt16_lo[at0 + (long long)e * ep.vt_pitch] = __float2half_rn(a - __half2float(hh));
+      }
+      continue;
+    }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float val = fold ? __fmul_rn(st.y, __fmaf_rn(-st.x, us[e], vals[e])) : vals[e];

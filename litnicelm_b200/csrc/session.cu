@@ -106,6 +106,8 @@ struct TcWeight {
   __half *h_hi = nullptr, *h_lo = nullptr;
   float *h_inv_scale = nullptr;  // device float
   TcMatrix f64{}, f128{}, f256{};
+  // QKV projection feeding the fp16-pair attention: fixed scale and inverse per 64 output columns (launch_head_scales)
+  float *head_scale = nullptr, *head_inv = nullptr;
   bool usable() const { return has64 || has128; }
 };
 
@@ -156,6 +158,10 @@ struct litnice_b200_session {
   long long vt_rows = 0;
   int vt_pitch = 0;
   TcMatrix qk_map{}, vt_map{};
+  // the same as fp16 pairs under fixed per-head scales (attention_tc16.cu; LITNICE_B200_ATTN16=0 keeps the TF32 pairs)
+  bool attn16 = false;
+  __half *qk16_hi = nullptr, *qk16_lo = nullptr, *vt16_hi = nullptr, *vt16_lo = nullptr;
+  TcMatrix qk16_map{}, vt16_map{};
   // measurement aid (LITNICE_B200_ATTN_TIMELINE, profile_step only): 10 stamps per profiled attention launch
   unsigned long long *attn_timeline = nullptr;
   int attn_timeline_used = 0;
@@ -244,6 +250,10 @@ void free_activations(litnice_b200_session *s) {
   }
   if (s->row_stats) cudaFree(s->row_stats);
   s->row_stats = nullptr;
+  for (__half **p : {&s->qk16_hi, &s->qk16_lo}) {
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+  }
   for (TcPairF16 *p : {&s->pair_ln, &s->pair_ctx, &s->pair_h}) {
     if (p->hi) cudaFree(p->hi);
     if (p->lo) cudaFree(p->lo);
@@ -319,7 +329,18 @@ void ensure_rows(litnice_b200_session *s, long long rows) {
     }
     LB_CUDA(cudaMemsetAsync(s->row_stats, 0, (size_t)rows * TC_STAT_SLOTS * sizeof(double2), s->st));
   }
-  if (s->tc_attn) {
+  if (s->attn16) {
+    const size_t bytes = (size_t)rows * 3 * D * 2;
+    if (cudaMalloc(reinterpret_cast<void **>(&s->qk16_hi), bytes) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void **>(&s->qk16_lo), bytes) != cudaSuccess) {
+      free_activations(s);
+      throw std::bad_alloc();
+    }
+    LB_CUDA(cudaMemsetAsync(s->qk16_hi, 0, bytes, s->st));
+    LB_CUDA(cudaMemsetAsync(s->qk16_lo, 0, bytes, s->st));
+    tc_make_map_f16(&s->qk16_map.hi, s->qk16_hi, (unsigned long long)rows, 3 * D, TC_BM);
+    tc_make_map_f16(&s->qk16_map.lo, s->qk16_lo, (unsigned long long)rows, 3 * D, TC_BM);
+  } else if (s->tc_attn) {
     alloc(&s->qkv_hi, rows * 3 * D);
     alloc(&s->qkv_lo, rows * 3 * D);
     LB_CUDA(cudaMemsetAsync(s->qkv_hi, 0, rows * 3 * D * 4, s->st));
@@ -338,7 +359,29 @@ void ensure_attention_scratch(litnice_b200_session *s, int B, int s_lo, int s_hi
     // V^T: one row per (stream, column), one entry per position, whole key tiles
     const long long rows = (long long)B * s->dims.d_model;
     const int pitch = (s_hi + 127) / 128 * 128;
-    if (rows > s->vt_rows || pitch > s->vt_pitch) {
+    if ((rows > s->vt_rows || pitch > s->vt_pitch) && s->attn16) {
+      LB_CUDA(cudaStreamSynchronize(s->st));
+      const long long new_rows = rows > s->vt_rows ? rows : s->vt_rows;
+      const int new_pitch = pitch > s->vt_pitch ? pitch : s->vt_pitch;
+      for (__half **p : {&s->vt16_hi, &s->vt16_lo}) {
+        if (*p) cudaFree(*p);
+        *p = nullptr;
+      }
+      s->vt_rows = 0;
+      s->vt_pitch = 0;
+      const size_t bytes = (size_t)new_rows * new_pitch * 2;
+      if (cudaMalloc(reinterpret_cast<void **>(&s->vt16_hi), bytes) != cudaSuccess) throw std::bad_alloc();
+      if (cudaMalloc(reinterpret_cast<void **>(&s->vt16_lo), bytes) != cudaSuccess) throw std::bad_alloc();
+      // positions past a stream's length are multiplied by zero probabilities:
+      // they must hold finite values from the start
+      LB_CUDA(cudaMemsetAsync(s->vt16_hi, 0, bytes, s->st));
+      LB_CUDA(cudaMemsetAsync(s->vt16_lo, 0, bytes, s->st));
+      tc_make_map_f16(&s->vt16_map.hi, s->vt16_hi, (unsigned long long)new_rows, (unsigned long long)new_pitch, 64);
+      tc_make_map_f16(&s->vt16_map.lo, s->vt16_lo, (unsigned long long)new_rows, (unsigned long long)new_pitch, 64);
+      s->vt_rows = new_rows;
+      s->vt_pitch = new_pitch;
+      ++s->generation;
+    } else if (rows > s->vt_rows || pitch > s->vt_pitch) {
       LB_CUDA(cudaStreamSynchronize(s->st));
       const long long new_rows = rows > s->vt_rows ? rows : s->vt_rows;
       const int new_pitch = pitch > s->vt_pitch ? pitch : s->vt_pitch;
@@ -497,8 +540,6 @@ void enqueue_body(litnice_b200_session *s, int B, int sl, const LoopState *dstat
     const float *qkv_bias = fold ? (*tw)[0].ln_v : P(s, o.qkv_b);
     if (s->f16) {
       // every projection input is an fp16 pair written by the kernel that produced it
-      consume1.vt_hi = s->vt_hi;
-      consume1.vt_lo = s->vt_lo;
       consume1.vt_col0 = 2 * D;
       consume1.vt_rows = D;
       consume1.vt_pitch = s->vt_pitch;
@@ -506,18 +547,31 @@ void enqueue_body(litnice_b200_session *s, int B, int sl, const LoopState *dstat
       consume1.vt_streams = B;
       consume1.state = dstate;
       consume1.bias = qkv_bias;
-      consume1.c_hi = s->qkv_hi;  // Q and K stay TF32 pairs for the attention kernel
-      consume1.c_lo = s->qkv_lo;
+      if (s->attn16) {  // Q, K and V^T as fp16 pairs under the heads' fixed scales
+        consume1.qk16_hi = s->qk16_hi;
+        consume1.qk16_lo = s->qk16_lo;
+        consume1.vt16_hi = s->vt16_hi;
+        consume1.vt16_lo = s->vt16_lo;
+        consume1.col_scale = (*tw)[0].head_scale;
+      } else {  // TF32 pairs
+        consume1.vt_hi = s->vt_hi;
+        consume1.vt_lo = s->vt_lo;
+        consume1.c_hi = s->qkv_hi;
+        consume1.c_lo = s->qkv_lo;
+      }
       projection_f16(s, PAIR_LN, R, D, &(*tw)[0], 3 * D, consume1);
       {
         ClassTimer t(s, &s->attn_ev);
-        launch_attention_tc(s->qk_map, s->vt_map, nullptr, nullptr, B, sl, d.n_heads, D, s->attn_scratch,
-                            s->attn_counters, dstate, s->err_dev, s->st,
-                            (s->stamping && s->attn_timeline &&
-                             s->attn_timeline_used < litnice_b200_session::kTimelineSlots)
-                                ? s->attn_timeline + 32 * s->attn_timeline_used++
-                                : nullptr,
-                            &s->pair_ctx);
+        unsigned long long *tl = (s->stamping && s->attn_timeline &&
+                                  s->attn_timeline_used < litnice_b200_session::kTimelineSlots)
+                                     ? s->attn_timeline + 32 * s->attn_timeline_used++
+                                     : nullptr;
+        if (s->attn16)
+          launch_attention_tc16(s->qk16_map, s->vt16_map, (*tw)[0].head_inv, B, sl, d.n_heads, D, s->attn_scratch,
+                                s->attn_counters, dstate, s->err_dev, s->st, tl, s->pair_ctx);
+        else
+          launch_attention_tc(s->qk_map, s->vt_map, nullptr, nullptr, B, sl, d.n_heads, D, s->attn_scratch,
+                              s->attn_counters, dstate, s->err_dev, s->st, tl, &s->pair_ctx);
         ++s->launches;
       }
       TcEpilogue e_out = produce;
@@ -780,6 +834,16 @@ void prepare_tc_weights(litnice_b200_session *s) {
   s->tcw.resize(d.n_layers);
   for (int l = 0; l < d.n_layers; ++l) {
     const LayerOff &o = s->lay.layer[l];
+    if (s->attn16) {
+      TcWeight &q = s->tcw[l][0];
+      if (q.head_scale == nullptr) {
+        if (cudaMalloc(reinterpret_cast<void **>(&q.head_scale), (size_t)(3 * D / 64) * 4) != cudaSuccess ||
+            cudaMalloc(reinterpret_cast<void **>(&q.head_inv), (size_t)(3 * D / 64) * 4) != cudaSuccess)
+          throw std::bad_alloc();
+      }
+      launch_head_scales(P(s, o.qkv_w), D, 3 * D, P(s, o.ln1_g), P(s, o.ln1_b), P(s, o.qkv_b), q.head_scale, q.head_inv,
+                         s->st);
+    }
     if (s->ln_fold) {
       prepare_one(s, &s->tcw[l][0], P(s, o.qkv_w), D, 3 * D, P(s, o.ln1_g), P(s, o.ln1_b), P(s, o.qkv_b), s->f16);
       prepare_one(s, &s->tcw[l][2], P(s, o.w1), D, F, P(s, o.ln2_g), P(s, o.ln2_b), P(s, o.b1), s->f16);
@@ -941,6 +1005,8 @@ static int session_create_impl(const litnice_b200_dims *dims, int32_t max_stream
     const char *f16_env = std::getenv("LITNICE_B200_F16");
     s->f16 = s->tc_attn && s->ln_fold && !(f16_env && f16_env[0] == '0');
     if (s->f16) must(cudaMalloc(reinterpret_cast<void **>(&s->amax_scratch), sizeof(int)));
+    const char *a16_env = std::getenv("LITNICE_B200_ATTN16");
+    s->attn16 = s->f16 && !(a16_env && a16_env[0] == '0');
     size_t lr = (size_t)(max_streams < 8 ? 8 : max_streams);
     if (s->tc) lr = (lr + TC_BM - 1) / TC_BM * TC_BM;
     s->xl_rows = (long long)lr;
@@ -1008,6 +1074,8 @@ void litnice_b200_session_destroy(litnice_b200_session *s) {
   if (s->amax_scratch) cudaFree(s->amax_scratch);
   if (s->vt_hi) cudaFree(s->vt_hi);
   if (s->vt_lo) cudaFree(s->vt_lo);
+  if (s->vt16_hi) cudaFree(s->vt16_hi);
+  if (s->vt16_lo) cudaFree(s->vt16_lo);
   if (s->tc_counters) cudaFree(s->tc_counters);
   if (s->attn_scratch) cudaFree(s->attn_scratch);
   if (s->attn_counters) cudaFree(s->attn_counters);
@@ -1020,6 +1088,8 @@ void litnice_b200_session_destroy(litnice_b200_session *s) {
       if (w.h_hi) cudaFree(w.h_hi);
       if (w.h_lo) cudaFree(w.h_lo);
       if (w.h_inv_scale) cudaFree(w.h_inv_scale);
+      if (w.head_scale) cudaFree(w.head_scale);
+      if (w.head_inv) cudaFree(w.head_inv);
     }
   if (s->tc_head.hi) cudaFree(s->tc_head.hi);
   if (s->tc_head.lo) cudaFree(s->tc_head.lo);

@@ -204,6 +204,17 @@ __device__ __forceinline__ void tc_mma_tf32_ts(unsigned tmem_d, unsigned tmem_a,
       ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with fp16 operands: a 32-bit tensor-memory column holds two consecutive k elements
+// (the lower k in the low half), so an instruction (16 of k) reads 8 columns of A.
+__device__ __forceinline__ void tc_mma_f16_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long b_desc,
+                                              unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void tc_st32(unsigned taddr, const unsigned (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "

@@ -117,3 +117,36 @@ def test_token_loop_graph_replay_equals_direct_launches(arena):
         else:
             os.environ["LITNICE_B200_GRAPHS"] = old
     assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("seq", [200, 384])
+def test_fixed_head_scales_with_skewed_weights(oracle, seq):
+    """The fp16-pair attention keeps Q, K and V under scales derived from the weights alone
+    (a bound over every possible LayerNorm output). Weights whose heads and thirds differ by
+    orders of magnitude, a wide LayerNorm scale and large shifts and biases must neither
+    overflow fp16 nor lose accuracy: logits against the oracle at the path's tolerance."""
+    arena = formats.make_param_arena(DIMS, 4321, bias_std=0.05, ln_std=0.3)
+    lay = formats.ParamLayout.build(DIMS)
+    D = DIMS.d_model
+    rng = np.random.default_rng(5)
+    for l in range(DIMS.n_layers):
+        w = lay.view(arena, f"layer{l}.attn_qkv_w")
+        b = lay.view(arena, f"layer{l}.attn_qkv_b")
+        # Q of head 0 large, K of head 1 tiny, V thirds 30x apart; one outlier column per third
+        col_scale = np.ones(3 * D, dtype=np.float32)
+        col_scale[0:64] = 40.0
+        col_scale[D + 64:D + 128] = 1e-3
+        col_scale[2 * D:2 * D + 64] = 30.0
+        col_scale[[5, D + 70, 2 * D + 100]] *= 25.0
+        w *= col_scale[None, :]
+        b *= col_scale[None, :]
+        lay.view(arena, f"layer{l}.ln1_beta")[...] += rng.normal(0.0, 2.0, size=(1, D)).astype(np.float32)
+    ids = formats.zipf_prompt(DIMS.vocab, seq, 600 + seq)
+    want = oracle.forward(DIMS, arena, ids)
+    assert np.isfinite(want).all()
+    with Session(DIMS, 2) as s:
+        s.load_params(arena)
+        got = s.forward(np.stack([ids, ids]), all_rows=True)
+    assert np.isfinite(got).all()
+    assert rel_err(got[0], want) < LOGIT_RTOL
+    assert np.array_equal(got[0], got[1])
