@@ -16,15 +16,17 @@
 //
 //   S = Q K^T   A = Q tile (128 queries x 64), B = K tile (128 keys x 64), K-major fp16
 //               pairs; one chain of 12 instructions (N = 128) in tensor memory.
-//   P           eight warps read S (thread = one query row and 64 of the 128 keys),
-//               scale, mask and exponentiate against the maximum of their own 64 keys,
+//   P           sixteen warps read S (thread = one query row and 32 of the 128 keys),
+//               scale, mask and exponentiate against the maximum of their own 32 keys,
 //               and store P * 2^12 as an fp16 pair in tensor memory (two keys per column).
-//   O += P V    A = P from tensor memory, B = V^T tile (64 x 128 keys, K-major), two
-//               chains (keys 0-63, 64-127) of 12 instructions (N = 64), rescaled to the
-//               row's running maximum and added into fp32 registers by the same threads.
+//   O += P V    A = P from tensor memory, B = V^T tile (64 x 128 keys, K-major), four
+//               chains (32 keys each) of 6 instructions (N = 64), rescaled to the row's
+//               running maximum and added into fp32 registers by the same threads (each
+//               16 of the 64 output columns). The softmax is bound by latency, not by
+//               issue slots: four warps per scheduler hide it better than two.
 //
 // Warp 0 issues TMA, warp 1 owns tensor memory and issues the MMAs (S of tile t+1
-// ahead of P V of tile t), warps 2-9 do the softmax and the output. Key ranges of a
+// ahead of P V of tile t), warps 2-17 do the softmax and the output. Key ranges of a
 // query tile may be cut into chunks for separate CTAs whose partial results the last
 // CTA to finish merges in chunk order. Every mbarrier wait is bounded; no cluster
 // launch and no multicast.
@@ -40,8 +42,15 @@ namespace {
 constexpr int TB_BQ = 128;   // query rows per CTA (one UMMA M = 128 tile)
 constexpr int TB_BK = 128;   // keys per tile
 constexpr int TB_DH = 64;    // head dimension
-constexpr int TB_THREADS = 320;
-constexpr int TB_SOFTMAX_THREADS = 256;
+#ifndef LB_ATTN16_GROUPS
+#define LB_ATTN16_GROUPS 4
+#endif
+constexpr int TB_G = LB_ATTN16_GROUPS;  // threads per query row = accumulation chains of P V per key tile
+constexpr int TB_KPT = TB_BK / TB_G;    // keys per thread and tile
+constexpr int TB_OC = TB_DH / TB_G;     // output columns per thread
+static_assert(TB_G == 2 || TB_G == 4, "16-column tensor-memory accesses");
+constexpr int TB_SOFTMAX_THREADS = 128 * TB_G;
+constexpr int TB_THREADS = 64 + TB_SOFTMAX_THREADS;
 constexpr float TB_NEG = -3.402823466e+38f;
 constexpr int TB_MAX_CHUNKS = 16;                   // as attention_tc_plan cuts them
 constexpr int TB_PART = TB_BQ * TB_DH + 2 * TB_BQ;  // floats of one partial: o[128][64], m[128], l[128]
@@ -61,9 +70,9 @@ constexpr int TB_Q_OFF = 0;
 constexpr int TB_K_OFF = TB_Q_OFF + TB_Q_BYTES;
 constexpr int TB_V_OFF = TB_K_OFF + TB_STAGES * TB_K_BYTES;
 constexpr int TB_BAR_OFF = TB_V_OFF + TB_STAGES * TB_V_BYTES;  // 14 barriers + holders
-constexpr int TB_XCH_OFF = TB_BAR_OFF + 256;             // [2 parities][max half 0, max half 1, sum half 0, sum half 1][128]
-constexpr int TB_AMAX_OFF = TB_XCH_OFF + 8 * TB_BQ * 4;  // [2 halves][128 rows]: largest magnitudes of the output rows
-constexpr int TB_SMEM = TB_AMAX_OFF + 2 * TB_BQ * 4 + 1024;
+constexpr int TB_XCH_OFF = TB_BAR_OFF + 256;  // [2 parities][maxima of the G key groups, their sums][128]
+constexpr int TB_AMAX_OFF = TB_XCH_OFF + 2 * 2 * TB_G * TB_BQ * 4;  // [G][128 rows]: largest magnitudes of the output rows
+constexpr int TB_SMEM = TB_AMAX_OFF + TB_G * TB_BQ * 4 + 1024;
 constexpr int TB_STAGE16_LD = TB_DH * 2 + 16;  // bytes per row of the staged fp16 output tile: conflict-free 16-byte accesses
 static_assert(TB_MERGE_SLOTS * TB_O_BYTES <= TB_BAR_OFF, "merge slots overlay the operand tiles only");
 static_assert(2 * TB_BQ * TB_STAGE16_LD <= TB_BAR_OFF, "output staging overlays the operand tiles only");
@@ -72,7 +81,7 @@ static_assert(2 * TB_BQ * TB_STAGE16_LD <= TB_BAR_OFF, "output staging overlays 
 constexpr unsigned TB_S_COL = 0;      // S: 128 columns (keys)
 constexpr unsigned TB_PHI_COL = 128;  // P high parts: 64 columns (two keys each)
 constexpr unsigned TB_PLO_COL = 192;  // P low parts
-constexpr unsigned TB_O_COL = 256;    // O chains: 2 x 64 columns (keys 0-63, keys 64-127)
+constexpr unsigned TB_O_COL = 256;    // O chains: G x 64 columns (one per key group)
 
 __device__ __forceinline__ float fast_exp2_16(float x) {
   float y;
@@ -101,7 +110,7 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
   volatile unsigned *tmem_holder = reinterpret_cast<volatile unsigned *>(base_ptr + TB_BAR_OFF + 128);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + TB_BAR_OFF + 132);
   volatile int *last_flag = reinterpret_cast<volatile int *>(base_ptr + TB_BAR_OFF + 136);
-  // per tile parity: maximum [half][row] and sum [half][row] of each thread's 64 keys
+  // per tile parity: maximum [group][row] and sum [group][row] of each thread's keys
   float *xch = reinterpret_cast<float *>(base_ptr + TB_XCH_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -289,22 +298,23 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
         const unsigned p_hi = tmem_base + TB_PHI_COL, p_lo = tmem_base + TB_PLO_COL;
         const unsigned vb = base + TB_V_OFF + (unsigned)(it & 1) * TB_V_BYTES;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          // chain c covers 64 keys: the keys one softmax thread scales by its own maximum
+        for (int c = 0; c < TB_G; ++c) {
+          // chain c covers the keys one softmax thread scales by its own maximum
           const unsigned tmem_d = tmem_base + TB_O_COL + (unsigned)(c * TB_DH);
-          const unsigned long long b_hi = umma_desc_k128(vb + c * TB_VSLAB);
-          const unsigned long long b_lo = umma_desc_k128(vb + (2 + c) * TB_VSLAB);
+          const int key0 = c * TB_KPT, slab = key0 / 64;  // a slab of the stage holds 64 keys (128-byte rows)
+          const unsigned long long b_hi = umma_desc_k128(vb + slab * TB_VSLAB);
+          const unsigned long long b_lo = umma_desc_k128(vb + (2 + slab) * TB_VSLAB);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);
-            const unsigned ac = (unsigned)(c * 32 + ks * 8);  // 16 keys = 8 columns
+          for (int ks = 0; ks < TB_KPT / 16; ++ks) {
+            const unsigned long long adv = (unsigned long long)(((key0 % 64) + ks * 16) * 2 >> 4);
+            const unsigned ac = (unsigned)((key0 + ks * 16) / 2);  // 16 keys = 8 columns
             tc_mma_f16_ts(tmem_d, p_lo + ac, b_hi + adv, idesc_o, ks == 0 ? 0u : 1u);
             tc_mma_f16_ts(tmem_d, p_hi + ac, b_lo + adv, idesc_o, 1u);
           }
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);
-            const unsigned ac = (unsigned)(c * 32 + ks * 8);
+          for (int ks = 0; ks < TB_KPT / 16; ++ks) {
+            const unsigned long long adv = (unsigned long long)(((key0 % 64) + ks * 16) * 2 >> 4);
+            const unsigned ac = (unsigned)((key0 + ks * 16) / 2);
             tc_mma_f16_ts(tmem_d, p_hi + ac, b_hi + adv, idesc_o, 1u);
           }
         }
@@ -323,8 +333,8 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
     }
     __syncwarp();
   } else {
-    // ---- softmax + output: thread = query row `r`, key half `g` (64 of the 128 keys = one O chain;
-    //      32 of the 64 output columns) ----
+    // ---- softmax + output: thread = query row `r`, key group `g` (TB_KPT of the 128 keys = one O chain;
+    //      TB_OC of the 64 output columns) ----
     // The head's three fixed scales (immutable since the weights were loaded): Q and K in the
     // exponent's factor, V (and the 2^12 of P) in the final normalisation.
     const int n_blocks = d_model / TB_DH;
@@ -332,106 +342,126 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
     const float out_factor = head_inv_scale[2 * n_blocks + h] * TB_P_INV;
     pdl_wait();  // scratch and ctx writes must follow the predecessor
     const int q = warp & 3;          // TMEM lane quarter this warp may touch
-    const int g = (warp - 2) >> 2;   // 0: warps 2-5, 1: warps 6-9
+    const int g = (warp - 2) >> 2;   // warps 2-5: group 0, warps 6-9: group 1, ...
     const int r = q * 32 + lane;
     const int qi = q0 + r;
     const unsigned lane_base = tmem_base + ((unsigned)(q * 32) << 16);
-    float o[32];
+    float o[TB_OC];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) o[j] = 0.f;
-    // Running maximum (of scores times log2 e) and sum of the whole row; both
+    for (int j = 0; j < TB_OC; ++j) o[j] = 0.f;
+    // Running maximum (of scores times log2 e) and sum of the whole row; all
     // threads of a row keep identical copies.
     float m_run = TB_NEG, l_run = 0.f;
     bool ok = true;
 
-    // O(t) = chain 0 * 2^(m0 - M) + chain 1 * 2^(m1 - M): each chain was scaled by the maximum of its own 64 keys
+    // O(t) = sum over chains c of chain c * 2^(m_c - M): each chain was scaled by the maximum of its own keys
     auto drain = [&](int t) {
-      const float *x = xch + (t & 1) * 4 * TB_BQ;
-      const float m0 = x[r], m1 = x[TB_BQ + r], ps0 = x[2 * TB_BQ + r], ps1 = x[3 * TB_BQ + r];
-      const float m_new = fmaxf(m_run, fmaxf(m0, m1));
-      const float a = fast_exp2_16(m_run - m_new), w0 = fast_exp2_16(m0 - m_new), w1 = fast_exp2_16(m1 - m_new);
-      unsigned c0[32], c1[32];
-      tc_ld32(lane_base + TB_O_COL + (unsigned)(g * 32), c0);
-      tc_ld32(lane_base + TB_O_COL + (unsigned)(TB_DH + g * 32), c1);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const float *x = xch + (t & 1) * 2 * TB_G * TB_BQ;
+      float mc[TB_G], pc[TB_G];
+      float m_new = m_run;
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        o[j] = fmaf(o[j], a, fmaf(__uint_as_float(c0[j]), w0, __fmul_rn(__uint_as_float(c1[j]), w1)));
-      l_run = fmaf(l_run, a, fmaf(ps0, w0, __fmul_rn(ps1, w1)));
+      for (int c = 0; c < TB_G; ++c) {
+        mc[c] = x[c * TB_BQ + r];
+        pc[c] = x[(TB_G + c) * TB_BQ + r];
+        m_new = fmaxf(m_new, mc[c]);
+      }
+      const float a = fast_exp2_16(m_run - m_new);
+      unsigned cv[TB_G][16 * (TB_OC / 16)];
+#pragma unroll
+      for (int c = 0; c < TB_G; ++c)
+#pragma unroll
+        for (int j0 = 0; j0 < TB_OC; j0 += 16)
+          tc_ld16(lane_base + TB_O_COL + (unsigned)(c * TB_DH + g * TB_OC + j0),
+                  *reinterpret_cast<unsigned(*)[16]>(&cv[c][j0]));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      float ls = l_run * a;
+#pragma unroll
+      for (int j = 0; j < TB_OC; ++j) o[j] *= a;
+#pragma unroll
+      for (int c = 0; c < TB_G; ++c) {
+        const float w = fast_exp2_16(mc[c] - m_new);
+        ls = fmaf(pc[c], w, ls);
+#pragma unroll
+        for (int j = 0; j < TB_OC; ++j) o[j] = fmaf(__uint_as_float(cv[c][j]), w, o[j]);
+      }
+      l_run = ls;
       m_run = m_new;
     };
 
     for (int it = 0; it < ntiles && ok; ++it) {
       const unsigned ph = (unsigned)it & 1u;
-      const int kbase = (kt_begin + it) * TB_BK + g * 64;
+      const int kbase = (kt_begin + it) * TB_BK + g * TB_KPT;
       ok = mbar_wait_warp(s_full, ph, abort_flag, err, 18);
       if (!ok) break;
       if (stamp && it == 0 && warp == 2 && lane == 0) timeline[3] = global_timer();
       if (stamp && nchunks == 1 && it >= 1 && it <= 4 && warp == 2 && lane == 0) timeline[11 + it] = global_timer();
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      float p[64];
+      float p[TB_KPT];
       {
-        unsigned t0[32], t1[32];
-        tc_ld32(lane_base + TB_S_COL + (unsigned)(g * 64), t0);
-        tc_ld32(lane_base + TB_S_COL + (unsigned)(g * 64 + 32), t1);
+        unsigned t0[TB_KPT];
+#pragma unroll
+        for (int j0 = 0; j0 < TB_KPT; j0 += 16)
+          tc_ld16(lane_base + TB_S_COL + (unsigned)(g * TB_KPT + j0), *reinterpret_cast<unsigned(*)[16]>(&t0[j0]));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(s_read);  // S may be overwritten by the next tile's product
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          p[j] = __uint_as_float(t0[j]);
-          p[32 + j] = __uint_as_float(t1[j]);
-        }
+        for (int j = 0; j < TB_KPT; ++j) p[j] = __uint_as_float(t0[j]);
       }
       // Raw scores of the scaled operands: the maximum commutes with the positive factor, and the factor
       // joins the subtraction in one fused multiply-add: p = 2^(s * c - max(s) * c). Only the tile on
       // the diagonal has keys past a query; the others skip the mask.
-      float mx = TB_NEG, psum = 0.f;
+      // (maximum and sum as four interleaved partial chains: a single chain of dependent operations
+      // is as long as the thread's keys)
+      float mx4[4] = {TB_NEG, TB_NEG, TB_NEG, TB_NEG}, ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      float mx;
       if (kt_begin + it == qt) {
 #pragma unroll
-        for (int j = 0; j < 64; ++j)
-          if (kbase + j <= qi) mx = fmaxf(mx, p[j]);
-        mx = __fmul_rn(mx, qk_factor);
+        for (int j = 0; j < TB_KPT; ++j)
+          if (kbase + j <= qi) mx4[j & 3] = fmaxf(mx4[j & 3], p[j]);
+        mx = __fmul_rn(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])), qk_factor);
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
+        for (int j = 0; j < TB_KPT; ++j) {
           p[j] = (kbase + j <= qi) ? fast_exp2_16(__fmaf_rn(p[j], qk_factor, -mx)) : 0.f;
-          psum += p[j];
+          ps4[j & 3] += p[j];
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < 64; ++j) mx = fmaxf(mx, p[j]);
-        mx = __fmul_rn(mx, qk_factor);
+        for (int j = 0; j < TB_KPT; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], p[j]);
+        mx = __fmul_rn(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])), qk_factor);
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
+        for (int j = 0; j < TB_KPT; ++j) {
           p[j] = fast_exp2_16(__fmaf_rn(p[j], qk_factor, -mx));
-          psum += p[j];
+          ps4[j & 3] += p[j];
         }
       }
+      const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       if (it > 0) {  // PV(it-1) complete: P may be overwritten, O(it-1) can be read
         ok = mbar_wait_warp(o_full, ph ^ 1u, abort_flag, err, 19);
         if (!ok) break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       {
-        float *x = xch + (it & 1) * 4 * TB_BQ;
+        float *x = xch + (it & 1) * 2 * TB_G * TB_BQ;
         x[g * TB_BQ + r] = mx;
-        x[(2 + g) * TB_BQ + r] = psum;
+        x[(TB_G + g) * TB_BQ + r] = psum;
       }
-      {
-        // the thread's 64 keys as 32 columns of packed pairs, times 2^12
-        unsigned hi[32], lo[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float a = p[2 * j] * TB_P_SCALE, c = p[2 * j + 1] * TB_P_SCALE;
+      for (int j0 = 0; j0 < TB_KPT / 2; j0 += 16) {
+        // the thread's keys as columns of packed pairs, times 2^12
+        unsigned hi[16], lo[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float a = p[2 * (j0 + j)] * TB_P_SCALE, c = p[2 * (j0 + j) + 1] * TB_P_SCALE;
           const __half2 h2 = __floats2half2_rn(a, c);
           const float2 f2 = __half22float2(h2);
           const __half2 l2 = __floats2half2_rn(a - f2.x, c - f2.y);
           hi[j] = *reinterpret_cast<const unsigned *>(&h2);
           lo[j] = *reinterpret_cast<const unsigned *>(&l2);
         }
-        tc_st32(lane_base + TB_PHI_COL + (unsigned)(g * 32), hi);
-        tc_st32(lane_base + TB_PLO_COL + (unsigned)(g * 32), lo);
+        tc_st16(lane_base + TB_PHI_COL + (unsigned)(g * (TB_KPT / 2) + j0), hi);
+        tc_st16(lane_base + TB_PLO_COL + (unsigned)(g * (TB_KPT / 2) + j0), lo);
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       if (stamp && it == 0 && warp == 2 && lane == 0) timeline[4] = global_timer();
@@ -458,8 +488,9 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
       float *mine = part + (first_item + chunk) * TB_PART;
       // partial outputs as [column / 4][row][4]: the 32 rows of a warp are contiguous
 #pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        reinterpret_cast<float4 *>(mine)[(g * 8 + j / 4) * TB_BQ + r] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+      for (int j = 0; j < TB_OC; j += 4)
+        reinterpret_cast<float4 *>(mine)[(g * (TB_OC / 4) + j / 4) * TB_BQ + r] =
+            make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
       if (g == 0) {
         mine[TB_BQ * TB_DH + r] = m_run;
         mine[TB_BQ * TB_DH + TB_BQ + r] = l_tot;
@@ -515,9 +546,9 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
           wv[j] = j < nchunks ? fast_exp2_16(wv[j] - mm) : 0.f;
           ll = fmaf(lv[j], wv[j], ll);
         }
-        float acc[32];
+        float acc[TB_OC];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) acc[c] = 0.f;
+        for (int c = 0; c < TB_OC; ++c) acc[c] = 0.f;
         // Chunks are combined in chunk order.
 #pragma unroll 1
         for (int first = 0, batch = 0; first < nchunks; first += TB_MERGE_SLOTS, ++batch) {
@@ -531,14 +562,14 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
           const int n = got ? min(TB_MERGE_SLOTS, nchunks - first) : 0;
 #pragma unroll 1
           for (int j = 0; j < n; ++j) {
-            const float4 *ps = reinterpret_cast<const float4 *>(base_ptr + j * TB_O_BYTES) + g * 8 * TB_BQ + r;
+            const float4 *ps = reinterpret_cast<const float4 *>(base_ptr + j * TB_O_BYTES) + g * (TB_OC / 4) * TB_BQ + r;
             const float w = wv[first + j];
             if (first + j == chunk) {  // uniform over the CTA
 #pragma unroll
-              for (int c = 0; c < 32; ++c) acc[c] = fmaf(o[c], w, acc[c]);
+              for (int c = 0; c < TB_OC; ++c) acc[c] = fmaf(o[c], w, acc[c]);
             } else {
 #pragma unroll
-              for (int c = 0; c < 8; ++c) {
+              for (int c = 0; c < TB_OC / 4; ++c) {
                 const float4 t = ps[c * TB_BQ];
                 acc[4 * c] = fmaf(t.x, w, acc[4 * c]);
                 acc[4 * c + 1] = fmaf(t.y, w, acc[4 * c + 1]);
@@ -549,7 +580,7 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
           }
         }
 #pragma unroll
-        for (int c = 0; c < 32; ++c) o[c] = acc[c];
+        for (int c = 0; c < TB_OC; ++c) o[c] = acc[c];
         asm volatile("bar.sync 1, %0;" ::"n"(TB_SOFTMAX_THREADS) : "memory");  // before the output is staged over the slots
         l_tot = ll;
       }
@@ -557,32 +588,33 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
 
     if (stamp && warp == 2 && lane == 0) timeline[6] = global_timer();
     // Output as the fp16 pair the out-projection reads, one scale per row of this head's 64 columns.
-    // A thread holds 32 columns of one row, so direct stores would touch 32 different lines per
+    // A thread holds a few columns of one row, so direct stores would touch 32 different lines per
     // instruction: normalise, exchange the row's largest magnitudes, convert, transpose through the
     // (now idle) tiles in shared memory, and store whole rows.
     if (cta_out) {
-      float *amx = reinterpret_cast<float *>(base_ptr + TB_AMAX_OFF);  // [2][128]
+      float *amx = reinterpret_cast<float *>(base_ptr + TB_AMAX_OFF);  // [G][128]
       unsigned char *st_hi = base_ptr + TB_Q_OFF;                      // [128][TB_STAGE16_LD] bytes
       unsigned char *st_lo = st_hi + TB_BQ * TB_STAGE16_LD;
       const float inv = finish ? out_factor / l_tot : 0.f;
       float am = 0.f;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
+      for (int j = 0; j < TB_OC; ++j) {
         o[j] *= inv;
         am = fmaxf(am, fabsf(o[j]));
       }
       amx[g * TB_BQ + r] = am;
       asm volatile("bar.sync 1, %0;" ::"n"(TB_SOFTMAX_THREADS) : "memory");
-      am = fmaxf(amx[r], amx[TB_BQ + r]);
+#pragma unroll
+      for (int c = 0; c < TB_G; ++c) am = fmaxf(am, amx[c * TB_BQ + r]);
       float sinv;
       const float scale = f16_block_scale(am, &sinv);
 #pragma unroll
-      for (int j = 0; j < 32; j += 8) {
+      for (int j = 0; j < TB_OC; j += 8) {
         uint2 h0, l0, h1, l1;
         f16_pair4(make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]), scale, h0, l0);
         f16_pair4(make_float4(o[j + 4], o[j + 5], o[j + 6], o[j + 7]), scale, h1, l1);
-        *reinterpret_cast<uint4 *>(st_hi + r * TB_STAGE16_LD + g * 64 + j * 2) = make_uint4(h0.x, h0.y, h1.x, h1.y);
-        *reinterpret_cast<uint4 *>(st_lo + r * TB_STAGE16_LD + g * 64 + j * 2) = make_uint4(l0.x, l0.y, l1.x, l1.y);
+        *reinterpret_cast<uint4 *>(st_hi + r * TB_STAGE16_LD + (g * TB_OC + j) * 2) = make_uint4(h0.x, h0.y, h1.x, h1.y);
+        *reinterpret_cast<uint4 *>(st_lo + r * TB_STAGE16_LD + (g * TB_OC + j) * 2) = make_uint4(l0.x, l0.y, l1.x, l1.y);
       }
       if (finish && g == 0 && q0 + r < s)
         ctx_f16.inv_scale[((long long)row0 + q0 + r) * (d_model / TC_F16_SLOT) + h] = sinv;

@@ -11,7 +11,10 @@ namespace lb {
 // terms (bias, folded-LayerNorm u) and the residual rows of the first step. Loaded ahead of
 // it (before the wait for the cluster's partial tiles), because the store loop would
 // otherwise start with an L2 round trip. Same thread-to-element mapping as tc_store_rows.
-constexpr int TC_STORE_G = 2;  // rows a thread of the store phase has in flight per trip
+#ifndef LB_STORE_G
+#define LB_STORE_G 2
+#endif
+constexpr int TC_STORE_G = LB_STORE_G;  // rows a thread of the store phase has in flight per trip
 
 struct TcStoreFirst {
   float4 res[TC_STORE_G];
