@@ -16,17 +16,26 @@
 //
 //   S = Q K^T   A = Q tile (128 queries x 64), B = K tile (128 keys x 64), K-major fp16
 //               pairs; one chain of 12 instructions (N = 128) in tensor memory.
-//   P           sixteen warps read S (thread = one query row and 32 of the 128 keys),
-//               scale, mask and exponentiate against the maximum of their own 32 keys,
-//               and store P * 2^12 as an fp16 pair in tensor memory (two keys per column).
-//   O += P V    A = P from tensor memory, B = V^T tile (64 x 128 keys, K-major), four
-//               chains (32 keys each) of 6 instructions (N = 64), rescaled to the row's
+//   P           eight warps read S (thread = one query row and 64 of the 128 keys),
+//               scale, mask and exponentiate against the maximum of their own 64 keys,
+//               and store P * 2^12 as an fp16 pair over their own columns of S (two keys
+//               per column: the pair takes exactly the columns the scores had).
+//   O += P V    A = P from tensor memory, B = V^T tile (64 x 128 keys, K-major), two
+//               chains (64 keys each) of 12 instructions (N = 64), rescaled to the row's
 //               running maximum and added into fp32 registers by the same threads (each
-//               16 of the 64 output columns). The softmax is bound by latency, not by
-//               issue slots: four warps per scheduler hide it better than two.
+//               32 of the 64 output columns).
+// Tensor memory holds two S/P buffers and two O buffers (tile t uses buffers t mod 2), so
+// no product waits for the softmax threads to finish with the previous tile's buffers
+// (with single buffers every tile paid the chain P stored -> P V -> accumulators read back
+// -> next P stored). Measured on the config-4 batch, attention launches of one forward:
+// 23.4 ms on TF32 pairs with one stage of K and V^T; 17.8 ms on fp16 pairs with two stages
+// and single tensor-memory buffers, two or four threads per row alike (19.0 ms); 17.3 ms
+// with these buffers; four threads per row with two S/P buffers and one set of four O
+// chains: 19.2 ms. The steps of a tile (24 + 12 instructions of 64 and 128 columns, about
+// 1.4 us; the softmax threads' loop; the hand-overs between them) are of similar length.
 //
-// Warp 0 issues TMA, warp 1 owns tensor memory and issues the MMAs (S of tile t+1
-// ahead of P V of tile t), warps 2-17 do the softmax and the output. Key ranges of a
+// Warp 0 issues TMA, warp 1 owns tensor memory and issues the MMAs (S of tile t+2 behind
+// P V of tile t), warps 2-9 do the softmax and the output. Key ranges of a
 // query tile may be cut into chunks for separate CTAs whose partial results the last
 // CTA to finish merges in chunk order. Every mbarrier wait is bounded; no cluster
 // launch and no multicast.
@@ -43,12 +52,12 @@ constexpr int TB_BQ = 128;   // query rows per CTA (one UMMA M = 128 tile)
 constexpr int TB_BK = 128;   // keys per tile
 constexpr int TB_DH = 64;    // head dimension
 #ifndef LB_ATTN16_GROUPS
-#define LB_ATTN16_GROUPS 4
+#define LB_ATTN16_GROUPS 2
 #endif
 constexpr int TB_G = LB_ATTN16_GROUPS;  // threads per query row = accumulation chains of P V per key tile
 constexpr int TB_KPT = TB_BK / TB_G;    // keys per thread and tile
 constexpr int TB_OC = TB_DH / TB_G;     // output columns per thread
-static_assert(TB_G == 2 || TB_G == 4, "16-column tensor-memory accesses");
+static_assert(TB_G == 2, "two S/P and two O buffers of G chains each fill the 512 columns at G = 2");
 constexpr int TB_SOFTMAX_THREADS = 128 * TB_G;
 constexpr int TB_THREADS = 64 + TB_SOFTMAX_THREADS;
 constexpr float TB_NEG = -3.402823466e+38f;
@@ -70,18 +79,22 @@ constexpr int TB_Q_OFF = 0;
 constexpr int TB_K_OFF = TB_Q_OFF + TB_Q_BYTES;
 constexpr int TB_V_OFF = TB_K_OFF + TB_STAGES * TB_K_BYTES;
 constexpr int TB_BAR_OFF = TB_V_OFF + TB_STAGES * TB_V_BYTES;  // 14 barriers + holders
-constexpr int TB_XCH_OFF = TB_BAR_OFF + 256;  // [2 parities][maxima of the G key groups, their sums][128]
-constexpr int TB_AMAX_OFF = TB_XCH_OFF + 2 * 2 * TB_G * TB_BQ * 4;  // [G][128 rows]: largest magnitudes of the output rows
+constexpr int TB_XCH_SLOTS = 4;  // a warp may be one tile ahead of another that still reads the slot of two tiles ago
+constexpr int TB_XCH_OFF = TB_BAR_OFF + 256;  // [slot = tile mod 4][maxima of the G key groups, their sums][128]
+constexpr int TB_AMAX_OFF = TB_XCH_OFF + TB_XCH_SLOTS * 2 * TB_G * TB_BQ * 4;  // [G][128 rows]: largest magnitudes of the output rows
 constexpr int TB_SMEM = TB_AMAX_OFF + TB_G * TB_BQ * 4 + 1024;
 constexpr int TB_STAGE16_LD = TB_DH * 2 + 16;  // bytes per row of the staged fp16 output tile: conflict-free 16-byte accesses
 static_assert(TB_MERGE_SLOTS * TB_O_BYTES <= TB_BAR_OFF, "merge slots overlay the operand tiles only");
 static_assert(2 * TB_BQ * TB_STAGE16_LD <= TB_BAR_OFF, "output staging overlays the operand tiles only");
 
-// tensor-memory columns
-constexpr unsigned TB_S_COL = 0;      // S: 128 columns (keys)
-constexpr unsigned TB_PHI_COL = 128;  // P high parts: 64 columns (two keys each)
-constexpr unsigned TB_PLO_COL = 192;  // P low parts
-constexpr unsigned TB_O_COL = 256;    // O chains: G x 64 columns (one per key group)
+// tensor-memory columns: buffer b of S/P at 128 b (S: one column per key; the P pair of key group g
+// over that group's own columns: high parts at g * KPT, low parts at g * KPT + KPT / 2, two keys per
+// column), buffer b of O at 256 + 128 b (G chains of 64 columns)
+__device__ __forceinline__ constexpr unsigned tb_s_col(int b) { return (unsigned)(b * TB_BK); }
+__device__ __forceinline__ constexpr unsigned tb_phi_col(int b, int g) { return (unsigned)(b * TB_BK + g * TB_KPT); }
+__device__ __forceinline__ constexpr unsigned tb_plo_col(int b, int g) { return (unsigned)(b * TB_BK + g * TB_KPT + TB_KPT / 2); }
+__device__ __forceinline__ constexpr unsigned tb_o_col(int b) { return (unsigned)(2 * TB_BK + b * TB_G * TB_DH); }
+static_assert(2 * TB_BK + 2 * TB_G * TB_DH <= 512, "tensor memory");
 
 __device__ __forceinline__ float fast_exp2_16(float x) {
   float y;
@@ -101,16 +114,26 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char *base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const unsigned bar_base = base + TB_BAR_OFF;
-  const unsigned q_full = bar_base, s_full = bar_base + 8, p_ready = bar_base + 16, o_full = bar_base + 24,
-                 s_read = bar_base + 32, m_full = bar_base + 40;
-  auto k_full = [&](int st) { return bar_base + 48u + 8u * st; };
-  auto v_full = [&](int st) { return bar_base + 64u + 8u * st; };
-  auto k_free = [&](int st) { return bar_base + 80u + 8u * st; };
-  auto v_free = [&](int st) { return bar_base + 96u + 8u * st; };
-  volatile unsigned *tmem_holder = reinterpret_cast<volatile unsigned *>(base_ptr + TB_BAR_OFF + 128);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + TB_BAR_OFF + 132);
-  volatile int *last_flag = reinterpret_cast<volatile int *>(base_ptr + TB_BAR_OFF + 136);
-  // per tile parity: maximum [group][row] and sum [group][row] of each thread's keys
+  // Per buffer b = tile mod 2 (use j = tile / 2 of a buffer completes phase j of its barriers; no barrier
+  // can complete two phases before its waiter has seen the first: every arrival of use j + 1 depends,
+  // through the other barriers, on the waiter having passed use j):
+  //   s_full[b]   S complete (tcgen05.commit)            -> softmax threads
+  //   p_ready[b]  P stored over S (every softmax warp)   -> MMA warp
+  //   o_full[b]   P V complete (commit)                  -> softmax threads (read O), MMA warp (S/P buffer free)
+  //   o_free[b]   O read back (every softmax warp)       -> MMA warp
+  const unsigned q_full = bar_base, m_full = bar_base + 8;
+  auto k_full = [&](int st) { return bar_base + 16u + 8u * st; };
+  auto v_full = [&](int st) { return bar_base + 32u + 8u * st; };
+  auto k_free = [&](int st) { return bar_base + 48u + 8u * st; };
+  auto v_free = [&](int st) { return bar_base + 64u + 8u * st; };
+  auto s_full = [&](int b) { return bar_base + 80u + 8u * b; };
+  auto p_ready = [&](int b) { return bar_base + 96u + 8u * b; };
+  auto o_full = [&](int b) { return bar_base + 112u + 8u * b; };
+  auto o_free = [&](int b) { return bar_base + 128u + 8u * b; };
+  volatile unsigned *tmem_holder = reinterpret_cast<volatile unsigned *>(base_ptr + TB_BAR_OFF + 160);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + TB_BAR_OFF + 164);
+  volatile int *last_flag = reinterpret_cast<volatile int *>(base_ptr + TB_BAR_OFF + 168);
+  // per tile (slot = tile mod 4): maximum [group][row] and sum [group][row] of each thread's keys
   float *xch = reinterpret_cast<float *>(base_ptr + TB_XCH_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -144,16 +167,16 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
   }
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, TB_SOFTMAX_THREADS / 32);  // one arrival per softmax warp
-    mbar_init(o_full, 1);
-    mbar_init(s_read, TB_SOFTMAX_THREADS / 32);
     mbar_init(m_full, 1);
     for (int st = 0; st < TB_STAGES; ++st) {
       mbar_init(k_full(st), 1);
       mbar_init(v_full(st), 1);
       mbar_init(k_free(st), 1);
       mbar_init(v_free(st), 1);
+      mbar_init(s_full(st), 1);
+      mbar_init(p_ready(st), TB_SOFTMAX_THREADS / 32);  // one arrival per softmax warp
+      mbar_init(o_full(st), 1);
+      mbar_init(o_free(st), TB_SOFTMAX_THREADS / 32);
     }
     *abort_flag = 0;
     *last_flag = 0;
@@ -244,13 +267,13 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
           if (global_timer() - t0 > 3 * WAIT_LIMIT_NS) break;
     }
   } else if (warp == 1) {
-    // ---- MMA issuer: S(0), then per tile S(it+1) ahead of PV(it) so that the softmax of tile it+1
-    //      runs while the tensor pipe works on PV(it) ----
+    // ---- MMA issuer: S(0), S(1), then per tile P V(it) and, once it has completed (P of tile it lies
+    //      over S of tile it), S(it+2) into the same buffer ----
     const unsigned idesc_s = umma_idesc_f16(TB_BK);   // N = 128 keys
     const unsigned idesc_o = umma_idesc_f16(TB_DH);   // N = 64 output columns
     auto issue_s = [&](int it) {  // one chain: S = Q K^T over the 64 head dimensions, 16 per instruction
       const int st = it & 1;
-      const unsigned tmem_d = tmem_base + TB_S_COL;
+      const unsigned tmem_d = tmem_base + tb_s_col(st);
       const unsigned kb = base + TB_K_OFF + (unsigned)st * TB_K_BYTES;
       const unsigned long long a_hi = umma_desc_k128(base + TB_Q_OFF);
       const unsigned long long a_lo = umma_desc_k128(base + TB_Q_OFF + TB_SLAB);
@@ -267,68 +290,72 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
         const unsigned long long adv = (unsigned long long)(ks * 32 >> 4);
         tc_mma_f16(tmem_d, a_hi + adv, b_hi + adv, idesc_s, 1u);
       }
-      tc_commit(s_full);       // S complete
+      tc_commit(s_full(st));   // S complete
       tc_commit(k_free(st));   // and this stage of K may be overwritten
     };
     bool ok = mbar_wait_warp(q_full, 0u, abort_flag, err, 13);
-    if (ok) ok = mbar_wait_warp(k_full(0), 0u, abort_flag, err, 14);
-    if (ok) {
-      if (stamp && lane == 0) timeline[2] = global_timer();
+    for (int it = 0; it < min(2, ntiles) && ok; ++it) {
+      ok = mbar_wait_warp(k_full(it), 0u, abort_flag, err, 14);
+      if (!ok) break;
+      if (stamp && it == 0 && lane == 0) timeline[2] = global_timer();
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (lane == 0) issue_s(0);
+      if (lane == 0) issue_s(it);
       __syncwarp();
     }
     int pv_commits = 0;
     for (int it = 0; it < ntiles && ok; ++it) {
-      const unsigned ph = (unsigned)it & 1u;
-      if (it + 1 < ntiles) {
-        // S(it+1) overwrites S(it): every softmax warp must have read it
-        ok = mbar_wait_warp(s_read, ph, abort_flag, err, 21);
-        if (ok) ok = mbar_wait_warp(k_full((it + 1) & 1), (unsigned)((it + 1) >> 1) & 1u, abort_flag, err, 14);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (lane == 0) issue_s(it + 1);
-        __syncwarp();
-      }
-      ok = mbar_wait_warp(p_ready, ph, abort_flag, err, 15);  // P(it) stored, O(it-1) drained
-      if (ok) ok = mbar_wait_warp(v_full(it & 1), (unsigned)(it >> 1) & 1u, abort_flag, err, 16);
+      const int b = it & 1;
+      const unsigned ph = (unsigned)(it >> 1) & 1u;
+      ok = mbar_wait_warp(p_ready(b), ph, abort_flag, err, 15);  // P(it) stored
+      if (ok) ok = mbar_wait_warp(v_full(b), ph, abort_flag, err, 16);
+      if (ok && it >= 2) ok = mbar_wait_warp(o_free(b), ph ^ 1u, abort_flag, err, 21);  // O(it-2) read back
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (lane == 0) {
-        const unsigned p_hi = tmem_base + TB_PHI_COL, p_lo = tmem_base + TB_PLO_COL;
-        const unsigned vb = base + TB_V_OFF + (unsigned)(it & 1) * TB_V_BYTES;
+        const unsigned vb = base + TB_V_OFF + (unsigned)b * TB_V_BYTES;
 #pragma unroll
         for (int c = 0; c < TB_G; ++c) {
           // chain c covers the keys one softmax thread scales by its own maximum
-          const unsigned tmem_d = tmem_base + TB_O_COL + (unsigned)(c * TB_DH);
+          const unsigned tmem_d = tmem_base + tb_o_col(b) + (unsigned)(c * TB_DH);
+          const unsigned p_hi = tmem_base + tb_phi_col(b, c), p_lo = tmem_base + tb_plo_col(b, c);
           const int key0 = c * TB_KPT, slab = key0 / 64;  // a slab of the stage holds 64 keys (128-byte rows)
           const unsigned long long b_hi = umma_desc_k128(vb + slab * TB_VSLAB);
           const unsigned long long b_lo = umma_desc_k128(vb + (2 + slab) * TB_VSLAB);
 #pragma unroll
           for (int ks = 0; ks < TB_KPT / 16; ++ks) {
             const unsigned long long adv = (unsigned long long)(((key0 % 64) + ks * 16) * 2 >> 4);
-            const unsigned ac = (unsigned)((key0 + ks * 16) / 2);  // 16 keys = 8 columns
+            const unsigned ac = (unsigned)(ks * 8);  // 16 keys = 8 columns
             tc_mma_f16_ts(tmem_d, p_lo + ac, b_hi + adv, idesc_o, ks == 0 ? 0u : 1u);
             tc_mma_f16_ts(tmem_d, p_hi + ac, b_lo + adv, idesc_o, 1u);
           }
 #pragma unroll
           for (int ks = 0; ks < TB_KPT / 16; ++ks) {
             const unsigned long long adv = (unsigned long long)(((key0 % 64) + ks * 16) * 2 >> 4);
-            const unsigned ac = (unsigned)((key0 + ks * 16) / 2);
+            const unsigned ac = (unsigned)(ks * 8);
             tc_mma_f16_ts(tmem_d, p_hi + ac, b_hi + adv, idesc_o, 1u);
           }
         }
-        tc_commit(o_full);            // O chains complete; P may be overwritten
-        tc_commit(v_free(it & 1));    // and this stage of V^T
+        tc_commit(o_full(b));   // O chains complete; the S/P buffer may be overwritten
+        tc_commit(v_free(b));   // and this stage of V^T
       }
       __syncwarp();
       ++pv_commits;
+      if (it + 2 < ntiles) {
+        // S(it+2) goes where P(it) lies: after P V(it) has completed (long before its softmax is due)
+        ok = mbar_wait_warp(o_full(b), ph, abort_flag, err, 22);
+        if (ok) ok = mbar_wait_warp(k_full(b), ph ^ 1u, abort_flag, err, 14);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (lane == 0) issue_s(it + 2);
+        __syncwarp();
+      }
     }
     if (!ok) {  // give the tensor pipe a bounded chance to finish before TMEM is freed
-      if (lane == 0) tc_commit(o_full);
+      const int b = pv_commits & 1;
+      if (lane == 0) tc_commit(o_full(b));
       __syncwarp();
       const unsigned long long t0 = global_timer();
-      while (!mbar_try_wait(o_full, (unsigned)pv_commits & 1u))
+      while (!mbar_try_wait(o_full(b), (unsigned)(pv_commits >> 1) & 1u))
         if (global_timer() - t0 > WAIT_LIMIT_NS) break;
     }
     __syncwarp();
@@ -356,7 +383,7 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
 
     // O(t) = sum over chains c of chain c * 2^(m_c - M): each chain was scaled by the maximum of its own keys
     auto drain = [&](int t) {
-      const float *x = xch + (t & 1) * 2 * TB_G * TB_BQ;
+      const float *x = xch + (t & (TB_XCH_SLOTS - 1)) * 2 * TB_G * TB_BQ;
       float mc[TB_G], pc[TB_G];
       float m_new = m_run;
 #pragma unroll
@@ -371,7 +398,7 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
       for (int c = 0; c < TB_G; ++c)
 #pragma unroll
         for (int j0 = 0; j0 < TB_OC; j0 += 16)
-          tc_ld16(lane_base + TB_O_COL + (unsigned)(c * TB_DH + g * TB_OC + j0),
+          tc_ld16(lane_base + tb_o_col(t & 1) + (unsigned)(c * TB_DH + g * TB_OC + j0),
                   *reinterpret_cast<unsigned(*)[16]>(&cv[c][j0]));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       float ls = l_run * a;
@@ -389,9 +416,10 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
     };
 
     for (int it = 0; it < ntiles && ok; ++it) {
-      const unsigned ph = (unsigned)it & 1u;
+      const int b = it & 1;
+      const unsigned ph = (unsigned)(it >> 1) & 1u;
       const int kbase = (kt_begin + it) * TB_BK + g * TB_KPT;
-      ok = mbar_wait_warp(s_full, ph, abort_flag, err, 18);
+      ok = mbar_wait_warp(s_full(b), ph, abort_flag, err, 18);
       if (!ok) break;
       if (stamp && it == 0 && warp == 2 && lane == 0) timeline[3] = global_timer();
       if (stamp && nchunks == 1 && it >= 1 && it <= 4 && warp == 2 && lane == 0) timeline[11 + it] = global_timer();
@@ -401,11 +429,8 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
         unsigned t0[TB_KPT];
 #pragma unroll
         for (int j0 = 0; j0 < TB_KPT; j0 += 16)
-          tc_ld16(lane_base + TB_S_COL + (unsigned)(g * TB_KPT + j0), *reinterpret_cast<unsigned(*)[16]>(&t0[j0]));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(s_read);  // S may be overwritten by the next tile's product
+          tc_ld16(lane_base + tb_s_col(b) + (unsigned)(g * TB_KPT + j0), *reinterpret_cast<unsigned(*)[16]>(&t0[j0]));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");  // all of the thread's scores are in registers: P may go over them
 #pragma unroll
         for (int j = 0; j < TB_KPT; ++j) p[j] = __uint_as_float(t0[j]);
       }
@@ -437,13 +462,8 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
         }
       }
       const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
-      if (it > 0) {  // PV(it-1) complete: P may be overwritten, O(it-1) can be read
-        ok = mbar_wait_warp(o_full, ph ^ 1u, abort_flag, err, 19);
-        if (!ok) break;
-      }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       {
-        float *x = xch + (it & 1) * 2 * TB_G * TB_BQ;
+        float *x = xch + (it & (TB_XCH_SLOTS - 1)) * 2 * TB_G * TB_BQ;
         x[g * TB_BQ + r] = mx;
         x[(TB_G + g) * TB_BQ + r] = psum;
       }
@@ -460,17 +480,25 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap map_qk_hi, const __gri
           hi[j] = *reinterpret_cast<const unsigned *>(&h2);
           lo[j] = *reinterpret_cast<const unsigned *>(&l2);
         }
-        tc_st16(lane_base + TB_PHI_COL + (unsigned)(g * (TB_KPT / 2) + j0), hi);
-        tc_st16(lane_base + TB_PLO_COL + (unsigned)(g * (TB_KPT / 2) + j0), lo);
+        tc_st16(lane_base + tb_phi_col(b, g) + (unsigned)j0, hi);
+        tc_st16(lane_base + tb_plo_col(b, g) + (unsigned)j0, lo);
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       if (stamp && it == 0 && warp == 2 && lane == 0) timeline[4] = global_timer();
-      if (it > 0) drain(it - 1);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
+      if (lane == 0) mbar_arrive(p_ready(b));
+      if (it > 0) {  // P V(it-1) is complete or under way: read its accumulators back and hand the buffer on
+        ok = mbar_wait_warp(o_full(b ^ 1), (unsigned)((it - 1) >> 1) & 1u, abort_flag, err, 19);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        drain(it - 1);
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(o_free(b ^ 1));
+      }
     }
-    if (ok) ok = mbar_wait_warp(o_full, (unsigned)(ntiles - 1) & 1u, abort_flag, err, 19);
+    if (ok) ok = mbar_wait_warp(o_full((ntiles - 1) & 1), (unsigned)((ntiles - 1) >> 1) & 1u, abort_flag, err, 19);
     if (ok) {
       if (stamp && warp == 2 && lane == 0) timeline[5] = global_timer();
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
