@@ -255,8 +255,13 @@ def rank_streams(workload: str, world: int, rank: int):
 def make_rank_inputs(workload: str, first: int, count: int):
     key, _, plen, max_new, temp, top_k, top_p, cidx = WORKLOADS[workload]
     d = formats.CONFIG_DIMS[key]
-    arena = formats.make_param_arena(d, 1000 + cidx)
-    prompts = np.stack([formats.zipf_prompt(d.vocab, plen, 2000 * cidx + first + i) for i in range(count)])
+    if workload == "c1":
+        # the reference's own smoke case: the inputs of tests/golden/small_c1.npz (prompt "a b c ", biases drawn)
+        arena = formats.make_param_arena(d, 1001, bias_std=0.02)
+        prompts = np.stack([np.array([0, 1, 2, 1, 3, 1], dtype=np.int32) for _ in range(count)])
+    else:
+        arena = formats.make_param_arena(d, 1000 + cidx)
+        prompts = np.stack([formats.zipf_prompt(d.vocab, plen, 2000 * cidx + first + i) for i in range(count)])
     seeds = np.array([3000 + first + i for i in range(count)], dtype=np.uint32)
     return d, arena, prompts, seeds, (plen, max_new, temp, top_k, top_p)
 
@@ -272,6 +277,12 @@ def check_against_fixture(workload: str, first: int, tokens: np.ndarray):
             z = np.load(os.path.join(gold, "c2_full.npz"))
             ref, got, gaps = z["greedy_tokens"], tokens[0], z["top2_gap"]
             name = "tests/golden/c2_full.npz"
+        elif workload == "c1" and first == 0:
+            z = np.load(os.path.join(gold, "small_c1.npz"))
+            step = z["greedy_step_logits"].astype(np.float64)
+            srt = np.sort(step, axis=1)
+            ref, got, gaps = z["greedy_tokens"], tokens[0], (srt[:, -1] - srt[:, -2])
+            name = "tests/golden/small_c1.npz (written by the reference itself)"
         elif workload == "c5" and first == 0:
             z = np.load(os.path.join(gold, "c5_dims.npz"))
             ref, gaps = z["greedy_tokens"], z["top2_gap"]
