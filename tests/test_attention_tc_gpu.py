@@ -150,3 +150,34 @@ def test_fixed_head_scales_with_skewed_weights(oracle, seq):
     assert np.isfinite(got).all()
     assert rel_err(got[0], want) < LOGIT_RTOL
     assert np.array_equal(got[0], got[1])
+
+
+class tf32_pair_attention:
+    """Sessions created inside this block keep Q, K and V^T as TF32 pairs (attention_tc.cu)."""
+
+    def __enter__(self):
+        self.old = os.environ.get("LITNICE_B200_ATTN16")
+        os.environ["LITNICE_B200_ATTN16"] = "0"
+
+    def __exit__(self, *exc):
+        if self.old is None:
+            del os.environ["LITNICE_B200_ATTN16"]
+        else:
+            os.environ["LITNICE_B200_ATTN16"] = self.old
+
+
+@pytest.mark.parametrize("streams,seq", [(1, 300), (19, 512)])
+def test_tf32_pair_kernel_matches_oracle_and_fp16_pair_kernel(oracle, arena, streams, seq):
+    """The kernel behind LITNICE_B200_ATTN16=0 (split-key and multi-tile schedules) against the
+    oracle, and the default fp16-pair kernel against it."""
+    ids = np.stack([formats.zipf_prompt(DIMS.vocab, seq, 800 + b) for b in range(streams)])
+    with tf32_pair_attention():
+        with Session(DIMS, streams) as s:
+            s.load_params(arena)
+            old = s.forward(ids, all_rows=True)
+    with Session(DIMS, streams) as s:
+        s.load_params(arena)
+        new = s.forward(ids, all_rows=True)
+    for b in (0, streams - 1):
+        assert rel_err(old[b], oracle.forward(DIMS, arena, ids[b])) < LOGIT_RTOL
+    assert rel_err(new, old) < KERNEL_RTOL
