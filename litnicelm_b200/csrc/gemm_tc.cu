@@ -401,9 +401,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
   if (go && ep.has_vt())
     tc_store_vt<BN, tc_threads(BN)>(ep, m, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits, rows_each, row_begin,
                                     row_end);
-  if (go && !(ep.has_vt() && n0 >= ep.vt_col0))  // a tile of V columns only has left already
-    tc_store_rows<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits, rows_each,
-                                      row_begin, row_end, first);
+  if (go && !(ep.has_vt() && n0 >= ep.vt_col0)) {  // a tile of V columns only has left already
+    // the token loop's three forms with their terms fixed at compile time (a loop body that stays in
+    // the instruction cache), everything else through the general form
+    const unsigned form = tc_ep_form(ep);
+    if (F16 && form == TC_EP_FORM_QKV)
+      tc_store_rows<BN, tc_threads(BN), TC_EP_FORM_QKV>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits,
+                                                        rows_each, row_begin, row_end, first);
+    else if (F16 && form == TC_EP_FORM_W1)
+      tc_store_rows<BN, tc_threads(BN), TC_EP_FORM_W1>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits,
+                                                       rows_each, row_begin, row_end, first);
+    else if (F16 && form == TC_EP_FORM_RES)
+      tc_store_rows<BN, tc_threads(BN), TC_EP_FORM_RES>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits,
+                                                        rows_each, row_begin, row_end, first);
+    else
+      tc_store_rows<BN, tc_threads(BN)>(ep, m, n, m0, n0, (int)threadIdx.x, stage, row_stats, cluster_splits, rows_each,
+                                        row_begin, row_end, first);
+  }
   if (stamp && warp == 2 && lane == 0) ep.timeline[12] = global_timer();
   if (ep.stats_out != nullptr) {
     asm volatile("bar.sync 2, %0;" ::"n"(tc_threads(BN)) : "memory");

@@ -11,13 +11,14 @@ namespace lb {
 // terms (bias, folded-LayerNorm u) and the residual rows of the first step. Loaded ahead of
 // it (before the wait for the cluster's partial tiles), because the store loop would
 // otherwise start with an L2 round trip. Same thread-to-element mapping as tc_store_rows.
-#ifndef LB_STORE_G
-#define LB_STORE_G 2
-#endif
-constexpr int TC_STORE_G = LB_STORE_G;  // rows a thread of the store phase has in flight per trip
+// Rows a thread of the store phase has in flight per trip. Measured: one for tiles up to 128 columns
+// (the single-stream shapes: 2696 against 2650 tokens/s at config 2 with two), two for the 256-column
+// tiles of the many-row shapes (config 4: 80.6 against 82.3 ms with one); four is slower everywhere.
+__host__ __device__ constexpr int tc_store_g(int bn) { return bn > 128 ? 2 : 1; }
+constexpr int TC_STORE_G_MAX = 2;
 
 struct TcStoreFirst {
-  float4 res[TC_STORE_G];
+  float4 res[TC_STORE_G_MAX];
   float4 uu, bb;
 };
 template <int BN, int NT>
@@ -31,7 +32,7 @@ __device__ __forceinline__ void tc_store_first(const TcEpilogue &ep, int m, int 
   out.uu = ep.ln_u != nullptr ? __ldg(reinterpret_cast<const float4 *>(ep.ln_u + col)) : zero4;
   out.bb = ep.bias != nullptr ? __ldg(reinterpret_cast<const float4 *>(ep.bias + col)) : zero4;
 #pragma unroll
-  for (int g = 0; g < TC_STORE_G; ++g) {
+  for (int g = 0; g < tc_store_g(BN); ++g) {
     const int rg = row_begin + r0 + g * RPT;
     out.res[g] = (ep.residual != nullptr && rg < row_end && m0 + rg < m)
                      ? __ldg(reinterpret_cast<const float4 *>(ep.residual + (long long)(m0 + rg) * n + col))
@@ -51,23 +52,49 @@ __device__ __forceinline__ void tc_store_first(const TcEpilogue &ep, int m, int 
 // every rank has pushed its partial sums of those rows into this CTA's staging area, rank z
 // at rows [z * rows_each, z * rows_each + row_end - row_begin), and they are added in rank
 // order. Otherwise the area holds the tile itself (row_begin 0).
-template <int BN, int NT>
+// The loop runs out of the instruction cache of a scheduler only when its body is small: with every
+// epilogue term and output format behind run-time tests the body is several hundred instructions and
+// each trip is fetched again (two rows per trip measured faster than four, one faster than two). F
+// names the terms at compile time (TC_EP_* bits) for the forms the token loop uses; TC_EP_GENERIC
+// keeps the run-time tests for every other caller.
+constexpr unsigned TC_EP_FOLD = 1u, TC_EP_RELU = 2u, TC_EP_RESIDUAL = 4u, TC_EP_C = 8u, TC_EP_SPLIT = 16u,
+                   TC_EP_QK16 = 32u, TC_EP_F16 = 64u, TC_EP_STATS = 128u, TC_EP_BIAS = 256u, TC_EP_GENERIC = 1u << 31;
+// the three forms of the fp16-pair token loop
+constexpr unsigned TC_EP_FORM_QKV = TC_EP_FOLD | TC_EP_BIAS | TC_EP_QK16;
+constexpr unsigned TC_EP_FORM_W1 = TC_EP_FOLD | TC_EP_BIAS | TC_EP_RELU | TC_EP_F16;
+constexpr unsigned TC_EP_FORM_RES = TC_EP_BIAS | TC_EP_RESIDUAL | TC_EP_C | TC_EP_F16 | TC_EP_STATS;
+__device__ __forceinline__ unsigned tc_ep_form(const TcEpilogue &ep) {
+  return (ep.ln_u != nullptr ? TC_EP_FOLD : 0u) | (ep.relu ? TC_EP_RELU : 0u) | (ep.residual != nullptr ? TC_EP_RESIDUAL : 0u) |
+         (ep.c != nullptr ? TC_EP_C : 0u) | (ep.c_hi != nullptr ? TC_EP_SPLIT : 0u) | (ep.qk16_hi != nullptr ? TC_EP_QK16 : 0u) |
+         (ep.c_f16.hi != nullptr ? TC_EP_F16 : 0u) | (ep.stats_out != nullptr ? TC_EP_STATS : 0u) |
+         (ep.bias != nullptr ? TC_EP_BIAS : 0u);
+}
+
+template <int BN, int NT, unsigned F = TC_EP_GENERIC>
 __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n, int m0, int n0, int tid,
                                               float *stage, const float2 *row_stats, int csplits, int rows_each,
                                               int row_begin, int row_end, const TcStoreFirst &first) {
+  constexpr bool GEN = (F & TC_EP_GENERIC) != 0;
+  const bool has_relu = GEN ? ep.relu != 0 : (F & TC_EP_RELU) != 0;
+  const bool has_res = GEN ? ep.residual != nullptr : (F & TC_EP_RESIDUAL) != 0;
+  const bool out_c = GEN ? ep.c != nullptr : (F & TC_EP_C) != 0;
+  const bool out_split = GEN ? ep.c_hi != nullptr : (F & TC_EP_SPLIT) != 0;
+  const bool out_qk16 = GEN ? ep.qk16_hi != nullptr : (F & TC_EP_QK16) != 0;
+  const bool out_f16 = GEN ? ep.c_f16.hi != nullptr : (F & TC_EP_F16) != 0;
+  const bool out_stats = GEN ? ep.stats_out != nullptr : (F & TC_EP_STATS) != 0;
   constexpr int LDS = BN + 4;
   constexpr int PER_ROW = BN / 4;
   static_assert(NT % PER_ROW == 0 && NT % 32 == 0, "a thread keeps its column; whole warps");
   constexpr int RPT = NT / PER_ROW;  // rows covered by the threads at once
-  constexpr int G = TC_STORE_G;
+  constexpr int G = tc_store_g(BN);
   const int c4 = tid % PER_ROW, r0 = tid / PER_ROW;
   const int col = n0 + c4 * 4;
   const bool col_active = !(ep.has_vt() && col >= ep.vt_col0);  // V columns leave transposed, elsewhere
-  const float cs16 = ep.qk16_hi != nullptr ? __ldg(ep.col_scale + col / 64) : 1.f;
-  const bool fold = ep.ln_u != nullptr;
+  const float cs16 = out_qk16 ? __ldg(ep.col_scale + col / 64) : 1.f;
+  const bool fold = GEN ? ep.ln_u != nullptr : (F & TC_EP_FOLD) != 0;
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
   const float4 uu = first.uu, bb = first.bb;
-  const float *res_col = ep.residual ? ep.residual + (long long)m0 * n + col : nullptr;
+  const float *res_col = has_res ? ep.residual + (long long)m0 * n + col : nullptr;
   auto residual_row = [&](int rg) {
     return (res_col != nullptr && rg < row_end && m0 + rg < m) ? __ldg(reinterpret_cast<const float4 *>(res_col + (long long)rg * n))
                                                                : zero4;
@@ -107,7 +134,7 @@ __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n
       v[g].y += bb.y + res[g].y;
       v[g].z += bb.z + res[g].z;
       v[g].w += bb.w + res[g].w;
-      if (ep.relu) {
+      if (has_relu) {
         v[g].x = fmaxf(v[g].x, 0.f); v[g].y = fmaxf(v[g].y, 0.f);
         v[g].z = fmaxf(v[g].z, 0.f); v[g].w = fmaxf(v[g].w, 0.f);
       }
@@ -118,8 +145,8 @@ __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n
       if (!act[g]) continue;
       const int rg = rr + g * RPT;
       const long long off = (long long)(m0 + rg) * n + col;
-      if (ep.c) *reinterpret_cast<float4 *>(ep.c + off) = v[g];
-      if (ep.c_hi) {
+      if (out_c) *reinterpret_cast<float4 *>(ep.c + off) = v[g];
+      if (out_split) {
         float4 hh, ll;
         split_tf32(v[g].x, hh.x, ll.x);
         split_tf32(v[g].y, hh.y, ll.y);
@@ -128,16 +155,16 @@ __device__ __forceinline__ void tc_store_rows(const TcEpilogue &ep, int m, int n
         *reinterpret_cast<float4 *>(ep.c_hi + off) = hh;
         *reinterpret_cast<float4 *>(ep.c_lo + off) = ll;
       }
-      if (ep.qk16_hi) {  // fp16 pair under the head's fixed scale
+      if (out_qk16) {  // fp16 pair under the head's fixed scale
         uint2 hi, lo;
         f16_pair4(v[g], cs16, hi, lo);
         *reinterpret_cast<uint2 *>(ep.qk16_hi + off) = hi;
         *reinterpret_cast<uint2 *>(ep.qk16_lo + off) = lo;
       }
-      if (ep.stats_out != nullptr)  // final values, over the thread's own rank-0 partial
+      if (out_stats)  // final values, over the thread's own rank-0 partial
         *reinterpret_cast<float4 *>(stage + (rg - row_begin) * LDS + c4 * 4) = v[g];
     }
-    if (ep.c_f16.hi != nullptr) {
+    if (out_f16) {
       // fp16 pair: the 16 lanes of a 64-column block of a row agree on its scale
 #pragma unroll
       for (int g = 0; g < G; ++g) {
