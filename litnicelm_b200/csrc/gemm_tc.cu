@@ -702,7 +702,12 @@ TcPlan tc_plan(int m, int n, int k, bool has64, bool has128, bool has256, int k_
     // A long k on few tiles: a 128-column tile halves the tile count, so twice the k ranges fit,
     // and it reads less shared memory per flop; its larger epilogue costs about three k-blocks.
     // Only as clusters (the partial sums of a wide tile through global scratch are too slow).
-    if (clusters_ok && tc_clusters_enabled() && p.bn == 64 && has128) {
+    // LITNICE_B200_PLAN_WIDE=0 keeps the 64-column tiles (a knob for comparisons).
+    static const bool plan_wide = [] {
+      const char *e = std::getenv("LITNICE_B200_PLAN_WIDE");
+      return !(e && e[0] == '0');
+    }();
+    if (plan_wide && clusters_ok && tc_clusters_enabled() && p.bn == 64 && has128) {
       const int *cap = tc_cluster_capacity();
       const long long wide = mt * (n / 128);
       int s2 = (int)(148 / wide);
