@@ -41,7 +41,7 @@ namespace {
 // helper warps that only take part in the store phase, which is bound by instruction latency and
 // wants as many warps as the register file allows.
 __host__ __device__ constexpr int tc_drain_warps(int bn) { return bn == 64 ? 4 : 8; }
-__host__ __device__ constexpr int tc_threads(int bn) { return bn > 128 ? 320 : 512; }
+__host__ __device__ constexpr int tc_threads(int bn) { return bn > 128 ? 384 : 512; }
 template <int BN, int STAGES>
 struct TcSmem {
   static constexpr int A_BYTES = TC_BM * TC_BK * 4;  // 16 KiB
