@@ -75,13 +75,23 @@ __global__ void sum_squares_kernel(const float *__restrict__ x, long long n, dou
 
 __global__ void ordered_sum_kernel(const double *__restrict__ partial, int count, double scale, double *out_f64,
                                    float *out_f32) {
-  // One warp: lanes fetch 32 consecutive terms at a time (one round trip instead of 32), lane 0
-  // adds them in index order, which keeps the sum identical to a sequential loop.
+  // One warp: the lanes bring 256 consecutive terms at a time into shared memory (eight loads in
+  // flight per lane), lane 0 adds them in index order from there (a chain of dependent adds, four
+  // clocks each, instead of a shuffle per term), which keeps the sum identical to a sequential loop.
+  __shared__ double terms[256];
   double acc = 0.0;
-  for (int i0 = 0; i0 < count; i0 += 32) {
-    const int i = i0 + (int)threadIdx.x;
-    const double mine = i < count ? partial[i] : 0.0;
-    for (int j = 0; j < 32 && i0 + j < count; ++j) acc += __shfl_sync(0xffffffffu, mine, j);
+  for (int i0 = 0; i0 < count; i0 += 256) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = i0 + j * 32 + (int)threadIdx.x;
+      terms[j * 32 + threadIdx.x] = i < count ? partial[i] : 0.0;
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) {
+      const int n = min(256, count - i0);
+      for (int j = 0; j < n; ++j) acc += terms[j];
+    }
+    __syncwarp();
   }
   if (threadIdx.x != 0) return;
   acc *= scale;
@@ -232,20 +242,35 @@ __global__ void embedding_grad_pos_kernel(RowView d_cur, long long tokens, long 
 
 __global__ void embedding_grad_tok_kernel(const char *ids, int ids_is_f32, RowView iv, RowView d_cur, long long tokens,
                                           RowView d_tok, long long vocab, DevErr *err) {
+  // Thread = one column of the embedding rows whose id falls into this CTA's class (id mod classes):
+  // it walks the tokens in order, so every element of d_tok receives its additions in token order as
+  // the CPU loop does. The ids come through shared memory in pieces (one coalesced load per token
+  // instead of a dependent global load per token and thread); -1 marks an id out of range or of
+  // another class.
+  constexpr int PIECE = 1024;
+  __shared__ int sid[PIECE];
   const long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   const int klass = blockIdx.y, classes = gridDim.y;
-  for (long long t = 0; t < tokens; ++t) {
-    const long long id = load_index(ids, ids_is_f32, iv, t);
-    if (id < 0 || id >= vocab) {
-      if (klass == 0 && c == 0) {
+  for (long long t0 = 0; t0 < tokens; t0 += PIECE) {
+    const int n = (int)(tokens - t0 < PIECE ? tokens - t0 : PIECE);
+    __syncthreads();
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+      const long long id = load_index(ids, ids_is_f32, iv, t0 + j);
+      const bool bad = id < 0 || id >= vocab;
+      if (bad && klass == 0 && blockIdx.x == 0) {
         err->code = DEVERR_BAD_TOKEN_ID;
         err->detail = (int)id;
       }
-      continue;
+      sid[j] = (bad || (int)(id % classes) != klass) ? -1 : (int)id;  // only this CTA's class is kept
     }
-    if ((int)(id % classes) != klass || c >= d_cur.cols) continue;
-    const long long to = row_offset(d_tok, id);
-    st(d_tok, to, c, ld(d_tok, to, c) + ld(d_cur, row_offset(d_cur, t), c));
+    __syncthreads();
+    if (c >= d_cur.cols) continue;
+    for (int j = 0; j < n; ++j) {
+      const int id = sid[j];
+      if (id < 0) continue;
+      const long long to = row_offset(d_tok, id);
+      st(d_tok, to, c, ld(d_tok, to, c) + ld(d_cur, row_offset(d_cur, t0 + j), c));
+    }
   }
 }
 
