@@ -232,8 +232,9 @@ def run_reference_arm(args, rank, world):
 
 def workload_name(workload, streams, plen, max_new):
     d = formats.CONFIG_DIMS[WORKLOADS[workload][0]]
+    prompt = 'the prompt "a b c " of the reference\'s smoke script' if workload == "c1" else f"{plen}-token Zipf(1.1) prompt"
     return (f"{workload}: L{d.n_layers} H{d.n_heads} D{d.d_model} F{d.d_ff} V{d.vocab} S{d.max_seq}, "
-            f"{streams} stream(s)/GPU, {plen}-token Zipf(1.1) prompt, {max_new} new tokens, "
+            f"{streams} stream(s)/GPU, {prompt}, {max_new} new tokens, "
             "whole-context recomputation per token")
 
 
